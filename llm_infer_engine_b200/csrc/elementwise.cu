@@ -1,0 +1,298 @@
+// Memory-bound parts of a step: embedding gather, residual add fused with RMSNorm,
+// SwiGLU, rotary position encoding fused with the KV-cache write, and the small kernels
+// that keep per-sequence lengths on the device. The residual stream is float32 in both
+// precisions; activations between GEMMs are T (float or bfloat16).
+#include "common.cuh"
+
+namespace llmie {
+
+// ------------------------------------------------------------------------------------------
+// h[t, :] = table[token[t], :]         (src/model.py:157 of the reference: a plain row gather)
+template <typename W>
+__global__ void embedding_kernel(const int* __restrict__ tokens, const W* __restrict__ table,
+                                 float* __restrict__ h, int d, int vocab) {
+  const int t = blockIdx.x;
+  int id = tokens[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // the host refuses such ids; never read outside
+  const W* row = table + (size_t)id * d;
+  float* out = h + (size_t)t * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) out[i] = to_f32(row[i]);
+}
+
+// ------------------------------------------------------------------------------------------
+// Residual add + RMSNorm (src/rms_norm.py:32-39 and src/model.py:113-127 of the reference):
+//   r = rows ? rows[b] : b
+//   x = h[r] (+ delta[r])                     float32 sum
+//   if (!rows && delta) h[r] = x              the residual stream is updated in place
+//   y[b] = x * rsqrt(mean(x^2) + eps) * w     one rounding, at the store
+// One block per output row; the row is held in shared memory between the two passes.
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ delta,
+                                   const float* __restrict__ w, T* __restrict__ y,
+                                   const int* __restrict__ rows, int d, float eps) {
+  extern __shared__ float row_buf[];
+  __shared__ float red[32];
+  const int b = blockIdx.x;
+  const int r = rows ? rows[b] : b;
+  float* hr = h + (size_t)r * d;
+  const T* dr = delta ? delta + (size_t)r * d : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float x = hr[i];
+    if (dr) {
+      x += to_f32(dr[i]);
+      if (!rows) hr[i] = x;
+    }
+    row_buf[i] = x;
+    ss += x * x;
+  }
+  ss = block_sum(ss, red);
+  const float rstd = rsqrtf(ss / (float)d + eps);
+  T* yr = y + (size_t)b * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) yr[i] = from_f32<T>(row_buf[i] * rstd * w[i]);
+}
+
+// h += delta, no norm (used when a block arrangement needs the bare sum)
+template <typename T>
+__global__ void residual_add_kernel(float* __restrict__ h, const T* __restrict__ delta, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) h[i] += to_f32(delta[i]);
+}
+
+// ------------------------------------------------------------------------------------------
+// out[t, j] = silu(gate_up[t, j]) * gate_up[t, ff + j]      (src/model.py:23 of the reference)
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int ff, size_t total) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const size_t t = i / ff;
+    const int j = (int)(i - t * ff);
+    const float g = to_f32(gate_up[t * 2 * ff + j]);
+    const float u = to_f32(gate_up[t * 2 * ff + ff + j]);
+    const float s = g / (1.f + expf(-g));
+    out[i] = from_f32<T>(s * u);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Rotary position encoding fused with the KV-cache write
+// (src/rope.py:74-91 rotate-half, :122-185 the fused K rotation + cache write of the reference).
+//   qkv[t] = [ q heads | k heads | v heads ], each head `hd` wide
+//   q_out[t, h] = rot(q)          k_cache[page(t), hk, pos % P] = rot(k)       v_cache[...] = v
+// rot pairs element i with i + rot_dim/2 for i < rot_dim/2 using table[pos] = (cos, sin);
+// elements >= rot_dim pass through. table == nullptr means no rotation at all.
+// With write_kv == 0 only q is produced (a layer that reads another layer's cache).
+template <typename T>
+__global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out,
+                                  T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                  const float2* __restrict__ table, const int* __restrict__ tok_pos,
+                                  const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
+                                  const int* __restrict__ block_table, int max_pages, int page_size,
+                                  int n_q, int n_kv, int hd, int rot_dim, int table_len, int write_kv) {
+  const int t = blockIdx.x;
+  int pos = tok_pos[t];
+  const int half = rot_dim >> 1;
+  const int row_w = (n_q + 2 * n_kv) * hd;
+  const T* src = qkv + (size_t)t * row_w;
+  const int tpos = pos < table_len ? pos : table_len - 1;  // the host refuses pos >= table_len
+  const float2* cs = table ? table + (size_t)tpos * half : nullptr;
+
+  // q heads: items are (head, i) with i < hd; rotated pairs are produced by the thread of i < half
+  const int q_items = n_q * hd;
+  T* qo = q_out + (size_t)t * q_items;
+  for (int it = threadIdx.x; it < q_items; it += blockDim.x) {
+    const int i = it % hd;
+    const int base = it - i;
+    if (cs && i < rot_dim) {
+      if (i < half) {
+        const float x1 = to_f32(src[base + i]), x2 = to_f32(src[base + i + half]);
+        const float2 c = cs[i];
+        qo[base + i] = from_f32<T>(x1 * c.x - x2 * c.y);
+        qo[base + i + half] = from_f32<T>(x2 * c.x + x1 * c.y);
+      }
+    } else {
+      qo[base + i] = src[base + i];
+    }
+  }
+  if (!write_kv) return;
+
+  const int slot = seq_slot[tok_seq[t]];
+  const int page = block_table[(size_t)slot * max_pages + pos / page_size];
+  const int in_page = pos % page_size;
+  const int kv_items = n_kv * hd;
+  const T* ks = src + q_items;
+  const T* vs = ks + kv_items;
+  for (int it = threadIdx.x; it < kv_items; it += blockDim.x) {
+    const int i = it % hd;
+    const int hk = it / hd;
+    const size_t dst = (((size_t)page * n_kv + hk) * page_size + in_page) * hd;
+    v_cache[dst + i] = vs[it];
+    if (cs && i < rot_dim) {
+      if (i < half) {
+        const float x1 = to_f32(ks[it]), x2 = to_f32(ks[it + half]);
+        const float2 c = cs[i];
+        k_cache[dst + i] = from_f32<T>(x1 * c.x - x2 * c.y);
+        k_cache[dst + i + half] = from_f32<T>(x2 * c.x + x1 * c.y);
+      }
+    } else {
+      k_cache[dst + i] = ks[it];
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Decode-step metadata from the device-resident lengths, so that a captured step needs no
+// host rewrites: lane i continues sequence slots[i] by one token at position len[slot].
+__global__ void prepare_decode_kernel(const int* __restrict__ slots, const int* __restrict__ seq_lens,
+                                      int* __restrict__ tok_pos, int* __restrict__ tok_seq,
+                                      int* __restrict__ cu_q, int* __restrict__ seq_start,
+                                      int* __restrict__ seq_kvlen, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    const int len = seq_lens[slots[i]];
+    tok_pos[i] = len;
+    tok_seq[i] = i;
+    cu_q[i] = i;
+    seq_start[i] = len;
+    seq_kvlen[i] = len + 1;
+  }
+  if (i == 0) cu_q[n] = n;
+}
+
+// seq_lens[slot] = kv length after the step, except for the scratch slot that padding lanes use.
+__global__ void advance_lengths_kernel(const int* __restrict__ slots, const int* __restrict__ seq_kvlen,
+                                       int* __restrict__ seq_lens, int n, int scratch_slot) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    const int s = slots[i];
+    if (s != scratch_slot) seq_lens[s] = seq_kvlen[i];
+  }
+}
+
+static inline int norm_threads(int d) {
+  int t = (d + 7) / 8;
+  t = ((t + 31) / 32) * 32;
+  return t < 32 ? 32 : (t > 1024 ? 1024 : t);
+}
+
+}  // namespace llmie
+
+using namespace llmie;
+
+extern "C" int llmie_embedding(const int* tokens, const void* table, int table_dtype, float* h, int n_tokens,
+                               int d, int vocab, cudaStream_t stream) {
+  if (n_tokens < 0 || d <= 0 || vocab <= 0) return LLMIE_ERR_BAD_ARG;
+  if (n_tokens == 0) return LLMIE_OK;
+  const int threads = norm_threads(d);
+  if (table_dtype == LLMIE_F32)
+    embedding_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, h, d, vocab);
+  else if (table_dtype == LLMIE_BF16)
+    embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, h, d, vocab);
+  else
+    return LLMIE_ERR_DTYPE;
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+template <typename T>
+static int add_rmsnorm_launch(float* h, const void* delta, const float* w, void* y, const int* rows, int n_out,
+                              int d, float eps, cudaStream_t stream) {
+  const size_t smem = (size_t)d * sizeof(float);
+  if (smem > 200 * 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  add_rmsnorm_kernel<T><<<n_out, norm_threads(d), smem, stream>>>(h, (const T*)delta, w, (T*)y, rows, d, eps);
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+// y[n_out, d] (dtype) from h[*, d] float32; delta (dtype) and rows may be null.
+extern "C" int llmie_add_rmsnorm(float* h, const void* delta, const float* w, void* y, const int* rows, int n_out,
+                                 int d, float eps, int dtype, cudaStream_t stream) {
+  if (n_out < 0 || d <= 0) return LLMIE_ERR_BAD_ARG;
+  if (n_out == 0) return LLMIE_OK;
+  if (dtype == LLMIE_F32) return add_rmsnorm_launch<float>(h, delta, w, y, rows, n_out, d, eps, stream);
+  if (dtype == LLMIE_BF16) return add_rmsnorm_launch<__nv_bfloat16>(h, delta, w, y, rows, n_out, d, eps, stream);
+  return LLMIE_ERR_DTYPE;
+}
+
+extern "C" int llmie_residual_add(float* h, const void* delta, long long n, int dtype, cudaStream_t stream) {
+  if (n < 0) return LLMIE_ERR_BAD_ARG;
+  if (n == 0) return LLMIE_OK;
+  const int threads = 256;
+  long long blocks = (n + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == LLMIE_F32)
+    residual_add_kernel<float><<<(int)blocks, threads, 0, stream>>>(h, (const float*)delta, (size_t)n);
+  else if (dtype == LLMIE_BF16)
+    residual_add_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>(h, (const __nv_bfloat16*)delta, (size_t)n);
+  else
+    return LLMIE_ERR_DTYPE;
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+extern "C" int llmie_swiglu(const void* gate_up, void* out, int n_tokens, int ff, int dtype, cudaStream_t stream) {
+  if (n_tokens < 0 || ff <= 0) return LLMIE_ERR_BAD_ARG;
+  const size_t total = (size_t)n_tokens * ff;
+  if (total == 0) return LLMIE_OK;
+  const int threads = 256;
+  size_t blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (dtype == LLMIE_F32)
+    swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, ff, total);
+  else if (dtype == LLMIE_BF16)
+    swiglu_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up,
+                                                                     (__nv_bfloat16*)out, ff, total);
+  else
+    return LLMIE_ERR_DTYPE;
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+extern "C" int llmie_rope_store(const void* qkv, void* q_out, void* k_cache, void* v_cache, const float* table,
+                                const int* tok_pos, const int* tok_seq, const int* seq_slot,
+                                const int* block_table, int max_pages, int page_size, int n_tokens, int n_q,
+                                int n_kv, int hd, int rot_dim, int table_len, int write_kv, int dtype,
+                                cudaStream_t stream) {
+  if (n_tokens < 0 || n_q <= 0 || n_kv < 0 || hd <= 0 || page_size <= 0 || max_pages <= 0) return LLMIE_ERR_BAD_ARG;
+  if (rot_dim < 0 || rot_dim > hd || (rot_dim & 1)) return LLMIE_ERR_BAD_ARG;
+  if (table && table_len <= 0) return LLMIE_ERR_BAD_ARG;
+  if (n_tokens == 0) return LLMIE_OK;
+  int threads = ((n_q * hd / 2 + 31) / 32) * 32;
+  threads = threads < 64 ? 64 : (threads > 512 ? 512 : threads);
+  const float2* tab = reinterpret_cast<const float2*>(table);
+  if (dtype == LLMIE_F32)
+    rope_store_kernel<float><<<n_tokens, threads, 0, stream>>>(
+        (const float*)qkv, (float*)q_out, (float*)k_cache, (float*)v_cache, tab, tok_pos, tok_seq, seq_slot,
+        block_table, max_pages, page_size, n_q, n_kv, hd, rot_dim, table_len, write_kv);
+  else if (dtype == LLMIE_BF16)
+    rope_store_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+        (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tab,
+        tok_pos, tok_seq, seq_slot, block_table, max_pages, page_size, n_q, n_kv, hd, rot_dim, table_len, write_kv);
+  else
+    return LLMIE_ERR_DTYPE;
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+extern "C" int llmie_prepare_decode(const int* slots, const int* seq_lens, int* tok_pos, int* tok_seq, int* cu_q,
+                                    int* seq_start, int* seq_kvlen, int n, cudaStream_t stream) {
+  if (n <= 0) return LLMIE_ERR_BAD_ARG;
+  prepare_decode_kernel<<<(n + 127) / 128, 128, 0, stream>>>(slots, seq_lens, tok_pos, tok_seq, cu_q, seq_start,
+                                                             seq_kvlen, n);
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+extern "C" int llmie_advance_lengths(const int* slots, const int* seq_kvlen, int* seq_lens, int n, int scratch_slot,
+                                     cudaStream_t stream) {
+  if (n <= 0) return LLMIE_ERR_BAD_ARG;
+  advance_lengths_kernel<<<(n + 127) / 128, 128, 0, stream>>>(slots, seq_kvlen, seq_lens, n, scratch_slot);
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}

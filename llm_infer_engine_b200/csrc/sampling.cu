@@ -1,0 +1,179 @@
+// Token choice on the device: argmax, and temperature sampling with a top-p cut.
+//
+// The reference samples with torch ops on the logits (src/sampler.py:4-33): temperature <= 0
+// is argmax; otherwise softmax(logits / T), tokens sorted by falling probability are dropped
+// once the mass BEFORE them exceeds top_p (the first is always kept), the rest is renormalised
+// and one token is drawn. Here one block per row does the same in float32 without a sort:
+//   w_i = exp((x_i - max) / T),  Z = sum w
+//   S(t) = sum of w_i > t;  kept = { i : S(w_i) <= top_p * Z }, found by bisection on the bits of t
+//   draw: inverse CDF over token ids among the kept, at u * (kept mass)
+// u is a counter-based uniform number from (seed, sequence id, how many tokens that sequence
+// has drawn), so a sequence's draws do not depend on what else is in the batch.
+#include "common.cuh"
+#include <math.h>
+
+namespace llmie {
+
+constexpr int kSampleThreads = 1024;
+
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
+  z ^= z >> 30; z *= 0xbf58476d1ce4e5b9ULL;
+  z ^= z >> 27; z *= 0x94d049bb133111ebULL;
+  z ^= z >> 31;
+  return z;
+}
+// 24 random bits scaled into [0, 1): exact in float32.
+__device__ __forceinline__ float uniform24(unsigned long long seed, int seq_id, int counter) {
+  unsigned long long x = mix64(seed + 0x9E3779B97F4A7C15ULL * (unsigned long long)(seq_id + 1));
+  x = mix64(x + 0x9E3779B97F4A7C15ULL * (unsigned long long)(counter + 1));
+  return (float)(x >> 40) * (1.0f / 16777216.0f);
+}
+
+struct MaxIdx { float v; int i; };
+__device__ __forceinline__ MaxIdx better(MaxIdx a, MaxIdx b) {
+  return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
+}
+
+// argmax over a row with 1024 threads; ties go to the lowest index. NaN never wins.
+__device__ MaxIdx block_argmax(const float* row, int V, MaxIdx* scratch) {
+  MaxIdx best{-INFINITY, 0x7fffffff};
+  for (int i = threadIdx.x; i < V; i += blockDim.x) best = better(best, MaxIdx{row[i], i});
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    MaxIdx other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) scratch[warp] = best;
+  __syncthreads();
+  MaxIdx r = (lane < (blockDim.x >> 5)) ? scratch[lane] : MaxIdx{-INFINITY, 0x7fffffff};
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    MaxIdx other{__shfl_xor_sync(0xffffffffu, r.v, o), __shfl_xor_sync(0xffffffffu, r.i, o)};
+    r = better(r, other);
+  }
+  if (r.i == 0x7fffffff) r.i = 0;  // a row of NaN or -inf: still a valid token id
+  return r;
+}
+
+__global__ void __launch_bounds__(kSampleThreads)
+sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature, float top_p,
+              unsigned long long seed, const int* __restrict__ seq_ids, int* __restrict__ counters,
+              int* __restrict__ out) {
+  __shared__ MaxIdx arg_scratch[32];
+  __shared__ float red[32];
+  __shared__ float chunk_sum[kSampleThreads];
+  __shared__ int chosen;
+  const int r = blockIdx.x;
+  const float* row = logits + (size_t)r * ld;
+  const MaxIdx top = block_argmax(row, V, arg_scratch);
+  if (temperature <= 0.f) {
+    if (threadIdx.x == 0) out[r] = top.i;
+    return;
+  }
+  const float inv_t = 1.f / temperature;
+  const float mx = top.v;
+
+  // contiguous chunk per thread, so that the inverse CDF runs in token-id order
+  const int chunk = (V + blockDim.x - 1) / blockDim.x;
+  const int begin = min(V, (int)threadIdx.x * chunk), end = min(V, begin + chunk);
+
+  float z = 0.f;
+  for (int i = begin; i < end; ++i) z += expf((row[i] - mx) * inv_t);
+  const float Z = block_sum(z, red);
+
+  float thresh = 0.f;  // keep w >= thresh
+  if (top_p < 1.f) {
+    const float target = fmaxf(top_p, 0.f) * Z;
+    unsigned lo = 0u, hi = 0x3f800000u;  // bits of 0.0 .. 1.0; S(bits(1.0)) = 0 always qualifies
+    while (lo < hi) {
+      const unsigned mid = lo + ((hi - lo) >> 1);
+      const float t = __uint_as_float(mid);
+      float s = 0.f;
+      for (int i = begin; i < end; ++i) {
+        const float w = expf((row[i] - mx) * inv_t);
+        if (w > t) s += w;
+      }
+      s = block_sum(s, red);
+      if (s <= target) hi = mid; else lo = mid + 1;
+    }
+    thresh = __uint_as_float(lo);
+  }
+
+  float mine = 0.f;
+  for (int i = begin; i < end; ++i) {
+    const float w = expf((row[i] - mx) * inv_t);
+    if (w >= thresh) mine += w;
+  }
+  chunk_sum[threadIdx.x] = mine;
+  if (threadIdx.x == 0) chosen = -1;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    // serial scan over 1024 partial sums: cheap, and the order is fixed
+    float total = 0.f;
+    for (int i = 0; i < kSampleThreads; ++i) total += chunk_sum[i];
+    const int counter = counters[r];
+    const float u = uniform24(seed, seq_ids[r], counter);
+    counters[r] = counter + 1;
+    const float target = u * total;
+    float run = 0.f;
+    int owner = -1;
+    for (int i = 0; i < kSampleThreads; ++i) {
+      if (chunk_sum[i] > 0.f) {
+        if (target < run + chunk_sum[i]) { owner = i; break; }
+        run += chunk_sum[i];
+      }
+    }
+    int pick = top.i;  // falls back to the most likely token if rounding ran past the end
+    if (owner >= 0) {
+      const int b = min(V, owner * chunk), e = min(V, b + chunk);
+      int last_kept = -1;
+      bool found = false;
+      for (int i = b; i < e; ++i) {
+        const float w = expf((row[i] - mx) * inv_t);
+        if (w >= thresh) {
+          last_kept = i;
+          run += w;
+          if (target < run) { pick = i; found = true; break; }
+        }
+      }
+      if (!found && last_kept >= 0) pick = last_kept;
+    }
+    chosen = pick;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) out[r] = chosen;
+}
+
+// tokens[i] = sampled[i] for the lanes of a decode step (feeds the next step on the device)
+__global__ void copy_int_kernel(const int* __restrict__ src, int* __restrict__ dst, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = src[i];
+}
+
+}  // namespace llmie
+
+using namespace llmie;
+
+// logits: [n_rows, ld] float32 with V <= ld valid columns. seq_ids / counters: [n_rows] (unused when
+// temperature <= 0, may then be null). out: [n_rows] int32.
+extern "C" int llmie_sample(const float* logits, int n_rows, int V, int ld, float temperature, float top_p,
+                            unsigned long long seed, const int* seq_ids, int* counters, int* out,
+                            cudaStream_t stream) {
+  if (n_rows < 0 || V <= 0 || ld < V) return LLMIE_ERR_BAD_ARG;
+  if (temperature > 0.f && (!seq_ids || !counters)) return LLMIE_ERR_BAD_ARG;
+  if (n_rows == 0) return LLMIE_OK;
+  sample_kernel<<<n_rows, kSampleThreads, 0, stream>>>(logits, ld, V, temperature, top_p, seed, seq_ids, counters,
+                                                       out);
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+extern "C" int llmie_copy_int(const int* src, int* dst, int n, cudaStream_t stream) {
+  if (n < 0) return LLMIE_ERR_BAD_ARG;
+  if (n == 0) return LLMIE_OK;
+  copy_int_kernel<<<(n + 255) / 256, 256, 0, stream>>>(src, dst, n);
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}

@@ -1,0 +1,49 @@
+"""What one step looks like to the parts: the ragged batch as device index arrays plus the
+host-side bounds needed to size launches, and the attention service that picks a kernel.
+
+    tokens     [T]    token ids of all sequences, packed one sequence after another
+    tok_pos    [T]    absolute position of each token in its sequence
+    tok_seq    [T]    which sequence of this step (0..n-1) each token belongs to
+    cu_q       [n+1]  where each sequence's tokens start in the packed arrays
+    seq_slot   [n]    cache slot of each sequence
+    seq_start  [n]    tokens the sequence held before this step
+    seq_kvlen  [n]    tokens it holds after this step
+    logit_rows [R]    packed rows whose logits are wanted
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ..kernels import ops
+
+
+@dataclass
+class StepContext:
+    n_tokens: int
+    n_seqs: int
+    decode: bool                 # every sequence brings exactly one token
+    max_q_len: int               # host-side upper bounds, for launch sizing only
+    max_kv_len: int
+    tokens: torch.Tensor
+    tok_pos: torch.Tensor
+    tok_seq: torch.Tensor
+    cu_q: torch.Tensor
+    seq_slot: torch.Tensor
+    seq_start: torch.Tensor
+    seq_kvlen: torch.Tensor
+    logit_rows: torch.Tensor
+    dtype: torch.dtype
+    device: torch.device
+    kernels: Optional[object] = None     # the engine's kernel choices (KernelPlan)
+
+    def attention(self, q, kv, out, n_q: int, n_kv: int, head_dim: int, scale: float, window: int) -> None:
+        """softmax(q k^T * scale) v over the cache unit `kv`, each token seeing the keys of its own
+        sequence up to its own position (and no further back than `window`, if set)."""
+        plan = self.kernels
+        if plan is not None and plan.attention(self, q, kv, out, n_q, n_kv, head_dim, scale, window):
+            return
+        ops.attention_paged(q, kv.k, kv.v, out, self.tok_pos, self.tok_seq, self.seq_slot, kv.block_table,
+                            kv.page_size, n_q, n_kv, head_dim, scale, window)

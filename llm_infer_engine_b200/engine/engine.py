@@ -1,0 +1,248 @@
+"""The engine: a model, its cache, and the one step function that everything above uses.
+
+`step()` runs exactly the tokens it is given, as one batch, from the cache that earlier steps
+left, and returns float32 logits at the wanted places. Sequences of a batch may have unequal
+lengths; prompts go in one step, then one token each. Generation (`generate.py`) and trace
+replay (`bin/trace_run`) both drive this function; there is no second forward pass.
+
+The reference's step is `Llama3.forward(tokens[B, S], start_pos, kv_cache)` with one shared
+start position and equal lengths (src/model.py:145-185), and its decode graph is B = 1 with
+host rewrites per token (src/cuda_graph.py:57-70). Here a one-token step for a batch bucket is
+captured once with all per-step inputs (tokens, slots, lengths) in device memory.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Union
+
+import numpy as np
+import torch
+
+from ..cache.cache import Cache
+from ..kernels import ops
+from ..weights.loader import build_model
+from .context import StepContext
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+class EngineError(RuntimeError):
+    pass
+
+
+def resolve_dtype(dtype: Union[str, torch.dtype]) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise EngineError(f"dtype {dtype} is not supported (bfloat16, float32)")
+        return dtype
+    if dtype not in _DTYPES:
+        raise EngineError(f"dtype {dtype!r} is not supported (bfloat16, float32)")
+    return _DTYPES[dtype]
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class Engine:
+    def __init__(self, model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16", device: Union[str, int] = 0,
+                 max_batch: int = 8, max_seq_len: Optional[int] = None, max_tokens: Optional[int] = None,
+                 cuda_graph: bool = True):
+        """max_batch: sequences held at once (slots). max_seq_len: longest sequence (default and
+        upper bound: the model's max_position_embeddings). max_tokens: positions all live sequences
+        may hold together, in whole pages of 64 (default: max_batch * max_seq_len)."""
+        if not torch.cuda.is_available():
+            raise EngineError("no CUDA device: this library runs on a GPU only (there is no CPU path)")
+        self.device = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
+        if self.device.type != "cuda":
+            raise EngineError(f"device {device!r} is not a CUDA device")
+        torch.cuda.set_device(self.device)
+        self.dtype = resolve_dtype(dtype)
+        self.model, self.config = build_model(model_dir, self.dtype, self.device, max_seq_len)
+        self.max_seq_len = self.model.runtime.max_positions
+        self.max_batch = int(max_batch)
+        page = 64
+        if max_tokens is None:
+            max_tokens = self.max_batch * _round_up(self.max_seq_len, page)
+        self.cache = Cache(self.model.unit_requests, self.max_batch, int(max_tokens), self.max_seq_len, self.dtype,
+                           self.device)
+        self.vocab_size = self.model.vocab_size
+        self.use_cuda_graph = bool(cuda_graph)
+        from .plan import KernelPlan
+        self.kernels = KernelPlan(self)
+        self._graphs: Dict[int, "DecodeGraph"] = {}
+        self.launches = 0
+
+    # ---------------------------------------------------------------- sequences
+    def open(self) -> int:
+        """Takes a cache slot for a new sequence."""
+        return self.cache.take_slot()
+
+    def close(self, slot: int) -> None:
+        """Gives the slot and everything it holds back."""
+        self.cache.give_back_slot(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.lengths[slot]
+
+    # ---------------------------------------------------------------- the step
+    def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
+             want: Union[str, Sequence[Sequence[int]]] = "last") -> torch.Tensor:
+        """Appends tokens[i] to the sequence in slots[i] and returns float32 logits [R, vocab] at
+        the wanted places: `want[i]` lists indices into tokens[i] ("last" = the last token of each,
+        "all" = every token), in the order of the sequences and of `want`."""
+        n = len(slots)
+        if n == 0 or len(tokens) != n:
+            raise EngineError("step: slots and tokens must be non-empty lists of the same length")
+        if len(set(slots)) != n:
+            raise EngineError("step: a slot appears twice in one step")
+        lens = [len(t) for t in tokens]
+        if min(lens) < 1:
+            raise EngineError("step: every sequence must bring at least one token")
+        if want == "last":
+            want = [[l - 1] for l in lens]
+        elif want == "all":
+            want = [list(range(l)) for l in lens]
+        if len(want) != n:
+            raise EngineError("step: want must have one list per sequence")
+        cache = self.cache
+        starts = []
+        for s, l in zip(slots, lens):
+            if not cache.slots.is_held(s):
+                raise EngineError(f"step: slot {s} is not open")
+            start = cache.lengths[s]
+            if start + l > self.max_seq_len:
+                raise EngineError(f"step: slot {s} would hold {start + l} tokens, more than max_seq_len "
+                                  f"{self.max_seq_len}")
+            starts.append(start)
+        for s, st, l in zip(slots, starts, lens):
+            cache.reserve(s, st + l)
+
+        T = sum(lens)
+        flat = np.fromiter((t for seq in tokens for t in seq), dtype=np.int64, count=T)
+        if flat.min() < 0 or flat.max() >= self.vocab_size:
+            raise EngineError(f"step: token id outside the vocabulary (0..{self.vocab_size - 1})")
+        cu = np.zeros(n + 1, dtype=np.int64)
+        np.cumsum(lens, out=cu[1:])
+        rows = []
+        for i, w in enumerate(want):
+            for j in w:
+                if not 0 <= j < lens[i]:
+                    raise EngineError(f"step: want index {j} is outside sequence {i}'s {lens[i]} tokens")
+                rows.append(int(cu[i]) + j)
+        R = len(rows)
+        tok_seq = np.repeat(np.arange(n), lens)
+        tok_pos = np.arange(T) - cu[tok_seq] + np.asarray(starts)[tok_seq]
+        kvlen = np.asarray(starts) + np.asarray(lens)
+        # one packed upload: [tokens | tok_pos | tok_seq | cu_q | seq_slot | seq_start | seq_kvlen | rows]
+        sizes = [T, T, T, n + 1, n, n, n, R]
+        offs = np.concatenate([[0], np.cumsum([_round_up(s, 4) for s in sizes])])
+        packed = np.zeros(int(offs[-1]), dtype=np.int32)
+        for k, arr in enumerate((flat, tok_pos, tok_seq, cu, np.asarray(slots), np.asarray(starts), kvlen,
+                                 np.asarray(rows, dtype=np.int64))):
+            packed[offs[k]:offs[k] + sizes[k]] = arr
+        dev = torch.from_numpy(packed).to(self.device)
+        view = [dev[int(offs[k]):int(offs[k]) + sizes[k]] for k in range(8)]
+        ctx = StepContext(
+            n_tokens=T, n_seqs=n, decode=max(lens) == 1, max_q_len=max(lens), max_kv_len=int(kvlen.max()),
+            tokens=view[0], tok_pos=view[1], tok_seq=view[2], cu_q=view[3], seq_slot=view[4], seq_start=view[5],
+            seq_kvlen=view[6], logit_rows=view[7], dtype=self.dtype, device=self.device, kernels=self.kernels)
+        logits = self.model.forward(ctx, cache)
+        ops.advance_lengths(ctx.seq_slot, ctx.seq_kvlen, cache.seq_lens, n, cache.scratch_slot)
+        for s, new_len in zip(slots, kvlen):
+            cache.note_appended(s, int(new_len), device_updated=True)
+        return logits
+
+    # ---------------------------------------------------------------- captured one-token step
+    def decode_graph(self, n_lanes: int) -> "DecodeGraph":
+        g = self._graphs.get(n_lanes)
+        if g is None:
+            g = DecodeGraph(self, n_lanes)
+            self._graphs[n_lanes] = g
+        return g
+
+    def weight_bytes_per_step(self) -> int:
+        return self.model.weight_bytes_per_step()
+
+    def kv_bytes_per_token(self) -> int:
+        """Cache bytes one position of one sequence occupies, over all units."""
+        esize = 2 if self.dtype == torch.bfloat16 else 4
+        total = 0
+        for reqs in self.model.unit_requests:
+            for r in reqs:
+                if hasattr(r, "n_kv_heads"):
+                    total += 2 * r.n_kv_heads * r.head_dim * esize
+        return total
+
+
+BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+
+def bucket_for(n: int) -> int:
+    """The smallest lane count a captured step is kept for that holds n sequences."""
+    for b in BUCKETS:
+        if b >= n:
+            return b
+    return n
+
+
+class DecodeGraph:
+    """One captured one-token step for `n_lanes` sequences. Inputs live in device buffers:
+    `tokens[n_lanes]`, `slots[n_lanes]` (padding lanes name the scratch slot), and the lengths in
+    the cache's `seq_lens`; the step derives positions from them, so replaying needs no host
+    writes beyond the two buffers when the set of sequences changes. `logits` is [n_lanes, vocab]."""
+
+    def __init__(self, engine: Engine, n_lanes: int):
+        self.engine = engine
+        self.n = n_lanes
+        dev = engine.device
+        cache = engine.cache
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.tokens = torch.zeros(n_lanes, **i32)
+        self.slots = torch.full((n_lanes,), cache.scratch_slot, **i32)
+        self.tok_pos = torch.zeros(n_lanes, **i32)
+        self.tok_seq = torch.zeros(n_lanes, **i32)
+        self.cu_q = torch.zeros(n_lanes + 1, **i32)
+        self.seq_start = torch.zeros(n_lanes, **i32)
+        self.seq_kvlen = torch.zeros(n_lanes, **i32)
+        self.rows = torch.arange(n_lanes, **i32)
+        self.logits: Optional[torch.Tensor] = None
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self._lane_slots: List[int] = [cache.scratch_slot] * n_lanes
+        self._capture()
+
+    def _run(self) -> torch.Tensor:
+        e = self.engine
+        ops.prepare_decode(self.slots, e.cache.seq_lens, self.tok_pos, self.tok_seq, self.cu_q, self.seq_start,
+                           self.seq_kvlen, self.n)
+        ctx = StepContext(
+            n_tokens=self.n, n_seqs=self.n, decode=True, max_q_len=1, max_kv_len=e.max_seq_len, tokens=self.tokens,
+            tok_pos=self.tok_pos, tok_seq=self.tok_seq, cu_q=self.cu_q, seq_slot=self.slots, seq_start=self.seq_start,
+            seq_kvlen=self.seq_kvlen, logit_rows=self.rows, dtype=e.dtype, device=e.device, kernels=e.kernels)
+        logits = e.model.forward(ctx, e.cache)
+        ops.advance_lengths(self.slots, self.seq_kvlen, e.cache.seq_lens, self.n, e.cache.scratch_slot)
+        return logits
+
+    def _capture(self) -> None:
+        # a first eager run on the scratch slot loads every kernel library and sizes the pools
+        side = torch.cuda.Stream(device=self.engine.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._run()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(self.engine.device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = self._run()
+
+    def set_lanes(self, slots: Sequence[int]) -> None:
+        """Which sequences the lanes continue; the rest are padding."""
+        if len(slots) > self.n:
+            raise EngineError(f"{len(slots)} sequences do not fit a graph of {self.n} lanes")
+        lane_slots = list(slots) + [self.engine.cache.scratch_slot] * (self.n - len(slots))
+        if lane_slots != self._lane_slots:
+            self.slots.copy_(torch.tensor(lane_slots, dtype=torch.int32))
+            self._lane_slots = lane_slots
+
+    def replay(self) -> torch.Tensor:
+        self.graph.replay()
+        return self.logits

@@ -1,0 +1,254 @@
+"""Python faces of the CUDA kernels: argument checks, then one ctypes call per launch.
+
+Every function takes CUDA tensors, checks dtype / shape / contiguity on the host (the checks
+stand in for a memory checker: no kernel is ever launched on sizes it was not written for),
+launches on torch's current stream and returns without synchronising. There is no CPU or
+library fallback: a tensor that is not on a GPU, or a kernel library that cannot be built,
+raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+
+_c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+_ERRORS = {-1: "bad argument", -2: "size not supported by this kernel", -3: "pointer not aligned",
+           -4: "dtype not supported"}
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+_fn_cache = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _fn(family: str, name: str, argtypes):
+    key = (family, name)
+    f = _fn_cache.get(key)
+    if f is None:
+        lib = build.load(family)
+        f = getattr(lib, name)
+        f.argtypes = argtypes
+        f.restype = _c_int
+        _fn_cache[key] = f
+    return f
+
+
+def _check(status: int, name: str) -> None:
+    if status == 0:
+        return
+    if status < 0:
+        raise KernelError(f"{name}: {_ERRORS.get(status, 'error ' + str(status))}")
+    raise KernelError(f"{name}: CUDA error {status} at launch")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dt(t: torch.Tensor, what: str) -> int:
+    code = _DT.get(t.dtype)
+    if code is None:
+        raise KernelError(f"{what}: dtype {t.dtype} is not supported (float32 or bfloat16)")
+    return code
+
+
+def _need(t: torch.Tensor, what: str, dtype=None, shape=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{what}: must be a CUDA tensor (this library has no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{what}: must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{what}: dtype {t.dtype}, expected {dtype}")
+    if shape is not None:
+        if t.dim() != len(shape) or any(s is not None and s != a for s, a in zip(shape, t.shape)):
+            raise KernelError(f"{what}: shape {tuple(t.shape)}, expected {tuple(shape)}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+# ------------------------------------------------------------------------------------------
+def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = table[tokens[t]] as float32. tokens int32 [T]; table [V, d]; out float32 [T, d]."""
+    T = tokens.shape[0]
+    V, d = table.shape
+    _need(tokens, "tokens", torch.int32, (T,))
+    _need(table, "table")
+    _need(out, "out", torch.float32, (T, d))
+    f = _fn("elementwise", "llmie_embedding",
+            [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(tokens.data_ptr(), table.data_ptr(), _dt(table, "table"), out.data_ptr(), T, d, V, _stream()),
+           "embedding")
+    return out
+
+
+def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """h += delta (float32, in place, when rows is None); out = rmsnorm(h) * weight.
+
+    h float32 [T, d]; delta [T, d] of out's dtype or None; weight float32 [d]; out [n_out, d].
+    With `rows` (int32 [n_out]) only those rows of h (+ delta) are normalised and h is left as it is."""
+    T, d = h.shape
+    n_out = T if rows is None else rows.shape[0]
+    _need(h, "h", torch.float32)
+    _need(weight, "weight", torch.float32, (d,))
+    _need(out, "out", None, (n_out, d))
+    if delta is not None:
+        _need(delta, "delta", out.dtype, (T, d))
+    if rows is not None:
+        _need(rows, "rows", torch.int32, (n_out,))
+    f = _fn("elementwise", "llmie_add_rmsnorm",
+            [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_int, _c_void_p])
+    _check(f(h.data_ptr(), _ptr(delta), weight.data_ptr(), out.data_ptr(), _ptr(rows), n_out, d, float(eps),
+             _dt(out, "out"), _stream()), "add_rmsnorm")
+    return out
+
+
+def residual_add(h: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    """h += delta; h float32, delta float32 or bfloat16 of the same shape."""
+    _need(h, "h", torch.float32)
+    _need(delta, "delta", None, tuple(h.shape))
+    f = _fn("elementwise", "llmie_residual_add", [_c_void_p, _c_void_p, ctypes.c_longlong, _c_int, _c_void_p])
+    _check(f(h.data_ptr(), delta.data_ptr(), h.numel(), _dt(delta, "delta"), _stream()), "residual_add")
+    return h
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, j] = silu(gate_up[t, j]) * gate_up[t, ff + j]; gate_up [T, 2 ff], out [T, ff]."""
+    T, ff = out.shape
+    _need(out, "out")
+    _need(gate_up, "gate_up", out.dtype, (T, 2 * ff))
+    f = _fn("elementwise", "llmie_swiglu", [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(gate_up.data_ptr(), out.data_ptr(), T, ff, _dt(out, "out"), _stream()), "swiglu")
+    return out
+
+
+def rope_store(qkv, q_out, k_cache, v_cache, table, tok_pos, tok_seq, seq_slot, block_table, page_size: int,
+               n_q: int, n_kv: int, head_dim: int, rot_dim: int, write_kv: bool = True):
+    """Rotates q and k by position and writes k, v into the paged cache.
+
+    qkv [T, (n_q + 2 n_kv) hd]; q_out [T, n_q hd]; caches [n_pages, n_kv, page_size, hd] (same dtype);
+    table float32 [max_pos, rot_dim / 2, 2] of (cos, sin) or None for no rotation;
+    tok_pos, tok_seq int32 [T]; seq_slot int32 [n]; block_table int32 [n_slots, max_pages]."""
+    T = qkv.shape[0]
+    _need(qkv, "qkv", None, (T, (n_q + 2 * n_kv) * head_dim))
+    _need(q_out, "q_out", qkv.dtype, (T, n_q * head_dim))
+    _need(tok_pos, "tok_pos", torch.int32)
+    _need(tok_seq, "tok_seq", torch.int32)
+    _need(seq_slot, "seq_slot", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    if tok_pos.shape[0] < T or tok_seq.shape[0] < T:
+        raise KernelError("rope_store: tok_pos / tok_seq shorter than the token count")
+    table_len = 0
+    if table is not None:
+        _need(table, "table", torch.float32, (None, rot_dim // 2, 2))
+        table_len = table.shape[0]
+    if write_kv:
+        _need(k_cache, "k_cache", qkv.dtype, (None, n_kv, page_size, head_dim))
+        _need(v_cache, "v_cache", qkv.dtype, tuple(k_cache.shape))
+    f = _fn("elementwise", "llmie_rope_store",
+            [_c_void_p] * 9 + [_c_int] * 10 + [_c_void_p])
+    _check(f(qkv.data_ptr(), q_out.data_ptr(), _ptr(k_cache) if write_kv else None,
+             _ptr(v_cache) if write_kv else None, _ptr(table), tok_pos.data_ptr(), tok_seq.data_ptr(),
+             seq_slot.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, T, n_q,
+             n_kv, head_dim, rot_dim, table_len, 1 if write_kv else 0, _dt(qkv, "qkv"), _stream()), "rope_store")
+    return q_out
+
+
+def attention_paged(q, k_cache, v_cache, out, tok_pos, tok_seq, seq_slot, block_table, page_size: int,
+                    n_q: int, n_kv: int, head_dim: int, scale: float, window: int = 0):
+    """Plain attention over the paged cache, one warp per (token, query head).
+    q, out [T, n_q hd]; caches [n_pages, n_kv, page_size, hd]; window 0 = all earlier keys."""
+    T = q.shape[0]
+    _need(q, "q", None, (T, n_q * head_dim))
+    _need(out, "out", q.dtype, (T, n_q * head_dim))
+    _need(k_cache, "k_cache", q.dtype, (None, n_kv, page_size, head_dim))
+    _need(v_cache, "v_cache", q.dtype, tuple(k_cache.shape))
+    for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("seq_slot", seq_slot), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    if head_dim % 16 or head_dim > 256:
+        raise KernelError(f"attention_paged: head_dim {head_dim} must be a multiple of 16 and at most 256")
+    f = _fn("attention_simt", "llmie_attention_paged",
+            [_c_void_p] * 8 + [_c_int] * 6 + [_c_float, _c_int, _c_int, _c_void_p])
+    _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), tok_pos.data_ptr(),
+             tok_seq.data_ptr(), seq_slot.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, T,
+             n_q, n_kv, head_dim, float(scale), int(window), _dt(q, "q"), _stream()), "attention_paged")
+    return out
+
+
+def gemm_f32_nt(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ w[N, K]^T in true float32 (FMA on CUDA cores, fixed summation order)."""
+    M, K = a.shape
+    N = w.shape[0]
+    _need(a, "a", torch.float32)
+    _need(w, "w", torch.float32, (N, K))
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    _need(out, "out", torch.float32, (M, N))
+    f = _fn("gemm_simt", "llmie_gemm_f32_nt", [_c_void_p] * 3 + [_c_int] * 6 + [_c_void_p])
+    _check(f(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, K, K, N, _stream()), "gemm_f32_nt")
+    return out
+
+
+def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float = 0.0, top_p: float = 1.0, seed: int = 0,
+           seq_ids: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row of float32 logits [R, V]: argmax when temperature <= 0 (lowest index wins a
+    tie), else a draw from softmax(logits / T) cut by top_p, with the uniform number of
+    (seed, seq_ids[r], counters[r]); counters[r] is then incremented. out int32 [R]."""
+    R, V = logits.shape
+    _need(logits, "logits", torch.float32)
+    _need(out, "out", torch.int32)
+    if out.shape[0] < R:
+        raise KernelError("sample: out is shorter than the number of rows")
+    if temperature > 0:
+        if seq_ids is None or counters is None:
+            raise KernelError("sample: seq_ids and counters are required when temperature > 0")
+        _need(seq_ids, "seq_ids", torch.int32)
+        _need(counters, "counters", torch.int32)
+        if seq_ids.shape[0] < R or counters.shape[0] < R:
+            raise KernelError("sample: seq_ids / counters shorter than the number of rows")
+    f = _fn("sampling", "llmie_sample",
+            [_c_void_p, _c_int, _c_int, _c_int, _c_float, _c_float, ctypes.c_ulonglong, _c_void_p, _c_void_p,
+             _c_void_p, _c_void_p])
+    _check(f(logits.data_ptr(), R, V, logits.stride(0), float(temperature), float(top_p),
+             int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(seq_ids), _ptr(counters), out.data_ptr(), _stream()), "sample")
+    return out
+
+
+def copy_int(src: torch.Tensor, dst: torch.Tensor, n: int) -> None:
+    _need(src, "src", torch.int32)
+    _need(dst, "dst", torch.int32)
+    if src.numel() < n or dst.numel() < n:
+        raise KernelError("copy_int: n exceeds a buffer")
+    f = _fn("sampling", "llmie_copy_int", [_c_void_p, _c_void_p, _c_int, _c_void_p])
+    _check(f(src.data_ptr(), dst.data_ptr(), n, _stream()), "copy_int")
+
+
+def prepare_decode(slots, seq_lens, tok_pos, tok_seq, cu_q, seq_start, seq_kvlen, n: int) -> None:
+    """Per-lane metadata of a one-token step from the device-resident lengths."""
+    for name, t in (("slots", slots), ("seq_lens", seq_lens), ("tok_pos", tok_pos), ("tok_seq", tok_seq),
+                    ("cu_q", cu_q), ("seq_start", seq_start), ("seq_kvlen", seq_kvlen)):
+        _need(t, name, torch.int32)
+    if min(slots.numel(), tok_pos.numel(), tok_seq.numel(), seq_start.numel(), seq_kvlen.numel()) < n \
+            or cu_q.numel() < n + 1:
+        raise KernelError("prepare_decode: a buffer is shorter than n")
+    f = _fn("elementwise", "llmie_prepare_decode", [_c_void_p] * 7 + [_c_int, _c_void_p])
+    _check(f(slots.data_ptr(), seq_lens.data_ptr(), tok_pos.data_ptr(), tok_seq.data_ptr(), cu_q.data_ptr(),
+             seq_start.data_ptr(), seq_kvlen.data_ptr(), n, _stream()), "prepare_decode")
+
+
+def advance_lengths(slots, seq_kvlen, seq_lens, n: int, scratch_slot: int) -> None:
+    """seq_lens[slots[i]] = seq_kvlen[i] for the n lanes of a step, except the scratch slot."""
+    for name, t in (("slots", slots), ("seq_kvlen", seq_kvlen), ("seq_lens", seq_lens)):
+        _need(t, name, torch.int32)
+    f = _fn("elementwise", "llmie_advance_lengths", [_c_void_p] * 3 + [_c_int, _c_int, _c_void_p])
+    _check(f(slots.data_ptr(), seq_kvlen.data_ptr(), seq_lens.data_ptr(), n, scratch_slot, _stream()),
+           "advance_lengths")

@@ -1,0 +1,9 @@
+from .base import (Block, FeedForward, Mixer, Norm, ParamSpec, Part, PositionEncoding, Runtime, build_part, lookup,
+                   register_block, register_feed_forward, register_mixer, register_norm,
+                   register_position_encoding)
+from . import attention, block, mlp, norm, rope  # noqa: F401  (register the built-in parts)
+from .linear import Linear
+
+__all__ = ["Block", "FeedForward", "Mixer", "Norm", "ParamSpec", "Part", "PositionEncoding", "Runtime",
+           "build_part", "lookup", "register_block", "register_feed_forward", "register_mixer", "register_norm",
+           "register_position_encoding", "Linear"]

@@ -1,0 +1,69 @@
+"""Grouped-query attention over the paged cache.
+
+q = x Wq^T, k = x Wk^T, v = x Wv^T without bias; q and k position-encoded; scores
+q.k / sqrt(head_dim) over the keys a token may see, softmax in float32, times v; heads
+concatenated in head order, then Wo (src/model.py:39-90 of the reference). Query head h reads
+key/value head h // (n_heads / n_kv_heads) (src/flash_attn.py:92-94). The three projections are
+one GEMM over row-concatenated weights.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..cache.cache import KVRequest
+from ..kernels import ops
+from .base import Mixer, ParamSpec, build_part, register_mixer
+from .linear import Linear
+
+
+class GroupedQueryAttention(Mixer):
+    """params: hidden, n_heads, n_kv_heads, head_dim, position (PartSpec of a position encoding),
+    window (0 = every earlier key), scale (None = 1/sqrt(head_dim))."""
+
+    def __init__(self, params, runtime):
+        super().__init__(params, runtime)
+        self.hidden = int(params["hidden"])
+        self.n_heads = int(params["n_heads"])
+        self.n_kv_heads = int(params["n_kv_heads"])
+        self.head_dim = int(params["head_dim"])
+        self.window = int(params.get("window") or 0)
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError(f"n_heads ({self.n_heads}) must be a multiple of n_kv_heads ({self.n_kv_heads})")
+        if self.head_dim % 16 or self.head_dim > 256:
+            raise ValueError(f"head_dim {self.head_dim} is not supported by the attention kernels "
+                             "(multiples of 16 up to 256)")
+        scale = params.get("scale")
+        self.scale = float(scale) if scale is not None else self.head_dim ** -0.5
+        self.position = build_part("position_encoding", params["position"], runtime)
+        self.qkv: Linear = None
+        self.o: Linear = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        hq, hkv, hd, d = self.n_heads, self.n_kv_heads, self.head_dim, self.hidden
+        return {"q_proj.weight": ParamSpec((hq * hd, d)), "k_proj.weight": ParamSpec((hkv * hd, d)),
+                "v_proj.weight": ParamSpec((hkv * hd, d)), "o_proj.weight": ParamSpec((d, hq * hd))}
+
+    def load(self, tensors):
+        ws = [tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]]
+        dtype = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
+        self.qkv = Linear(torch.cat([w.to(dtype) for w in ws], dim=0))
+        self.o = Linear(tensors["o_proj.weight"])
+
+    def weight_bytes(self) -> int:
+        return self.qkv.nbytes() + self.o.nbytes()
+
+    def cache_requests(self):
+        return [KVRequest(self.n_kv_heads, self.head_dim, self.window)]
+
+    def forward(self, x, ctx, unit, owns_cache):
+        kv = unit.kv
+        qkv = self.qkv(x)
+        q = self.position.encode_and_store(qkv, ctx, kv, self.n_heads, self.n_kv_heads, self.head_dim, owns_cache)
+        out = torch.empty_like(q)
+        ctx.attention(q, kv, out, self.n_heads, self.n_kv_heads, self.head_dim, self.scale, self.window)
+        return self.o(out)
+
+
+register_mixer("gqa_attention", GroupedQueryAttention)

@@ -1,0 +1,40 @@
+"""Matrix products y = x W^T of the parts (no bias), chosen by the weight's precision.
+
+bfloat16 weights: the library GEMM (cuBLAS through torch.mm), as the reference does with
+nn.Linear (src/model.py:17-19,34-37,137), accumulating in float32. float32 weights: this
+library's own FMA kernel, true 32-bit with a fixed summation order; that is the whole of
+the 32-bit path, and also what a bfloat16 engine does with a tensor that its checkpoint
+stores in 32-bit.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..kernels import ops
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor):
+        if weight.dim() != 2:
+            raise ValueError(f"a linear weight must be [out, in], got {tuple(weight.shape)}")
+        if weight.dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"linear weight dtype {weight.dtype} is not supported")
+        self.weight = weight.contiguous()
+        self.out_features, self.in_features = weight.shape
+
+    def nbytes(self) -> int:
+        return self.weight.numel() * self.weight.element_size()
+
+    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """x [T, in] float32 or bfloat16 -> [T, out] in out_dtype (default: x's dtype)."""
+        out_dtype = out_dtype or x.dtype
+        w = self.weight
+        if w.dtype == torch.float32:
+            y = ops.gemm_f32_nt(x if x.dtype == torch.float32 else x.float(), w)
+            return y if out_dtype == torch.float32 else y.to(out_dtype)
+        xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+        if out_dtype == torch.bfloat16:
+            return torch.mm(xb, w.t())
+        return torch.mm(xb, w.t(), out_dtype=torch.float32)

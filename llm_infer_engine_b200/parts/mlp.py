@@ -1,0 +1,46 @@
+"""Dense gated feed-forward: down(silu(gate x) * (up x)), no bias (src/model.py:14-25 of the
+reference, w1 = gate, w3 = up, w2 = down). gate and up are one GEMM over row-concatenated
+weights; the activation and product are one kernel."""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..kernels import ops
+from .base import FeedForward, ParamSpec, register_feed_forward
+from .linear import Linear
+
+
+class SwiGLU(FeedForward):
+    """params: hidden, intermediate."""
+
+    def __init__(self, params, runtime):
+        super().__init__(params, runtime)
+        self.hidden = int(params["hidden"])
+        self.intermediate = int(params["intermediate"])
+        self.gate_up: Linear = None
+        self.down: Linear = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {"gate_proj.weight": ParamSpec((self.intermediate, self.hidden)),
+                "up_proj.weight": ParamSpec((self.intermediate, self.hidden)),
+                "down_proj.weight": ParamSpec((self.hidden, self.intermediate))}
+
+    def load(self, tensors):
+        g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        dtype = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
+        self.gate_up = Linear(torch.cat([g.to(dtype), u.to(dtype)], dim=0))
+        self.down = Linear(tensors["down_proj.weight"])
+
+    def weight_bytes(self) -> int:
+        return self.gate_up.nbytes() + self.down.nbytes()
+
+    def forward(self, x, ctx):
+        gu = self.gate_up(x)
+        act = torch.empty((x.shape[0], self.intermediate), dtype=gu.dtype, device=x.device)
+        ops.swiglu(gu, act)
+        return self.down(act)
+
+
+register_feed_forward("swiglu", SwiGLU)

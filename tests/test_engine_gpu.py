@@ -1,0 +1,80 @@
+"""The engine against the plain implementation, on the GPU, in 32-bit and in bfloat16:
+each request alone and whole; with the last 32 tokens one by one; in batches of unequal
+lengths whose shorter requests end earlier, one batch after another so that slots are used again."""
+import pytest
+import torch
+
+import helpers
+import plain_llama as plain
+
+pytestmark = pytest.mark.gpu
+
+# float32: the path is true 32-bit, so it must agree to rounding of a ~1-magnitude logit.
+# bfloat16: activations between kernels are rounded to 8 bits of mantissa; the bound is on the
+# logits' own scale and is the same for every way of cutting the work.
+TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+LENGTHS = {"a": [5, 11, 17, 40, 64, 65, 100], "b": [1, 9, 33, 70, 128, 129, 200]}
+
+_engines = {}
+
+
+def engine_for(tag, dtype):
+    from llm_infer_engine_b200 import Engine
+    key = (tag, dtype)
+    if key not in _engines:
+        _engines[key] = Engine(helpers.model_folder(tag), dtype=dtype, max_batch=8, max_tokens=64 * 24,
+                               cuda_graph=False)
+    return _engines[key]
+
+
+def requests_for(tag):
+    cfg = helpers.TINY[tag]["cfg"]
+    lens = [l for l in LENGTHS[tag] if l <= cfg["max_position_embeddings"]]
+    return {f"r{i}": helpers.random_tokens(cfg["vocab_size"], n, seed=100 + i) for i, n in enumerate(lens)}
+
+
+def oracle(tag, requests):
+    folder = helpers.model_folder(tag)
+    w, cfg = helpers.plain_weights(folder), helpers.read_config(folder)
+    return {rid: plain.logits(w, cfg, toks) for rid, toks in requests.items()}
+
+
+def check(got, want, tol, what):
+    for rid in want:
+        assert got[rid].shape == want[rid].shape, (what, rid, got[rid].shape, want[rid].shape)
+        diff = (got[rid] - want[rid]).abs()
+        worst = int(diff.max(dim=1).values.argmax())
+        assert float(diff.max()) <= tol, (f"{what}: request {rid} differs by {float(diff.max()):.3e} "
+                                          f"(tolerance {tol}), first at token {int((diff.max(dim=1).values > tol).nonzero()[0])}, "
+                                          f"worst at token {worst} of {len(diff)}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("tag", ["a", "b"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "batched"])
+def test_replay_matches_plain(tag, dtype, mode):
+    requests = requests_for(tag)
+    want = oracle(tag, requests)
+    if mode == "whole":
+        steps = helpers.plan_whole(requests)
+    elif mode == "tail":
+        steps = helpers.plan_tail(requests, 32)
+    else:
+        steps = helpers.plan_batched(requests, batch_size=3)
+    engine = engine_for(tag, dtype)
+    got = helpers.run_plan_engine(engine, steps)
+    check(got, want, TOL[dtype], f"{tag}/{dtype}/{mode}")
+    assert engine.cache.free_slots() == engine.cache.n_slots
+    assert engine.cache.free_pages() == engine.cache.n_pages
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(dtype):
+    """bin/trace_run itself, as a subprocess, on batches of unequal lengths."""
+    tag = "b"
+    requests = requests_for(tag)
+    want = oracle(tag, requests)
+    steps = helpers.plan_batched(requests, batch_size=4)
+    got = helpers.run_plan_trace_run(helpers.model_folder(tag), dtype, steps, helpers.max_tokens_for(steps),
+                                     helpers.TINY[tag]["cfg"]["vocab_size"])
+    check(got, want, TOL[dtype], f"trace_run/{dtype}")
