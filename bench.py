@@ -1,0 +1,297 @@
+"""Decode and prefill throughput of the engine on one B200, Llama 3.2 1B shape, random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+
+A "step" is one decode step of the whole batch (captured forward + sampling). The default run
+is BASELINE's 1B configuration in bfloat16 with a batch of 8, 512-token prompts and a 4096-token
+context limit. It prints ONE JSON line: `value` is decoded tokens per second over K timed steps
+(CUDA events, after W warm-up steps); `e2e` is the same through `generate()` with host tokens
+in and out every step; `prefill` is one 2,048-token prompt; `roofline` compares the decode
+step with the bytes it must read (every weight once + the live requests' cache) at the measured
+HBM bandwidth; `points` gives decode at batch 1 and 64. Weights (2.5 GB) are far larger than
+L2, so every step streams them from HBM; no extra L2 flush is needed (stated in `config`).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (Llama 3.2 1B)"
+
+# BASELINE.json configs[2]: the Llama 3.2 1B shape
+CONFIG_1B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 16, "hidden_size": 2048, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "head_dim": 64, "intermediate_size": 8192, "vocab_size": 128256, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 131072,
+    "hidden_act": "silu", "attention_bias": False, "mlp_bias": False, "bos_token_id": 128000,
+    "eos_token_id": 128001, "torch_dtype": "bfloat16",
+}
+CONTEXT = 4096
+PROMPT_LEN = 512
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                p = json.load(f)
+            return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "source": "measured"}
+        except (OSError, ValueError, KeyError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while timed work runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.samples = []
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        clocks, max_clocks, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for s in self.samples:
+            try:
+                clocks.append(int(float(s[0])))
+                max_clocks.append(int(float(s[1])))
+            except ValueError:
+                continue
+            for name, val in zip(names, s[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None,
+                "sm_max_mhz": max(max_clocks) if max_clocks else None, "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+def make_model_folder(n_layers: int, seed: int = 2) -> str:
+    from llm_infer_engine_b200 import write_random_model
+    cfg = dict(CONFIG_1B)
+    cfg["num_hidden_layers"] = n_layers
+    folder = tempfile.mkdtemp(prefix="llmie_bench_1b_")
+    t0 = time.time()
+    write_random_model(cfg, folder, seed=seed, std=0.02)
+    print(f"[bench] wrote a random {n_layers}-layer model folder in {time.time() - t0:.1f}s", file=sys.stderr)
+    return folder
+
+
+def random_prompts(batch: int, length: int, vocab: int, seed: int):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (length,), generator=g).tolist() for _ in range(batch)]
+
+
+def time_decode(engine, batch: int, steps: int, warmup: int, seed: int):
+    """Device time of `steps` decode steps of `batch` sequences after 512-token prompts.
+    Returns (seconds, mean context length over the timed steps, launches of this library's kernels)."""
+    import torch
+    from llm_infer_engine_b200.engine.engine import bucket_for
+    from llm_infer_engine_b200.kernels import ops
+    cache = engine.cache
+    prompts = random_prompts(batch, PROMPT_LEN, engine.vocab_size, seed)
+    slots = [engine.open() for _ in range(batch)]
+    try:
+        logits = engine.step(slots, prompts, "last")
+        sampled = torch.empty(batch, dtype=torch.int32, device=engine.device)
+        ops.sample(logits, sampled)
+        graph = engine.decode_graph(bucket_for(batch))
+        graph.set_lanes(slots)
+        graph.tokens[:batch].copy_(sampled)
+
+        def one_step():
+            for s in slots:
+                cache.reserve(s, cache.lengths[s] + 1)
+            out = graph.replay()
+            for s in slots:
+                cache.note_appended(s, cache.lengths[s] + 1, device_updated=True)
+            ops.sample(out[:batch], graph.tokens)      # greedy; feeds the next step on the device
+
+        for _ in range(warmup):
+            one_step()
+        torch.cuda.synchronize()
+        ctx0 = cache.lengths[slots[0]]
+        launches0 = ops.LAUNCHES
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            one_step()
+        end.record()
+        torch.cuda.synchronize()
+        seconds = start.elapsed_time(end) / 1e3
+        mean_ctx = ctx0 + (steps + 1) / 2.0
+        return seconds, mean_ctx, ops.LAUNCHES - launches0
+    finally:
+        for s in slots:
+            engine.close(s)
+
+
+def time_prefill(engine, n_tokens: int, warmup: int, reps: int, seed: int):
+    import torch
+    prompt = random_prompts(1, n_tokens, engine.vocab_size, seed)[0]
+    times = []
+    for i in range(warmup + reps):
+        slot = engine.open()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        engine.step([slot], [prompt], "last")
+        end.record()
+        torch.cuda.synchronize()
+        engine.close(slot)
+        if i >= warmup:
+            times.append(start.elapsed_time(end) / 1e3)
+    times.sort()
+    return times[len(times) // 2]
+
+
+def prefill_flops(cfg: dict, n_layers: int, T: int) -> float:
+    d, ff, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    hq, hkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_token = 2 * (d * (hq + 2 * hkv) * hd + hq * hd * d + 3 * d * ff)
+    gemm = n_layers * per_token * T + 2 * d * V            # the head runs on the last row only
+    attn = n_layers * 4 * hq * hd * (T * (T + 1) / 2)      # causal QK^T and PV
+    return gemm + attn
+
+
+def e2e_decode(engine, batch: int, steps: int, seed: int):
+    """Decoded tokens per second through generate(): host prompts in, host tokens out every step."""
+    from llm_infer_engine_b200 import GenerationStats, SamplingParams, generate
+    prompts = random_prompts(batch, PROMPT_LEN, engine.vocab_size, seed)
+    generate(engine, prompts[:batch], max_new_tokens=8, stop_ids=[])            # warm-up: graphs, pools
+    stats = GenerationStats()
+    generate(engine, prompts, max_new_tokens=steps + 1, sampling=SamplingParams(), stop_ids=[], stats=stats)
+    return stats.decode_tokens / stats.decode_seconds, stats
+
+
+def run_ours(args):
+    import torch
+    if not torch.cuda.is_available():
+        print(json.dumps({"metric": METRIC, "error": "no CUDA device"}))
+        return 1
+    from llm_infer_engine_b200 import Engine
+    pk = peaks()
+    full_layers = CONFIG_1B["num_hidden_layers"]
+    n_layers = args.layers or full_layers
+    folder = make_model_folder(n_layers)
+    max_batch = 64
+    per_seq = PROMPT_LEN + args.steps + args.warmup + 64
+    engine = Engine(folder, dtype="bfloat16", device=0, max_batch=max_batch, max_seq_len=CONTEXT,
+                    max_tokens=max(max_batch * ((per_seq + 63) // 64 * 64), PREFILL_TOKENS + 64), cuda_graph=True)
+    sampler = ClockSampler(0)
+    sampler.start()
+    results = {}
+    launches = 0
+    for batch in (args.batch, 1, 64):
+        if batch in results:
+            continue
+        sec, mean_ctx, n_launch = time_decode(engine, batch, args.steps, args.warmup, seed=10 + batch)
+        results[batch] = (sec, mean_ctx)
+        if batch == args.batch:
+            launches = n_launch
+    prefill_s = time_prefill(engine, PREFILL_TOKENS, warmup=max(3, min(args.warmup, 5)), reps=5, seed=99)
+    e2e_tps, stats = e2e_decode(engine, args.batch, args.steps, seed=10 + args.batch)
+    sampler.stop()
+
+    sec, mean_ctx = results[args.batch]
+    value = args.batch * args.steps / sec
+    step_bytes = engine.weight_bytes_per_step() + engine.kv_bytes_per_token() * mean_ctx * args.batch
+    achieved = step_bytes / (sec / args.steps) / 1e9
+    flops = prefill_flops(CONFIG_1B, n_layers, PREFILL_TOKENS)
+    out = {
+        "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(sec / args.steps * 1e3, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), "
+        "uniform-random token ids", "impl": "ours",
+        "config": {
+            "model": "Llama-3.2-1B shape", "global_batch": args.batch, "seq_len": CONTEXT, "parallelism": "single GPU",
+            "layers": n_layers, "layers_full": full_layers, "hidden_size": CONFIG_1B["hidden_size"],
+            "heads": CONFIG_1B["num_attention_heads"], "kv_heads": CONFIG_1B["num_key_value_heads"],
+            "head_dim": CONFIG_1B["head_dim"], "intermediate_size": CONFIG_1B["intermediate_size"],
+            "vocab_size": CONFIG_1B["vocab_size"], "prompt_len": PROMPT_LEN, "new_tokens": args.steps,
+            "tied_head": True, "cuda_graph": True, "sampling": "greedy",
+            "l2": "weights 2.5 GB per step >> 126 MB L2, no flush needed", "peaks": pk["source"],
+        },
+        "e2e": {"value": round(e2e_tps, 1), "unit": "tokens/s", "h2d_bytes_per_step": 4 * args.batch,
+                "d2h_bytes_per_step": 4 * args.batch},
+        "gpu_launches": int(launches),
+        "prefill": {"value": round(PREFILL_TOKENS / prefill_s, 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(prefill_s * 1e3, 3), "frac": round(flops / prefill_s / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": {f"decode_b{b}": round(b * args.steps / results[b][0], 1) for b in (1, 64)},
+        "clocks": sampler.summary(),
+    }
+    print(json.dumps(out))
+    return 0
+
+
+def run_reference(args):
+    # `python -m pip install --no-index --no-build-isolation --find-links /opt/wheelhouse --target baseline/_ref
+    # <reference>` fails: the reference has neither setup.py nor pyproject.toml, so nothing can be installed.
+    print(json.dumps({"impl": "reference", "unavailable": "pip cannot install the reference: the directory has "
+                      "neither setup.py nor pyproject.toml (not installable)"}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0 = all)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -231,8 +231,10 @@ class DecodeGraph:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize(self.engine.device)
         self.graph = torch.cuda.CUDAGraph()
+        before = ops.LAUNCHES
         with torch.cuda.graph(self.graph):
             self.logits = self._run()
+        self.launches_per_replay = ops.LAUNCHES - before      # this library's kernels inside one replay
 
     def set_lanes(self, slots: Sequence[int]) -> None:
         """Which sequences the lanes continue; the rest are padding."""
@@ -245,4 +247,5 @@ class DecodeGraph:
 
     def replay(self) -> torch.Tensor:
         self.graph.replay()
+        ops.LAUNCHES += self.launches_per_replay
         return self.logits

@@ -146,6 +146,9 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
             # --- one token each
             n = len(live)
             live_slots = [slots[i] for i in live]
+            # the tokens go back in from pinned host memory, as the reference writes each sampled id
+            # into its device input buffer (main.py:282): the host may have the last word on them
+            host_tokens[:n] = torch.tensor(still_tokens, dtype=torch.int32)
             if engine.use_cuda_graph:
                 lanes = bucket_for(n)
                 if graph is None or graph.n != lanes:
@@ -155,16 +158,15 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
                     cache.reserve(s, cache.lengths[s] + 1)
                 if changed:
                     graph.set_lanes(live_slots)
-                    graph.tokens[:n].copy_(torch.tensor(still_tokens, dtype=torch.int32))
                     seq_ids = torch.tensor([batch[i] for i in live], dtype=torch.int32, device=dev)
                     counters = torch.tensor([len(outputs[batch[i]]) for i in live], dtype=torch.int32, device=dev)
+                    sampled = torch.empty(n, dtype=torch.int32, device=dev)
+                graph.tokens[:n].copy_(host_tokens[:n], non_blocking=True)
                 logits = graph.replay()
                 for s in live_slots:
                     cache.note_appended(s, cache.lengths[s] + 1, device_updated=True)
-                # the sampled tokens land in the graph's token buffer: the next replay reads them there
-                ops.sample(logits[:n], graph.tokens, sampling.temperature, sampling.top_p, sampling.seed, seq_ids,
+                ops.sample(logits[:n], sampled, sampling.temperature, sampling.top_p, sampling.seed, seq_ids,
                            counters)
-                host_tokens[:n].copy_(graph.tokens[:n], non_blocking=True)
             else:
                 logits = engine.step(live_slots, [[t] for t in still_tokens], "last")
                 if changed:
@@ -172,7 +174,8 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
                     counters = torch.tensor([len(outputs[batch[i]]) for i in live], dtype=torch.int32, device=dev)
                     sampled = torch.empty(n, dtype=torch.int32, device=dev)
                 ops.sample(logits, sampled, sampling.temperature, sampling.top_p, sampling.seed, seq_ids, counters)
-                host_tokens[:n].copy_(sampled[:n], non_blocking=True)
+            # same stream: the upload above has read the pinned buffer before this download writes it
+            host_tokens[:n].copy_(sampled[:n], non_blocking=True)
             torch.cuda.current_stream().synchronize()
             new = host_tokens[:n].tolist()
             stats.decode_steps += 1

@@ -40,8 +40,13 @@ def _fn(family: str, name: str, argtypes):
     return f
 
 
+LAUNCHES = 0      # kernels of this library launched so far (captured launches count once, at capture)
+
+
 def _check(status: int, name: str) -> None:
     if status == 0:
+        global LAUNCHES
+        LAUNCHES += 1
         return
     if status < 0:
         raise KernelError(f"{name}: {_ERRORS.get(status, 'error ' + str(status))}")
