@@ -1,0 +1,304 @@
+// Split-KV attention for one-token steps over the paged cache.
+//
+// The reference splits the keys of a sequence into runs of 256, computes a partial
+// (max, sum, accumulator) per (sequence, query head, run) and merges the runs with a
+// log-sum-exp (src/flash_decode.py:8-137 and :140-212); every query head re-reads its KV head.
+// Here one block serves ALL query heads of a KV head for its run of keys, so the cache is
+// read once per KV head: block (run, kv head, sequence) computes G = Hq / Hkv partials, a
+// second kernel merges the runs. Lengths come from the device (`seq_kvlen`), so a captured
+// step needs no host rewrites; runs that lie beyond a sequence's length leave at once.
+//
+// A 16-byte load covers E elements of a key (8 bfloat16 or 4 float); LPK = HD / E lanes share
+// one key, 32 / LPK keys are in flight per warp. Scores, softmax and accumulators are float32.
+//
+// Scratch: part_m, part_l [n_seqs, Hq, n_runs] and part_acc [n_seqs, Hq, n_runs, HD], float32,
+// written by the first kernel and read by the second. Entries of runs that hold no visible key
+// are never written and never read.
+#include "common.cuh"
+#include <math.h>
+
+namespace llmie {
+
+constexpr int kDecWarps = 4;
+constexpr int kDecThreads = kDecWarps * 32;
+
+template <typename T> struct Vec16;
+template <> struct Vec16<__nv_bfloat16> { static constexpr int E = 8; };
+template <> struct Vec16<float> { static constexpr int E = 4; };
+
+template <typename T, int E>
+__device__ __forceinline__ void load_vec(const T* p, float (&out)[E]);
+template <>
+__device__ __forceinline__ void load_vec<__nv_bfloat16, 8>(const __nv_bfloat16* p, float (&out)[8]) { load8(p, out); }
+template <>
+__device__ __forceinline__ void load_vec<float, 4>(const float* p, float (&out)[4]) {
+  float4 a = *reinterpret_cast<const float4*>(p);
+  out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+}
+
+// The visible key range of a sequence that holds `len` tokens after this step: [lo, len).
+__device__ __forceinline__ int first_visible(int len, int window) {
+  return (window > 0 && len - window > 0) ? len - window : 0;
+}
+
+template <typename T, int HD, int GMAX>
+__global__ void __launch_bounds__(kDecThreads)
+decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                    float* __restrict__ part_m, float* __restrict__ part_l, float* __restrict__ part_acc,
+                    const int* __restrict__ seq_slot, const int* __restrict__ seq_kvlen,
+                    const int* __restrict__ block_table, int max_pages, int page_size, int n_q, int n_kv,
+                    float scale, int window, int run_len, int n_runs) {
+  constexpr int E = Vec16<T>::E;
+  constexpr int LPK = HD / E;          // lanes per key
+  constexpr int KPW = 32 / LPK;        // keys per warp per iteration
+  static_assert(LPK >= 1 && LPK <= 32 && 32 % LPK == 0, "head size not supported by this kernel");
+  extern __shared__ float smem[];      // scores [GMAX][run_len], then reduction [kDecWarps][GMAX][HD]
+
+  const int run = blockIdx.x, seq = blockIdx.z;
+  const int G = n_q / n_kv;
+  const int chunks = (G + GMAX - 1) / GMAX;
+  const int hk = blockIdx.y / chunks;
+  const int g0 = (blockIdx.y % chunks) * GMAX;       // first query head (within the group) of this block
+  const int ng = min(GMAX, G - g0);
+
+  const int len = seq_kvlen[seq];
+  const int lo = first_visible(len, window);
+  const int begin = max(run * run_len, lo);
+  const int end = min(len, (run + 1) * run_len);
+  if (begin >= end) return;
+  const int n_keys = end - begin;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane / LPK;          // which of the warp's KPW keys
+  const int e0 = (lane % LPK) * E;     // first element of this lane's slice
+  const int* pages = block_table + (size_t)seq_slot[seq] * max_pages;
+  float* scores = smem;                                  // [GMAX][run_len]
+  float* red = smem + GMAX * run_len;                    // [kDecWarps][GMAX][HD]
+
+  // this lane's slice of each query head, pre-scaled
+  float qv[GMAX][E];
+#pragma unroll
+  for (int g = 0; g < GMAX; ++g) {
+    if (g < ng) {
+      const T* qp = q + ((size_t)seq * n_q + (size_t)hk * G + g0 + g) * HD + e0;
+      float tmp[E];
+      load_vec<T, E>(qp, tmp);
+#pragma unroll
+      for (int e = 0; e < E; ++e) qv[g][e] = tmp[e] * scale;
+    } else {
+#pragma unroll
+      for (int e = 0; e < E; ++e) qv[g][e] = 0.f;
+    }
+  }
+
+  // ---- phase 1: scores
+  // the loop bound is the same for every lane of a warp (the shuffles below need all of them)
+  for (int jb = warp * KPW; jb < n_keys; jb += kDecWarps * KPW) {
+    const int j = jb + sub;
+    const bool valid = j < n_keys;
+    const int pos = begin + (valid ? j : 0);
+    const int page = pages[pos / page_size];
+    const T* kp = k_cache + (((size_t)page * n_kv + hk) * page_size + (pos % page_size)) * HD + e0;
+    float kv[E];
+    load_vec<T, E>(kp, kv);
+#pragma unroll
+    for (int g = 0; g < GMAX; ++g) {
+      float dot = 0.f;
+#pragma unroll
+      for (int e = 0; e < E; ++e) dot = fmaf(qv[g][e], kv[e], dot);
+#pragma unroll
+      for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      if (valid && (lane % LPK) == 0 && g < ng) scores[g * run_len + j] = dot;
+    }
+  }
+  __syncthreads();
+
+  // ---- phase 2: softmax statistics per head; scores become probabilities
+  for (int g = warp; g < ng; g += kDecWarps) {
+    float* s = scores + g * run_len;
+    float m = -INFINITY;
+    for (int j = lane; j < n_keys; j += 32) m = fmaxf(m, s[j]);
+    m = warp_max(m);
+    float l = 0.f;
+    for (int j = lane; j < n_keys; j += 32) {
+      const float p = expf(s[j] - m);
+      s[j] = p;
+      l += p;
+    }
+    l = warp_sum(l);
+    if (lane == 0) {
+      const size_t idx = ((size_t)seq * n_q + (size_t)hk * G + g0 + g) * n_runs + run;
+      part_m[idx] = m;
+      part_l[idx] = l;
+    }
+  }
+  __syncthreads();
+
+  // ---- phase 3: accumulate p * v
+  float acc[GMAX][E];
+#pragma unroll
+  for (int g = 0; g < GMAX; ++g)
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[g][e] = 0.f;
+  for (int j = warp * KPW + sub; j < n_keys; j += kDecWarps * KPW) {
+    const int pos = begin + j;
+    const int page = pages[pos / page_size];
+    const T* vp = v_cache + (((size_t)page * n_kv + hk) * page_size + (pos % page_size)) * HD + e0;
+    float vv[E];
+    load_vec<T, E>(vp, vv);
+#pragma unroll
+    for (int g = 0; g < GMAX; ++g) {
+      const float p = (g < ng) ? scores[g * run_len + j] : 0.f;
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[g][e] = fmaf(p, vv[e], acc[g][e]);
+    }
+  }
+  // lanes with the same element slice (same lane % LPK) hold different keys: add them up
+#pragma unroll
+  for (int g = 0; g < GMAX; ++g)
+#pragma unroll
+    for (int e = 0; e < E; ++e)
+#pragma unroll
+      for (int o = 16; o >= LPK; o >>= 1) acc[g][e] += __shfl_xor_sync(0xffffffffu, acc[g][e], o);
+  if (lane < LPK) {
+#pragma unroll
+    for (int g = 0; g < GMAX; ++g)
+#pragma unroll
+      for (int e = 0; e < E; ++e) red[(warp * GMAX + g) * HD + e0 + e] = acc[g][e];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < ng * HD; i += kDecThreads) {
+    const int g = i / HD, d = i % HD;
+    float sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) sum += red[(w * GMAX + g) * HD + d];
+    part_acc[(((size_t)seq * n_q + (size_t)hk * G + g0 + g) * n_runs + run) * HD + d] = sum;
+  }
+}
+
+// Merge of the runs (src/flash_decode.py:182-205): M = max m_r, w_r = exp(m_r - M),
+// out = sum w_r acc_r / sum w_r l_r, over the runs that hold a visible key, in run order.
+template <typename T>
+__global__ void decode_merge_kernel(const float* __restrict__ part_m, const float* __restrict__ part_l,
+                                    const float* __restrict__ part_acc, T* __restrict__ out,
+                                    const int* __restrict__ seq_kvlen, int n_q, int hd, int window, int run_len,
+                                    int n_runs) {
+  const int seq = blockIdx.y, h = blockIdx.x;
+  const int len = seq_kvlen[seq];
+  const int lo = first_visible(len, window);
+  const int r0 = lo / run_len, r1 = (len - 1) / run_len;      // len >= 1 always
+  const size_t base = ((size_t)seq * n_q + h) * n_runs;
+  float M = -INFINITY;
+  for (int r = r0; r <= r1; ++r) M = fmaxf(M, part_m[base + r]);
+  float denom = 0.f;
+  for (int r = r0; r <= r1; ++r) denom += expf(part_m[base + r] - M) * part_l[base + r];
+  const float inv = 1.f / denom;
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float num = 0.f;
+    for (int r = r0; r <= r1; ++r) num += expf(part_m[base + r] - M) * part_acc[(base + r) * hd + d];
+    out[((size_t)seq * n_q + h) * hd + d] = from_f32<T>(num * inv);
+  }
+}
+
+template <typename T, int HD, int GMAX>
+static int launch_split(const void* q, const void* k_cache, const void* v_cache, float* part_m, float* part_l,
+                        float* part_acc, const int* seq_slot, const int* seq_kvlen, const int* block_table,
+                        int max_pages, int page_size, int n_seqs, int n_q, int n_kv, float scale, int window,
+                        int run_len, int n_runs, cudaStream_t stream) {
+  const int G = n_q / n_kv;
+  const int chunks = (G + GMAX - 1) / GMAX;
+  const size_t smem = ((size_t)GMAX * run_len + (size_t)kDecWarps * GMAX * HD) * sizeof(float);
+  if (smem > 200 * 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(decode_split_kernel<T, HD, GMAX>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  dim3 grid(n_runs, n_kv * chunks, n_seqs);
+  decode_split_kernel<T, HD, GMAX><<<grid, kDecThreads, smem, stream>>>(
+      (const T*)q, (const T*)k_cache, (const T*)v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen, block_table,
+      max_pages, page_size, n_q, n_kv, scale, window, run_len, n_runs);
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+template <typename T, int HD>
+static int launch_split_g(int G, const void* q, const void* k_cache, const void* v_cache, float* part_m,
+                          float* part_l, float* part_acc, const int* seq_slot, const int* seq_kvlen,
+                          const int* block_table, int max_pages, int page_size, int n_seqs, int n_q, int n_kv,
+                          float scale, int window, int run_len, int n_runs, cudaStream_t stream) {
+  if (G <= 4)
+    return launch_split<T, HD, 4>(q, k_cache, v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen, block_table,
+                                  max_pages, page_size, n_seqs, n_q, n_kv, scale, window, run_len, n_runs, stream);
+  return launch_split<T, HD, 8>(q, k_cache, v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen, block_table,
+                                max_pages, page_size, n_seqs, n_q, n_kv, scale, window, run_len, n_runs, stream);
+}
+
+template <typename T>
+static int launch_split_hd(int hd, int G, const void* q, const void* k_cache, const void* v_cache, float* part_m,
+                           float* part_l, float* part_acc, const int* seq_slot, const int* seq_kvlen,
+                           const int* block_table, int max_pages, int page_size, int n_seqs, int n_q, int n_kv,
+                           float scale, int window, int run_len, int n_runs, cudaStream_t stream) {
+#define LLMIE_CASE(HD)                                                                                          \
+  case HD:                                                                                                      \
+    return launch_split_g<T, HD>(G, q, k_cache, v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen,          \
+                                 block_table, max_pages, page_size, n_seqs, n_q, n_kv, scale, window, run_len,  \
+                                 n_runs, stream);
+  switch (hd) {
+    LLMIE_CASE(16)
+    LLMIE_CASE(32)
+    LLMIE_CASE(64)
+    LLMIE_CASE(128)
+    default:
+      return LLMIE_ERR_UNSUPPORTED_SIZE;
+  }
+#undef LLMIE_CASE
+}
+
+}  // namespace llmie
+
+using namespace llmie;
+
+// 1 when attention_decode takes this head size and dtype, else 0 (the caller then uses the plain kernel).
+extern "C" int llmie_attention_decode_supported(int hd, int dtype) {
+  if (dtype != LLMIE_F32 && dtype != LLMIE_BF16) return 0;
+  return (hd == 16 || hd == 32 || hd == 64 || hd == 128) ? 1 : 0;
+}
+
+// q, out: [n_seqs, n_q * hd] (one token per sequence); caches [n_pages, n_kv, page_size, hd].
+// part_m, part_l: float32 [n_seqs * n_q * n_runs]; part_acc: float32 [n_seqs * n_q * n_runs * hd].
+// n_runs * run_len must cover the longest sequence the lengths on the device can name.
+extern "C" int llmie_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                      float* part_m, float* part_l, float* part_acc, const int* seq_slot,
+                                      const int* seq_kvlen, const int* block_table, int max_pages, int page_size,
+                                      int n_seqs, int n_q, int n_kv, int hd, float scale, int window, int run_len,
+                                      int n_runs, int dtype, cudaStream_t stream) {
+  if (n_seqs < 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv || page_size <= 0 || max_pages <= 0) return LLMIE_ERR_BAD_ARG;
+  if (run_len <= 0 || n_runs <= 0 || run_len % 32) return LLMIE_ERR_BAD_ARG;
+  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache)) return LLMIE_ERR_ALIGNMENT;
+  if (n_seqs == 0) return LLMIE_OK;
+  if (n_seqs > 65535 || n_runs > 0x7fffffff / 1) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  const int G = n_q / n_kv;
+  int rc;
+  if (dtype == LLMIE_F32)
+    rc = launch_split_hd<float>(hd, G, q, k_cache, v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen,
+                                block_table, max_pages, page_size, n_seqs, n_q, n_kv, scale, window, run_len, n_runs,
+                                stream);
+  else if (dtype == LLMIE_BF16)
+    rc = launch_split_hd<__nv_bfloat16>(hd, G, q, k_cache, v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen,
+                                        block_table, max_pages, page_size, n_seqs, n_q, n_kv, scale, window, run_len,
+                                        n_runs, stream);
+  else
+    return LLMIE_ERR_DTYPE;
+  if (rc != LLMIE_OK) return rc;
+  dim3 grid(n_q, n_seqs);
+  const int threads = hd < 32 ? 32 : (hd > 256 ? 256 : ((hd + 31) / 32) * 32);
+  if (dtype == LLMIE_F32)
+    decode_merge_kernel<float><<<grid, threads, 0, stream>>>(part_m, part_l, part_acc, (float*)out, seq_kvlen, n_q, hd,
+                                                             window, run_len, n_runs);
+  else
+    decode_merge_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(part_m, part_l, part_acc, (__nv_bfloat16*)out,
+                                                                     seq_kvlen, n_q, hd, window, run_len, n_runs);
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}

@@ -6,12 +6,31 @@ from __future__ import annotations
 
 import torch
 
+from ..kernels import ops
+
 
 class KernelPlan:
     def __init__(self, engine):
         self.engine = engine
         self.bf16 = engine.dtype == torch.bfloat16
 
+    @staticmethod
+    def decode_run_length(n_seqs: int, n_kv_heads: int, max_kv_len: int) -> int:
+        """Keys per block of the split-KV kernel: short runs when few (sequence, kv head) pairs
+        exist, so that the GPU still fills; 256 as in the reference otherwise
+        (src/flash_decode.py:271-272). Depends only on the step's shape, never on its data."""
+        pairs = max(1, n_seqs * n_kv_heads)
+        run = 256
+        while run > 64 and pairs * ((max_kv_len + run - 1) // run) < 2 * 148:
+            run //= 2
+        return run
+
     def attention(self, ctx, q, kv, out, n_q, n_kv, head_dim, scale, window) -> bool:
         """Returns True when a specialised kernel ran."""
+        if ctx.decode and ops.attention_decode_supported(head_dim, q.dtype):
+            run = self.decode_run_length(ctx.n_seqs, n_kv, ctx.max_kv_len)
+            n_runs = (ctx.max_kv_len + run - 1) // run
+            ops.attention_decode(q, kv.k, kv.v, out, ctx.seq_slot, ctx.seq_kvlen, kv.block_table, kv.page_size,
+                                 n_q, n_kv, head_dim, scale, window, run, n_runs)
+            return True
         return False

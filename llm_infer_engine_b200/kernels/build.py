@@ -30,6 +30,7 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fP
 FAMILIES: Dict[str, tuple] = {
     "elementwise": ("elementwise.cu", [], []),
     "attention_simt": ("attention_simt.cu", [], []),
+    "attention_decode": ("attention_decode.cu", [], []),
     "gemm_simt": ("gemm_simt.cu", [], []),
     "sampling": ("sampling.cu", [], []),
 }

@@ -189,6 +189,55 @@ def attention_paged(q, k_cache, v_cache, out, tok_pos, tok_seq, seq_slot, block_
     return out
 
 
+def attention_decode_supported(head_dim: int, dtype: torch.dtype) -> bool:
+    code = _DT.get(dtype)
+    if code is None:
+        return False
+    lib = build.load("attention_decode")
+    lib.llmie_attention_decode_supported.argtypes = [_c_int, _c_int]
+    lib.llmie_attention_decode_supported.restype = _c_int
+    return bool(lib.llmie_attention_decode_supported(head_dim, code))
+
+
+def decode_scratch_floats(n_seqs: int, n_q: int, head_dim: int, n_runs: int) -> int:
+    """float32 elements of scratch that attention_decode needs."""
+    return n_seqs * n_q * n_runs * (head_dim + 2)
+
+
+def attention_decode(q, k_cache, v_cache, out, seq_slot, seq_kvlen, block_table, page_size: int, n_q: int,
+                     n_kv: int, head_dim: int, scale: float, window: int, run_len: int, n_runs: int,
+                     scratch: Optional[torch.Tensor] = None):
+    """Split-KV attention for a step in which every sequence brings one token.
+
+    q, out [n, n_q hd]; seq_kvlen int32 [n] = keys each sequence holds INCLUDING this step's;
+    n_runs * run_len must be at least the longest length that seq_kvlen can name.
+    scratch: float32 with decode_scratch_floats(...) elements (allocated here if None)."""
+    n = q.shape[0]
+    _need(q, "q", None, (n, n_q * head_dim))
+    _need(out, "out", q.dtype, (n, n_q * head_dim))
+    _need(k_cache, "k_cache", q.dtype, (None, n_kv, page_size, head_dim))
+    _need(v_cache, "v_cache", q.dtype, tuple(k_cache.shape))
+    for name, t in (("seq_slot", seq_slot), ("seq_kvlen", seq_kvlen), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    if seq_slot.numel() < n or seq_kvlen.numel() < n:
+        raise KernelError("attention_decode: seq_slot / seq_kvlen shorter than the number of sequences")
+    need = decode_scratch_floats(n, n_q, head_dim, n_runs)
+    if scratch is None:
+        scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+    _need(scratch, "scratch", torch.float32)
+    if scratch.numel() < need:
+        raise KernelError(f"attention_decode: scratch holds {scratch.numel()} floats, {need} are needed")
+    n_ml = n * n_q * n_runs
+    base = scratch.data_ptr()
+    f = _fn("attention_decode", "llmie_attention_decode",
+            [_c_void_p] * 10 + [_c_int] * 6 + [_c_float] + [_c_int] * 4 + [_c_void_p])
+    _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), base, base + 4 * n_ml,
+             base + 8 * n_ml, seq_slot.data_ptr(), seq_kvlen.data_ptr(), block_table.data_ptr(),
+             block_table.shape[1], page_size, n, n_q, n_kv, head_dim, float(scale), int(window), int(run_len),
+             int(n_runs), _dt(q, "q"), _stream()), "attention_decode")
+    return out
+
+
 def gemm_f32_nt(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[M, N] = a[M, K] @ w[N, K]^T in true float32 (FMA on CUDA cores, fixed summation order)."""
     M, K = a.shape

@@ -1,0 +1,293 @@
+"""Each CUDA kernel alone against a plain float32 torch restatement of the same op, at sizes
+other than the engine's tiny models (widths that are no power of two, odd head counts, several
+head sizes, pages in scrambled order)."""
+import math
+
+import pytest
+import torch
+
+import plain_llama as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, f32=1e-5, bf16=2e-2):
+    return f32 if dtype == torch.float32 else bf16
+
+
+def ops():
+    from llm_infer_engine_b200.kernels import ops as o
+    return o
+
+
+# ------------------------------------------------------------------------------------------ elementwise
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d,vocab", [(96, 301), (2048, 1000), (40, 17)])
+def test_embedding(dtype, d, vocab):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(vocab, d, generator=g).to(dtype).to(DEV)
+    tokens = torch.randint(0, vocab, (37,), generator=g, dtype=torch.int32).to(DEV)
+    out = torch.empty(37, d, dtype=torch.float32, device=DEV)
+    ops().embedding(tokens, table, out)
+    assert torch.equal(out.cpu(), table.float().cpu()[tokens.cpu().long()])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d", [64, 96, 1000, 2048, 5120])
+def test_add_rmsnorm(dtype, d):
+    g = torch.Generator().manual_seed(1)
+    T, eps = 19, 3e-6
+    h = torch.randn(T, d, generator=g) * 3
+    delta = torch.randn(T, d, generator=g).to(dtype)
+    w = torch.rand(d, generator=g) + 0.5
+    h_dev = h.clone().to(DEV)
+    out = torch.empty(T, d, dtype=dtype, device=DEV)
+    ops().add_rmsnorm(h_dev, delta.to(DEV), w.to(DEV), eps, out)
+    h_ref = h + delta.float()
+    y_ref = plain.rms_norm(h_ref, w, eps)
+    assert torch.allclose(h_dev.cpu(), h_ref, atol=1e-6, rtol=1e-6)           # the sum is float32
+    assert torch.allclose(out.float().cpu(), y_ref, atol=tol(dtype, 2e-6, 3e-2), rtol=tol(dtype, 2e-6, 1e-2))
+    # no delta
+    h2 = h.clone().to(DEV)
+    ops().add_rmsnorm(h2, None, w.to(DEV), eps, out)
+    assert torch.equal(h2.cpu(), h)
+    assert torch.allclose(out.float().cpu(), plain.rms_norm(h, w, eps), atol=tol(dtype, 2e-6, 3e-2), rtol=1e-2)
+    # gathered rows: h is left alone
+    rows = torch.tensor([18, 0, 7], dtype=torch.int32, device=DEV)
+    h3 = h.clone().to(DEV)
+    out3 = torch.empty(3, d, dtype=dtype, device=DEV)
+    ops().add_rmsnorm(h3, delta.to(DEV), w.to(DEV), eps, out3, rows)
+    assert torch.equal(h3.cpu(), h)
+    assert torch.allclose(out3.float().cpu(), y_ref[[18, 0, 7]], atol=tol(dtype, 2e-6, 3e-2), rtol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("ff", [192, 250, 8192])
+def test_swiglu(dtype, ff):
+    g = torch.Generator().manual_seed(2)
+    gu = (torch.randn(11, 2 * ff, generator=g) * 2).to(dtype)
+    out = torch.empty(11, ff, dtype=dtype, device=DEV)
+    ops().swiglu(gu.to(DEV), out)
+    gate, up = gu.float()[:, :ff], gu.float()[:, ff:]
+    ref = gate * torch.sigmoid(gate) * up
+    assert torch.allclose(out.float().cpu(), ref, atol=tol(dtype, 1e-6, 2e-2), rtol=tol(dtype, 1e-5, 1e-2))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 300, 96), (5, 64, 50), (17, 129, 200), (70, 384, 96), (200, 2048, 513)])
+def test_gemm_f32(M, N, K):
+    g = torch.Generator().manual_seed(3)
+    a, w = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g)
+    out = ops().gemm_f32_nt(a.to(DEV), w.to(DEV)).cpu()
+    ref = (a.double() @ w.double().T).float()
+    assert torch.allclose(out, ref, atol=1e-4, rtol=1e-5)
+    # a row's result does not depend on the other rows of the launch
+    one = ops().gemm_f32_nt(a[M // 2:M // 2 + 1].contiguous().to(DEV), w.to(DEV)).cpu()
+    assert torch.equal(one[0], out[M // 2])
+
+
+# ------------------------------------------------------------------------------------------ paged cache helpers
+class Paged:
+    """Dense per-sequence K/V laid into scrambled pages, with the index arrays the kernels want."""
+
+    def __init__(self, seq_lens, n_kv, hd, dtype, page_size=64, seed=0, extra_slots=3):
+        g = torch.Generator().manual_seed(seed)
+        self.page_size, self.n_kv, self.hd = page_size, n_kv, hd
+        n = len(seq_lens)
+        n_slots = n + extra_slots
+        pages_per = [(l + page_size - 1) // page_size for l in seq_lens]
+        max_pages = max(pages_per) + 1
+        n_pages = sum(pages_per) + 5
+        perm = torch.randperm(n_pages, generator=g).tolist()
+        self.slots = torch.randperm(n_slots, generator=g)[:n].tolist()
+        self.block_table = torch.full((n_slots, max_pages), n_pages - 1, dtype=torch.int32)
+        nxt = 0
+        for i, s in enumerate(self.slots):
+            for p in range(pages_per[i]):
+                self.block_table[s, p] = perm[nxt]
+                nxt += 1
+        self.k = torch.zeros(n_pages, n_kv, page_size, hd, dtype=dtype)
+        self.v = torch.zeros(n_pages, n_kv, page_size, hd, dtype=dtype)
+        self.dense_k = [torch.randn(l, n_kv, hd, generator=g).to(dtype) for l in seq_lens]
+        self.dense_v = [torch.randn(l, n_kv, hd, generator=g).to(dtype) for l in seq_lens]
+
+    def fill(self, upto=None):
+        """Writes the dense tensors into their pages (positions < upto[i] if given)."""
+        for i, s in enumerate(self.slots):
+            L = self.dense_k[i].shape[0] if upto is None else upto[i]
+            for pos in range(L):
+                page = int(self.block_table[s, pos // self.page_size])
+                self.k[page, :, pos % self.page_size] = self.dense_k[i][pos]
+                self.v[page, :, pos % self.page_size] = self.dense_v[i][pos]
+
+    def dev(self):
+        return self.k.to(DEV), self.v.to(DEV), self.block_table.to(DEV)
+
+
+def ref_attention(q, k, v, positions, scale, window):
+    """q [T, Hq, hd] at absolute `positions`; k, v [L, Hkv, hd] float32; plain softmax attention."""
+    Hq, Hkv = q.shape[1], k.shape[1]
+    out = torch.zeros_like(q)
+    for t, p in enumerate(positions):
+        lo = max(0, p - window + 1) if window > 0 else 0
+        for h in range(Hq):
+            kk, vv = k[lo:p + 1, h // (Hq // Hkv)], v[lo:p + 1, h // (Hq // Hkv)]
+            s = (kk @ q[t, h]) * scale
+            out[t, h] = torch.softmax(s, dim=0) @ vv
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q,n_kv,hd", [(4, 2, 16), (3, 1, 32), (6, 2, 48), (8, 8, 64), (5, 5, 80), (4, 1, 128)])
+def test_rope_store_and_paged_attention(dtype, n_q, n_kv, hd):
+    """Ragged prefill at nonzero start positions: rotate + cache write, then plain attention."""
+    o = ops()
+    starts, news = [0, 70, 3], [50, 9, 130]
+    totals = [s + n for s, n in zip(starts, news)]
+    pg = Paged(totals, n_kv, hd, dtype, seed=hd)
+    pg.fill(upto=starts)              # what earlier steps left; this step's keys come from rope_store
+    theta, rot = 10000.0, hd
+    inv = plain.inv_frequencies(rot, theta, None)
+    max_pos = 256
+    cos, sin = plain.rotation_tables(torch.arange(max_pos), inv)
+    table = torch.stack([cos, sin], dim=-1).contiguous()
+    T = sum(news)
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn(T, (n_q + 2 * n_kv) * hd, generator=g).to(dtype)
+    tok_seq = torch.repeat_interleave(torch.arange(3), torch.tensor(news)).int()
+    tok_pos = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, news)]).int()
+    k_dev, v_dev, bt = pg.dev()
+    q_out = torch.empty(T, n_q * hd, dtype=dtype, device=DEV)
+    slots = torch.tensor(pg.slots, dtype=torch.int32, device=DEV)
+    o.rope_store(qkv.to(DEV), q_out, k_dev, v_dev, table.to(DEV), tok_pos.to(DEV), tok_seq.to(DEV), slots, bt, 64,
+                 n_q, n_kv, hd, rot)
+    # reference rotation in float32
+    qf = qkv.float()[:, :n_q * hd].view(T, n_q, hd)
+    kf = qkv.float()[:, n_q * hd:(n_q + n_kv) * hd].view(T, n_kv, hd)
+    vf = qkv.float()[:, (n_q + n_kv) * hd:].view(T, n_kv, hd)
+    c, s = cos[tok_pos.long()][:, None, :], sin[tok_pos.long()][:, None, :]
+    rot_q = plain.rotate_half(qf, c, s)
+    rot_k = plain.rotate_half(kf, c, s)
+    assert torch.allclose(q_out.float().cpu().view(T, n_q, hd), rot_q, atol=tol(dtype, 1e-6, 3e-2))
+    k_host, v_host = k_dev.cpu(), v_dev.cpu()
+    off = 0
+    for i, (st, n) in enumerate(zip(starts, news)):
+        for j in range(n):
+            pos = st + j
+            page = int(pg.block_table[pg.slots[i], pos // 64])
+            assert torch.allclose(k_host[page, :, pos % 64].float(), rot_k[off + j], atol=tol(dtype, 1e-6, 3e-2))
+            assert torch.equal(v_host[page, :, pos % 64].float(), vf[off + j].to(dtype).float())
+            # pages hold exactly what the dense history holds from here on
+            pg.dense_k[i][pos] = k_host[page, :, pos % 64]
+            pg.dense_v[i][pos] = v_host[page, :, pos % 64]
+        off += n
+    # attention over the cache, with and without a window
+    for window in (0, 40):
+        out = torch.empty(T, n_q * hd, dtype=dtype, device=DEV)
+        o.attention_paged(q_out, k_dev, v_dev, out, tok_pos.to(DEV), tok_seq.to(DEV), slots, bt, 64, n_q, n_kv, hd,
+                          hd ** -0.5, window)
+        off = 0
+        for i, n in enumerate(news):
+            ref = ref_attention(q_out.float().cpu().view(T, n_q, hd)[off:off + n], pg.dense_k[i].float(),
+                                pg.dense_v[i].float(), tok_pos[off:off + n].tolist(), hd ** -0.5, window)
+            got = out.float().cpu().view(T, n_q, hd)[off:off + n]
+            assert torch.allclose(got, ref, atol=tol(dtype, 2e-5, 2e-2)), (window, i, float((got - ref).abs().max()))
+            off += n
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q,n_kv,hd", [(4, 2, 16), (3, 1, 32), (32, 8, 64), (24, 8, 128), (12, 2, 64), (16, 1, 64)])
+@pytest.mark.parametrize("run_len", [64, 256])
+def test_attention_decode(dtype, n_q, n_kv, hd, run_len):
+    """Split-KV decode against the plain formula: unequal lengths from 1 to several runs, a
+    window, and a far key made to stand out so that a lost run or page cannot hide."""
+    o = ops()
+    assert o.attention_decode_supported(hd, dtype)
+    lens = [1, 63, 64, 65, 300, 777, 1024]
+    pg = Paged(lens, n_kv, hd, dtype, seed=7 + hd)
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(len(lens), n_q, hd, generator=g)
+    # needle: in the longest sequences one early key matches the query strongly
+    for i, L in enumerate(lens):
+        if L >= 300:
+            needle = 3 + i
+            qh = q[i, ::(n_q // n_kv)]                                           # first query head of each group
+            gain = 24.0 / ((qh * qh).sum(-1, keepdim=True) * hd ** -0.5)          # its score becomes 24
+            pg.dense_k[i][needle, :, :] = (qh * gain).to(dtype)
+            pg.dense_v[i][needle, :, :] = 5.0
+    pg.fill()
+    k_dev, v_dev, bt = pg.dev()
+    qd = q.to(dtype).reshape(len(lens), n_q * hd).to(DEV)
+    slots = torch.tensor(pg.slots, dtype=torch.int32, device=DEV)
+    kvlen = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    max_len = 1100
+    n_runs = (max_len + run_len - 1) // run_len
+    for window in (0, 100):
+        out = torch.full((len(lens), n_q * hd), float("nan"), dtype=dtype, device=DEV)
+        o.attention_decode(qd, k_dev, v_dev, out, slots, kvlen, bt, 64, n_q, n_kv, hd, hd ** -0.5, window, run_len,
+                           n_runs)
+        plain_out = torch.empty_like(out)
+        tok_pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=DEV)
+        tok_seq = torch.arange(len(lens), dtype=torch.int32, device=DEV)
+        o.attention_paged(qd, k_dev, v_dev, plain_out, tok_pos, tok_seq, slots, bt, 64, n_q, n_kv, hd, hd ** -0.5, window)
+        for i, L in enumerate(lens):
+            ref = ref_attention(qd.float().cpu().view(len(lens), n_q, hd)[i:i + 1], pg.dense_k[i].float(),
+                                pg.dense_v[i].float(), [L - 1], hd ** -0.5, window)[0]
+            got = out.float().cpu().view(len(lens), n_q, hd)[i]
+            assert torch.allclose(got, ref, atol=tol(dtype, 2e-5, 3e-2)), (window, L, float((got - ref).abs().max()))
+            if window == 0 and L >= 300:
+                assert float(got[::n_q // n_kv].mean()) > 4.5      # the needle's value is what comes out
+        assert torch.allclose(out.float(), plain_out.float(), atol=tol(dtype, 2e-5, 3e-2))
+
+
+# ------------------------------------------------------------------------------------------ sampling
+def test_argmax_ties_and_sizes():
+    o = ops()
+    for V in (17, 384, 1000, 128256):
+        g = torch.Generator().manual_seed(V)
+        logits = torch.randn(5, V, generator=g)
+        logits[1, 7] = logits[1].max() + 1
+        logits[2, [3, V - 1]] = 50.0              # a tie: the lowest index wins
+        logits[3, V - 1] = 60.0
+        out = torch.empty(5, dtype=torch.int32, device=DEV)
+        o.sample(logits.to(DEV), out)
+        assert out.cpu().tolist() == [plain.greedy(r) for r in logits]
+        assert out.cpu().tolist()[2] == 3
+
+
+@pytest.mark.parametrize("top_p", [1.0, 0.9, 0.3, 0.0])
+@pytest.mark.parametrize("V", [384, 5000])
+def test_temperature_sampling_matches_plain_draw(top_p, V):
+    from llm_infer_engine_b200.sampling import uniform_for
+    o = ops()
+    g = torch.Generator().manual_seed(13)
+    R, temperature, seed = 24, 0.8, 1234
+    logits = torch.randn(R, V, generator=g) * 3
+    seq_ids = torch.arange(100, 100 + R, dtype=torch.int32)
+    counters = torch.arange(R, dtype=torch.int32) % 5
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    cnt_dev = counters.clone().to(DEV)
+    o.sample(logits.to(DEV), out, temperature, top_p, seed, seq_ids.to(DEV), cnt_dev)
+    assert cnt_dev.cpu().tolist() == (counters + 1).tolist()
+    got = out.cpu().tolist()
+    for r in range(R):
+        u = uniform_for(seed, int(seq_ids[r]), int(counters[r]))
+        want = plain.sample_with_uniform(logits[r], temperature, top_p, u)
+        if got[r] != want:
+            # float32 vs float64 cumulative sums may put u on the other side of a boundary: then
+            # the two tokens must be neighbours in the kept set and u within rounding of the edge
+            probs = torch.softmax(logits[r].double() / temperature, dim=-1)
+            keep = plain.kept_by_top_p(probs, top_p)
+            assert bool(keep[got[r]]), (r, got[r], want)
+            cdf = torch.cumsum(torch.where(keep, probs, torch.zeros_like(probs)), 0) / probs[keep].sum()
+            edge = float(cdf[min(got[r], want)])
+            assert abs(edge - u) < 1e-5, (r, got[r], want, edge, u)
+    if top_p == 0.0:
+        assert got == [plain.greedy(r) for r in logits]
+    # the same sequence id and counter give the same draw whatever row it sits in
+    out2 = torch.empty(R, dtype=torch.int32, device=DEV)
+    perm = torch.randperm(R, generator=g)
+    o.sample(logits[perm].to(DEV), out2, temperature, top_p, seed, seq_ids[perm].to(DEV), counters[perm].clone().to(DEV))
+    assert out2.cpu().tolist() == [got[i] for i in perm.tolist()]
