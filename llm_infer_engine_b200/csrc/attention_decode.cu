@@ -302,3 +302,60 @@ extern "C" int llmie_attention_decode(const void* q, const void* k_cache, const 
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }
+
+// ------------------------------------------------------------------------------------------
+// The same attention for callers that must not allocate: scratch lives in the device image.
+// See attention_decode_noalloc.h for who needs this, the limit and the sharing rules.
+#include "attention_decode_noalloc.h"
+#include <mutex>
+
+namespace llmie {
+constexpr size_t kNoAllocFloats = LLMIE_NOALLOC_SCRATCH_BYTES / sizeof(float);
+// Device code could name this array directly. Host code cannot: on the host the name is only a
+// stand-in for the symbol, not a device address, so the launcher below asks the runtime for the
+// address once per device and hands THAT to the kernels.
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocFloats];
+
+constexpr int kMaxDevices = 64;
+static float* g_noalloc_addr[kMaxDevices] = {nullptr};
+static std::mutex g_noalloc_mutex;
+
+// Device address of the array on the CURRENT device; looked up on first use per device.
+static int noalloc_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return LLMIE_ERR_BAD_ARG;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_addr[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (!p) return LLMIE_ERR_BAD_ARG;
+    g_noalloc_addr[dev] = p;
+  }
+  *out = g_noalloc_addr[dev];
+  return LLMIE_OK;
+}
+}  // namespace llmie
+
+extern "C" unsigned long long llmie_attention_decode_noalloc_capacity(void) { return LLMIE_NOALLOC_SCRATCH_BYTES; }
+
+extern "C" int llmie_attention_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                              const int* seq_slot, const int* seq_kvlen, const int* block_table,
+                                              int max_pages, int page_size, int n_seqs, int n_q, int n_kv, int hd,
+                                              float scale, int window, int run_len, int n_runs, int dtype,
+                                              cudaStream_t stream) {
+  if (n_seqs < 0 || n_q <= 0 || n_runs <= 0 || hd <= 0) return LLMIE_ERR_BAD_ARG;
+  const unsigned long long n_ml = (unsigned long long)n_seqs * (unsigned long long)n_q * (unsigned long long)n_runs;
+  const unsigned long long need = n_ml * (unsigned long long)(hd + 2);
+  if (need > kNoAllocFloats) return LLMIE_ERR_SCRATCH_TOO_SMALL;
+  float* scratch = nullptr;
+  const int rc = noalloc_scratch(&scratch);
+  if (rc != LLMIE_OK) return rc;
+  // [part_m | part_l | part_acc]; every entry that the merge kernel reads is written by the split
+  // kernel of this same call, so what an earlier call left behind is never seen.
+  return llmie_attention_decode(q, k_cache, v_cache, out, scratch, scratch + n_ml, scratch + 2 * n_ml, seq_slot,
+                                seq_kvlen, block_table, max_pages, page_size, n_seqs, n_q, n_kv, hd, scale, window,
+                                run_len, n_runs, dtype, stream);
+}

@@ -1,0 +1,81 @@
+"""The allocation-free decode-attention entry point, called through its exported C symbol.
+
+Some callers cannot allocate device memory at the moment they need attention: all of it is
+already in a pool of their own, or they sit in a loop where a cudaMalloc stall is not allowed, or
+they are C programs with no tensor library. `llmie_attention_decode_noalloc` serves them from a
+fixed scratch array inside the library. Its results must be those of the ordinary entry point,
+call after call (the array is shared and keeps the previous call's contents), and a problem
+larger than the array must be refused, not run. This file is named to be collected last.
+"""
+import ctypes
+
+import pytest
+import torch
+
+from test_kernels_gpu import Paged
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _symbol():
+    from llm_infer_engine_b200.kernels import build
+    lib = build.load("attention_decode")
+    fn = lib.llmie_attention_decode_noalloc
+    fn.argtypes = [ctypes.c_void_p] * 7 + [ctypes.c_int] * 6 + [ctypes.c_float] + [ctypes.c_int] * 4 + [ctypes.c_void_p]
+    fn.restype = ctypes.c_int
+    cap = lib.llmie_attention_decode_noalloc_capacity
+    cap.restype = ctypes.c_ulonglong
+    return fn, int(cap())
+
+
+def _case(seed, lens, n_q, n_kv, hd, dtype):
+    pg = Paged(lens, n_kv, hd, dtype, seed=seed)
+    pg.fill()
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(len(lens), n_q * hd, generator=g).to(dtype).to(DEV)
+    k, v, bt = pg.dev()
+    slots = torch.tensor(pg.slots, dtype=torch.int32, device=DEV)
+    kvlen = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    return q, k, v, bt, slots, kvlen
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_no_alloc_matches_ordinary_entry_point_twice(dtype):
+    from llm_infer_engine_b200.kernels import ops
+    fn, capacity = _symbol()
+    assert capacity == 16 * 1024 * 1024
+    n_q, n_kv, hd, run_len = 12, 4, 64, 128
+    code = 0 if dtype == torch.float32 else 1
+    # two calls in a row with different data and different shapes: the second finds the first's
+    # leftovers in the shared array and must not be disturbed by them
+    for seed, lens in ((1, [5, 130, 700, 64, 333]), (2, [901, 17, 256])):
+        q, k, v, bt, slots, kvlen = _case(seed, lens, n_q, n_kv, hd, dtype)
+        n_runs = (1024 + run_len - 1) // run_len
+        want = torch.empty_like(q)
+        ops.attention_decode(q, k, v, want, slots, kvlen, bt, 64, n_q, n_kv, hd, hd ** -0.5, 0, run_len, n_runs)
+        got = torch.full_like(q, float("nan"))
+        stream = torch.cuda.current_stream().cuda_stream
+        before = torch.cuda.memory_allocated()
+        rc = fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), got.data_ptr(), slots.data_ptr(), kvlen.data_ptr(),
+                bt.data_ptr(), bt.shape[1], 64, len(lens), n_q, n_kv, hd, hd ** -0.5, 0, run_len, n_runs, code, stream)
+        assert rc == 0, rc
+        assert torch.cuda.memory_allocated() == before
+        torch.cuda.synchronize()
+        tol = 2e-5 if dtype == torch.float32 else 3e-2
+        assert torch.allclose(got.float(), want.float(), atol=tol), float((got.float() - want.float()).abs().max())
+
+
+def test_no_alloc_refuses_what_does_not_fit():
+    fn, capacity = _symbol()
+    n_q, n_kv, hd, run_len = 32, 8, 64, 64
+    lens = [10, 20]
+    q, k, v, bt, slots, kvlen = _case(3, lens, n_q, n_kv, hd, torch.bfloat16)
+    n_runs = capacity // 4 // (len(lens) * n_q * (hd + 2)) + 1          # one run too many for the array
+    out = torch.full_like(q, 7.0)
+    rc = fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), slots.data_ptr(), kvlen.data_ptr(),
+            bt.data_ptr(), bt.shape[1], 64, len(lens), n_q, n_kv, hd, hd ** -0.5, 0, run_len, n_runs, 1,
+            torch.cuda.current_stream().cuda_stream)
+    assert rc == -5
+    torch.cuda.synchronize()
+    assert bool((out == 7.0).all())         # nothing ran
