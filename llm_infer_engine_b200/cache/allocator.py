@@ -61,11 +61,11 @@ class FreeList:
 
     def check(self) -> None:
         """Every id is either free once or held, never both, never missing."""
-        free = sorted(self._free)
-        if len(set(free)) != len(free):
+        free = set(self._free)
+        if len(free) != len(self._free):
             raise CacheError(f"a {self.what} is in the free list twice")
         for i in range(self.n):
-            if self._held[i] == (i in set(free)):
+            if self._held[i] == (i in free):
                 raise CacheError(f"{self.what} {i} is {'held and free' if self._held[i] else 'neither held nor free'}")
 
 
