@@ -52,6 +52,45 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
   for (int i = threadIdx.x; i < d; i += blockDim.x) yr[i] = from_f32<T>(row_buf[i] * rstd * w[i]);
 }
 
+// The same for rows of at most 8 * 1024 elements with d % 8 == 0: each thread owns one run of 8
+// elements, kept in registers, so the row is read once.
+template <typename T>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const T* __restrict__ delta,
+                                       const float* __restrict__ w, T* __restrict__ y,
+                                       const int* __restrict__ rows, int d, float eps) {
+  __shared__ float red[32];
+  const int b = blockIdx.x;
+  const int r = rows ? rows[b] : b;
+  const int i = threadIdx.x * 8;
+  const bool active = i < d;
+  float x[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) x[e] = 0.f;
+  if (active) {
+    float* hr = h + (size_t)r * d + i;
+    load8(hr, x);
+    if (delta) {
+      float dv[8];
+      load8(delta + (size_t)r * d + i, dv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] += dv[e];
+      if (!rows) store8(hr, x);
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+  ss = block_sum(ss, red);
+  const float rstd = rsqrtf(ss / (float)d + eps);
+  if (active) {
+    float wv[8], o[8];
+    load8(w + i, wv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = x[e] * rstd * wv[e];
+    store8(y + (size_t)b * d + i, o);
+  }
+}
+
 // h += delta, no norm (used when a block arrangement needs the bare sum)
 template <typename T>
 __global__ void residual_add_kernel(float* __restrict__ h, const T* __restrict__ delta, size_t n) {
@@ -199,6 +238,12 @@ extern "C" int llmie_embedding(const int* tokens, const void* table, int table_d
 template <typename T>
 static int add_rmsnorm_launch(float* h, const void* delta, const float* w, void* y, const int* rows, int n_out,
                               int d, float eps, cudaStream_t stream) {
+  if (d % 8 == 0 && d <= 8 * 1024 && aligned16(h) && aligned16(w) && aligned16(y) && (!delta || aligned16(delta))) {
+    const int threads = ((d / 8 + 31) / 32) * 32;
+    add_rmsnorm_vec_kernel<T><<<n_out, threads, 0, stream>>>(h, (const T*)delta, w, (T*)y, rows, d, eps);
+    LLMIE_LAUNCH_CHECK();
+    return LLMIE_OK;
+  }
   const size_t smem = (size_t)d * sizeof(float);
   if (smem > 200 * 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
   if (smem > 48 * 1024) {

@@ -146,6 +146,53 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature
   if (threadIdx.x == 0) out[r] = chosen;
 }
 
+// Greedy choice with many blocks per row, for large vocabularies: block (s, r) scans one slice
+// of row r, a second kernel merges the slices. Ties go to the lowest index in both stages.
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float* __restrict__ logits, int ld, int V, int slices, float* __restrict__ part_val,
+                      int* __restrict__ part_idx) {
+  __shared__ MaxIdx scratch[32];
+  const int s = blockIdx.x, r = blockIdx.y;
+  const int chunk = (V + slices - 1) / slices;
+  const int begin = min(V, s * chunk), end = min(V, begin + chunk);
+  const float* row = logits + (size_t)r * ld;
+  MaxIdx best{-INFINITY, 0x7fffffff};
+  for (int i = begin + threadIdx.x; i < end; i += blockDim.x) best = better(best, MaxIdx{row[i], i});
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    MaxIdx other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) scratch[warp] = best;
+  __syncthreads();
+  if (warp == 0) {
+    MaxIdx m = (lane < (blockDim.x >> 5)) ? scratch[lane] : MaxIdx{-INFINITY, 0x7fffffff};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      MaxIdx other{__shfl_xor_sync(0xffffffffu, m.v, o), __shfl_xor_sync(0xffffffffu, m.i, o)};
+      m = better(m, other);
+    }
+    if (lane == 0) {
+      part_val[r * slices + s] = m.v;
+      part_idx[r * slices + s] = m.i;
+    }
+  }
+}
+
+__global__ void argmax_merge_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int slices,
+                                    int* __restrict__ out) {
+  const int r = blockIdx.x, lane = threadIdx.x;
+  MaxIdx best{-INFINITY, 0x7fffffff};
+  for (int s = lane; s < slices; s += 32) best = better(best, MaxIdx{part_val[r * slices + s], part_idx[r * slices + s]});
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    MaxIdx other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  if (lane == 0) out[r] = best.i == 0x7fffffff ? 0 : best.i;
+}
+
 // tokens[i] = sampled[i] for the lanes of a decode step (feeds the next step on the device)
 __global__ void copy_int_kernel(const int* __restrict__ src, int* __restrict__ dst, int n) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -174,6 +221,19 @@ extern "C" int llmie_copy_int(const int* src, int* dst, int n, cudaStream_t stre
   if (n < 0) return LLMIE_ERR_BAD_ARG;
   if (n == 0) return LLMIE_OK;
   copy_int_kernel<<<(n + 255) / 256, 256, 0, stream>>>(src, dst, n);
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+// Greedy tokens with `slices` blocks per row. part_val / part_idx: scratch of n_rows * slices elements.
+extern "C" int llmie_argmax(const float* logits, int n_rows, int V, int ld, int slices, float* part_val, int* part_idx,
+                            int* out, cudaStream_t stream) {
+  if (n_rows < 0 || V <= 0 || ld < V || slices <= 0 || slices > 1024) return LLMIE_ERR_BAD_ARG;
+  if (n_rows == 0) return LLMIE_OK;
+  if (n_rows > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  argmax_partial_kernel<<<dim3(slices, n_rows), 256, 0, stream>>>(logits, ld, V, slices, part_val, part_idx);
+  LLMIE_LAUNCH_CHECK();
+  argmax_merge_kernel<<<n_rows, 32, 0, stream>>>(part_val, part_idx, slices, out);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }

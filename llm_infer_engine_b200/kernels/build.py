@@ -32,6 +32,7 @@ FAMILIES: Dict[str, tuple] = {
     "attention_simt": ("attention_simt.cu", [], []),
     "attention_decode": ("attention_decode.cu", [], []),
     "gemm_simt": ("gemm_simt.cu", [], []),
+    "gemm_skinny": ("gemm_skinny.cu", [], []),
     "sampling": ("sampling.cu", [], []),
 }
 

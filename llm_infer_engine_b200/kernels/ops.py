@@ -252,12 +252,62 @@ def gemm_f32_nt(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = 
     return out
 
 
+SKINNY_STORE_BF16, SKINNY_STORE_F32, SKINNY_ADD_F32, SKINNY_SWIGLU = 0, 1, 2, 3
+SKINNY_MAX_BATCH = 32          # what the kernel takes
+SKINNY_BEST_BATCH = 8          # up to here it beats the library GEMM (measured on B200)
+
+
+def gemm_skinny_ok(batch: int, n: int, k: int, epilogue: int = SKINNY_STORE_BF16) -> bool:
+    """Whether gemm_skinny takes this shape (else the caller uses a tiled GEMM)."""
+    if not 0 < batch <= SKINNY_MAX_BATCH or k % 32:
+        return False
+    return (n % 2 == 0 and (n // 2) % 8 == 0) if epilogue == SKINNY_SWIGLU else n % 16 == 0
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> torch.Tensor:
+    """y = x w^T for a few rows of x and a large bfloat16 w [N, K] that is read once.
+
+    epilogue SKINNY_STORE_BF16 / SKINNY_STORE_F32: out [batch, N] = y;  SKINNY_ADD_F32: out (float32) += y;
+    SKINNY_SWIGLU: w = [gate rows; up rows], out bfloat16 [batch, N / 2] = silu(gate) * up."""
+    batch, K = x.shape
+    N = w.shape[0]
+    _need(x, "x", torch.bfloat16)
+    _need(w, "w", torch.bfloat16, (N, K))
+    if not gemm_skinny_ok(batch, N, K, epilogue):
+        raise KernelError(f"gemm_skinny: shape batch={batch}, N={N}, K={K} is not supported")
+    cols = N // 2 if epilogue == SKINNY_SWIGLU else N
+    want = torch.float32 if epilogue in (SKINNY_STORE_F32, SKINNY_ADD_F32) else torch.bfloat16
+    _need(out, "out", want, (batch, cols))
+    f = _fn("gemm_skinny", "llmie_gemm_skinny", [_c_void_p] * 3 + [_c_int] * 5 + [_c_void_p])
+    _check(f(x.data_ptr(), w.data_ptr(), out.data_ptr(), batch, N, K, cols, epilogue, _stream()), "gemm_skinny")
+    return out
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Greedy token per row of float32 logits [R, V] (lowest index wins a tie), many blocks per row."""
+    R, V = logits.shape
+    _need(logits, "logits", torch.float32)
+    _need(out, "out", torch.int32)
+    if out.shape[0] < R:
+        raise KernelError("argmax: out is shorter than the number of rows")
+    slices = max(1, min(128, V // 1024))
+    part_val = torch.empty(R * slices, dtype=torch.float32, device=logits.device)
+    part_idx = torch.empty(R * slices, dtype=torch.int32, device=logits.device)
+    f = _fn("sampling", "llmie_argmax", [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                                         _c_void_p])
+    _check(f(logits.data_ptr(), R, V, logits.stride(0), slices, part_val.data_ptr(), part_idx.data_ptr(),
+             out.data_ptr(), _stream()), "argmax")
+    return out
+
+
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float = 0.0, top_p: float = 1.0, seed: int = 0,
            seq_ids: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One token per row of float32 logits [R, V]: argmax when temperature <= 0 (lowest index wins a
     tie), else a draw from softmax(logits / T) cut by top_p, with the uniform number of
     (seed, seq_ids[r], counters[r]); counters[r] is then incremented. out int32 [R]."""
     R, V = logits.shape
+    if temperature <= 0 and V >= 4096 and logits.is_contiguous():
+        return argmax(logits, out)
     _need(logits, "logits", torch.float32)
     _need(out, "out", torch.int32)
     if out.shape[0] < R:

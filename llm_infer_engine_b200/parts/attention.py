@@ -22,6 +22,8 @@ class GroupedQueryAttention(Mixer):
     """params: hidden, n_heads, n_kv_heads, head_dim, position (PartSpec of a position encoding),
     window (0 = every earlier key), scale (None = 1/sqrt(head_dim))."""
 
+    adds_to_residual = True
+
     def __init__(self, params, runtime):
         super().__init__(params, runtime)
         self.hidden = int(params["hidden"])
@@ -57,12 +59,14 @@ class GroupedQueryAttention(Mixer):
     def cache_requests(self):
         return [KVRequest(self.n_kv_heads, self.head_dim, self.window)]
 
-    def forward(self, x, ctx, unit, owns_cache):
+    def forward(self, x, ctx, unit, owns_cache, residual=None):
         kv = unit.kv
         qkv = self.qkv(x)
         q = self.position.encode_and_store(qkv, ctx, kv, self.n_heads, self.n_kv_heads, self.head_dim, owns_cache)
         out = torch.empty_like(q)
         ctx.attention(q, kv, out, self.n_heads, self.n_kv_heads, self.head_dim, self.scale, self.window)
+        if residual is not None and self.o.add_into(out, residual):
+            return None
         return self.o(out)
 
 

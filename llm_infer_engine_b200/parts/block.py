@@ -7,10 +7,18 @@ from .base import Block, register_block
 
 
 class PreNormBlock(Block):
+    """A part that sets `adds_to_residual = True` accepts `residual=h` and may add its output into
+    h itself (in float32, inside its last kernel); it then returns None instead of a branch output."""
+
     def forward(self, h, pending, ctx, unit, owns_cache):
         x = self.mixer_norm.forward(h, pending)
-        mixed = self.mixer.forward(x, ctx, unit, owns_cache)
+        if getattr(self.mixer, "adds_to_residual", False):
+            mixed = self.mixer.forward(x, ctx, unit, owns_cache, residual=h)
+        else:
+            mixed = self.mixer.forward(x, ctx, unit, owns_cache)
         x = self.feed_forward_norm.forward(h, mixed)
+        if getattr(self.feed_forward, "adds_to_residual", False):
+            return h, self.feed_forward.forward(x, ctx, residual=h)
         return h, self.feed_forward.forward(x, ctx)
 
 

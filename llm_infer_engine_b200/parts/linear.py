@@ -35,6 +35,32 @@ class Linear:
             y = ops.gemm_f32_nt(x if x.dtype == torch.float32 else x.float(), w)
             return y if out_dtype == torch.float32 else y.to(out_dtype)
         xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+        T = xb.shape[0]
+        if T <= ops.SKINNY_BEST_BATCH and ops.gemm_skinny_ok(T, self.out_features, self.in_features):
+            f32 = out_dtype == torch.float32
+            out = torch.empty((T, self.out_features), dtype=out_dtype, device=x.device)
+            return ops.gemm_skinny(xb, w, out, ops.SKINNY_STORE_F32 if f32 else ops.SKINNY_STORE_BF16)
         if out_dtype == torch.bfloat16:
             return torch.mm(xb, w.t())
         return torch.mm(xb, w.t(), out_dtype=torch.float32)
+
+    def add_into(self, x: torch.Tensor, h: torch.Tensor) -> bool:
+        """h (float32 [T, out]) += x W^T inside the product's kernel, when a kernel for this shape
+        exists. Returns False (and does nothing) otherwise."""
+        if self.weight.dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
+            return False
+        if x.shape[0] > ops.SKINNY_BEST_BATCH or not ops.gemm_skinny_ok(x.shape[0], self.out_features, self.in_features):
+            return False
+        ops.gemm_skinny(x, self.weight, h, ops.SKINNY_ADD_F32)
+        return True
+
+    def swiglu(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        """For a weight that is [gate rows; up rows]: silu(x Wg^T) * (x Wu^T) in one kernel, or None
+        when no kernel for this shape exists."""
+        if self.weight.dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
+            return None
+        if x.shape[0] > ops.SKINNY_BEST_BATCH or not ops.gemm_skinny_ok(x.shape[0], self.out_features,
+                                                                         self.in_features, ops.SKINNY_SWIGLU):
+            return None
+        out = torch.empty((x.shape[0], self.out_features // 2), dtype=torch.bfloat16, device=x.device)
+        return ops.gemm_skinny(x, self.weight, out, ops.SKINNY_SWIGLU)

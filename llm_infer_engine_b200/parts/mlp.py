@@ -15,6 +15,8 @@ from .linear import Linear
 class SwiGLU(FeedForward):
     """params: hidden, intermediate."""
 
+    adds_to_residual = True
+
     def __init__(self, params, runtime):
         super().__init__(params, runtime)
         self.hidden = int(params["hidden"])
@@ -36,10 +38,14 @@ class SwiGLU(FeedForward):
     def weight_bytes(self) -> int:
         return self.gate_up.nbytes() + self.down.nbytes()
 
-    def forward(self, x, ctx):
-        gu = self.gate_up(x)
-        act = torch.empty((x.shape[0], self.intermediate), dtype=gu.dtype, device=x.device)
-        ops.swiglu(gu, act)
+    def forward(self, x, ctx, residual=None):
+        act = self.gate_up.swiglu(x)                 # one-token steps: product, activation and gate in one kernel
+        if act is None:
+            gu = self.gate_up(x)
+            act = torch.empty((x.shape[0], self.intermediate), dtype=gu.dtype, device=x.device)
+            ops.swiglu(gu, act)
+        if residual is not None and self.down.add_into(act, residual):
+            return None
         return self.down(act)
 
 

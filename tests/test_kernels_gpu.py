@@ -291,3 +291,49 @@ def test_temperature_sampling_matches_plain_draw(top_p, V):
     perm = torch.randperm(R, generator=g)
     o.sample(logits[perm].to(DEV), out2, temperature, top_p, seed, seq_ids[perm].to(DEV), counters[perm].clone().to(DEV))
     assert out2.cpu().tolist() == [got[i] for i in perm.tolist()]
+
+
+# ------------------------------------------------------------------------------------------ skinny GEMM
+@pytest.mark.parametrize("batch", [1, 3, 8, 9, 16, 27, 32])
+@pytest.mark.parametrize("N,K", [(96, 64), (3072, 2048), (384, 96), (2048, 8192)])
+def test_gemm_skinny_epilogues(batch, N, K):
+    o = ops()
+    g = torch.Generator().manual_seed(batch * 1000 + N)
+    x = torch.randn(batch, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    ref = x.double() @ w.double().T                       # exact product of the bfloat16 values
+    assert o.gemm_skinny_ok(batch, N, K)
+    xd, wd = x.to(DEV), w.to(DEV)
+    out32 = torch.full((batch, N), float("nan"), dtype=torch.float32, device=DEV)
+    o.gemm_skinny(xd, wd, out32, o.SKINNY_STORE_F32)
+    assert torch.allclose(out32.cpu().double(), ref, atol=2e-4, rtol=1e-4), float((out32.cpu().double() - ref).abs().max())
+    out16 = torch.empty((batch, N), dtype=torch.bfloat16, device=DEV)
+    o.gemm_skinny(xd, wd, out16, o.SKINNY_STORE_BF16)
+    assert torch.equal(out16.cpu(), out32.cpu().to(torch.bfloat16))           # one rounding of the same sums
+    h = torch.randn(batch, N, generator=g)
+    hd_ = h.clone().to(DEV)
+    o.gemm_skinny(xd, wd, hd_, o.SKINNY_ADD_F32)
+    assert torch.allclose(hd_.cpu(), h + out32.cpu(), atol=1e-6)
+    # gate/up pairing: the weight is [gate rows; up rows]
+    ff = N // 2
+    if ff % 8 == 0:
+        act = torch.empty((batch, ff), dtype=torch.bfloat16, device=DEV)
+        o.gemm_skinny(xd, wd, act, o.SKINNY_SWIGLU)
+        gate, up = ref[:, :ff], ref[:, ff:]
+        want = gate * torch.sigmoid(gate) * up
+        assert torch.allclose(act.cpu().double(), want, atol=2e-2, rtol=2e-2)
+    # rows do not depend on their neighbours in the batch
+    if batch > 1:
+        one = torch.empty((1, N), dtype=torch.float32, device=DEV)
+        o.gemm_skinny(xd[batch // 2:batch // 2 + 1].contiguous(), wd, one, o.SKINNY_STORE_F32)
+        assert torch.equal(one[0].cpu(), out32[batch // 2].cpu())
+
+
+def test_gemm_skinny_refuses_other_shapes():
+    o = ops()
+    assert not o.gemm_skinny_ok(33, 64, 64) and not o.gemm_skinny_ok(4, 60, 64) and not o.gemm_skinny_ok(4, 64, 48)
+    assert not o.gemm_skinny_ok(4, 24, 64, o.SKINNY_SWIGLU) and o.gemm_skinny_ok(4, 48, 64, o.SKINNY_SWIGLU)
+    x = torch.zeros(4, 48, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(64, 48, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(Exception, match="not supported"):
+        o.gemm_skinny(x, w, torch.zeros(4, 64, dtype=torch.bfloat16, device=DEV), o.SKINNY_STORE_BF16)

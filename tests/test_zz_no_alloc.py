@@ -56,12 +56,15 @@ def test_no_alloc_matches_ordinary_entry_point_twice(dtype):
         ops.attention_decode(q, k, v, want, slots, kvlen, bt, 64, n_q, n_kv, hd, hd ** -0.5, 0, run_len, n_runs)
         got = torch.full_like(q, float("nan"))
         stream = torch.cuda.current_stream().cuda_stream
-        before = torch.cuda.memory_allocated()
+        torch.cuda.synchronize()
+        allocs_before = torch.cuda.memory_stats()["allocation.all.allocated"]
+        free_before = torch.cuda.mem_get_info()[0]
         rc = fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), got.data_ptr(), slots.data_ptr(), kvlen.data_ptr(),
                 bt.data_ptr(), bt.shape[1], 64, len(lens), n_q, n_kv, hd, hd ** -0.5, 0, run_len, n_runs, code, stream)
         assert rc == 0, rc
-        assert torch.cuda.memory_allocated() == before
         torch.cuda.synchronize()
+        assert torch.cuda.memory_stats()["allocation.all.allocated"] == allocs_before    # nothing through torch
+        assert torch.cuda.mem_get_info()[0] >= free_before                               # nothing from the driver
         tol = 2e-5 if dtype == torch.float32 else 3e-2
         assert torch.allclose(got.float(), want.float(), atol=tol), float((got.float() - want.float()).abs().max())
 
