@@ -1,0 +1,199 @@
+// Inline-PTX building blocks for the Blackwell (sm_100a) tensor-core kernels of this library:
+// mbarriers with BOUNDED waits, TMA tile loads (cp.async.bulk.tensor, never multicast), TMEM
+// allocation, tcgen05.mma with shared-memory operand descriptors, tcgen05.ld, and the host
+// side that encodes TMA tensor maps through the driver entry point (no link against libcuda).
+//
+// Shared-memory operand layout used everywhere here: rows of exactly 128 bytes (64 bfloat16),
+// 128-byte swizzle (the 16-byte chunk index of a row is XORed with row % 8), tiles aligned to
+// 1024 bytes. A TMA box of {64 elements, R rows} with CU_TENSOR_MAP_SWIZZLE_128B writes exactly
+// this layout; so does `swizzle128_offset` for threads that write an operand themselves.
+#pragma once
+#include "common.cuh"
+#include <cuda.h>
+
+namespace llmie {
+namespace tc {
+
+// status codes a kernel leaves in its status word when a bounded wait gives up
+constexpr int kStatusOk = 0;
+constexpr int kStatusTimeoutFull = 1;     // waiting for a TMA load
+constexpr int kStatusTimeoutEmpty = 2;    // waiting for the MMAs to release a stage
+constexpr int kStatusTimeoutMma = 3;      // waiting for accumulators
+constexpr unsigned kSpinLimit = 1u << 22; // polls (with back-off) before a wait gives up: well under a second
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// ------------------------------------------------------------------------------------------ mbarrier
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Waits for the phase with the given parity to complete. Gives up after kSpinLimit polls and
+// returns false; the caller then records a status and winds the kernel down. `abort` (shared
+// memory) lets one role's failure end the others' waits promptly.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
+  for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
+    if (mbar_test(bar, parity)) return true;
+    if (spin > 64) {
+      __nanosleep(spin > 4096 ? 256 : 32);
+      if (*abort) return false;
+    }
+  }
+  return false;
+}
+
+// ------------------------------------------------------------------------------------------ TMA
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
+}
+// 2-D tile load: x is the coordinate along the contiguous dimension (x * element size must be a
+// multiple of 16 bytes), y the row. Completion is signalled on `bar` as transaction bytes.
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+// make generic-proxy writes to shared memory visible to the async proxy (TMA, tcgen05.mma)
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// byte offset of element chunk (16 bytes) `chunk` of row `row` in a 128-byte-row, 128B-swizzled tile
+__device__ __forceinline__ uint32_t swizzle128_offset(int row, int chunk) {
+  return (uint32_t)row * 128u + (uint32_t)((chunk ^ (row & 7)) << 4);
+}
+
+// ------------------------------------------------------------------------------------------ TMEM
+// Whole-warp calls. n_cols: a power of two in [32, 512].
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t n_cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)), "r"(n_cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t n_cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(n_cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp gets lane (base lane + i).
+// A warp may only touch the TMEM lanes 32 * (warp id % 4) .. + 31.
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ------------------------------------------------------------------------------------------ MMA
+// Shared-memory matrix descriptor, 128B swizzle. K-major operand (rows of the tile are M or N,
+// 64 elements of K per 128-byte row): `stride_bytes` is the distance between groups of 8 rows
+// (1024 for a dense tile); the leading offset is unused. MN-major operand (each 128-byte row holds
+// 64 consecutive M/N elements of one k): `stride_bytes` is the distance between groups of 8 k
+// (1024 for a dense tile), `leading_bytes` the distance between 64-element blocks along M/N.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t leading_bytes, uint32_t stride_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((leading_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((stride_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;      // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;      // layout type: 128-byte swizzle
+  return d;
+}
+// Instruction descriptor for kind::f16 with bfloat16 inputs and float32 accumulation.
+// a_mn / b_mn: 1 when that operand is MN-major in shared memory, 0 when K-major.
+__host__ __device__ constexpr uint32_t make_instr_desc_bf16(int m, int n, int a_mn, int b_mn) {
+  return (1u << 4)                       // accumulator format: float32
+         | (1u << 7) | (1u << 10)        // A and B: bfloat16
+         | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16)
+         | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+// D[tmem] (+)= A[smem] * B[smem]; one thread issues. accumulate == 0 overwrites D.
+__device__ __forceinline__ void mma_bf16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The mbarrier receives one arrival when every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+// ------------------------------------------------------------------------------------------ host: tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// Map of a row-major bfloat16 matrix [rows, cols] (row pitch `pitch_elems`), read in boxes of
+// {64 columns, box_rows rows} with 128-byte swizzle; elements outside the matrix read as zero.
+// Returns 0 on success. base must be 16-byte aligned and the pitch a multiple of 8 elements.
+static inline int make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                                    uint64_t pitch_elems, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return LLMIE_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) || (pitch_elems % 8) || box_rows == 0 || box_rows > 256)
+    return LLMIE_ERR_ALIGNMENT;
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstride[1] = {pitch_elems * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? LLMIE_OK : LLMIE_ERR_BAD_ARG;
+}
+
+}  // namespace tc
+}  // namespace llmie

@@ -33,6 +33,7 @@ FAMILIES: Dict[str, tuple] = {
     "attention_decode": ("attention_decode.cu", [], []),
     "gemm_simt": ("gemm_simt.cu", [], []),
     "gemm_skinny": ("gemm_skinny.cu", [], []),
+    "gemm_tc": ("gemm_tc.cu", [], []),
     "sampling": ("sampling.cu", [], []),
 }
 
@@ -140,6 +141,14 @@ def _compile(family: str, out_path: str, verbose: bool) -> None:
             pass
         raise KernelBuildError(f"nvcc failed for kernel family '{family}':\n{' '.join(cmd)}\n{out}")
     os.replace(tmp, out_path)
+    # objects of older versions of this family's source are never loaded again: drop them
+    folder = os.path.dirname(out_path)
+    for name in os.listdir(folder):
+        if name.startswith(family + "-") and name.endswith(".so") and os.path.join(folder, name) != out_path:
+            try:
+                os.remove(os.path.join(folder, name))
+            except OSError:
+                pass
     if verbose and out.strip():
         print(out, file=sys.stderr)
     print(f"[llm_infer_engine_b200] built '{family}' in {time.time() - t0:.1f}s -> {out_path}", file=sys.stderr, flush=True)

@@ -283,6 +283,45 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
     return out
 
 
+_tc_status = {}
+_TC_STATUS_TEXT = {1: "a TMA load did not arrive", 2: "the tensor cores did not release a stage",
+                   3: "the accumulators were not completed"}
+
+
+def tc_status_word(device) -> torch.Tensor:
+    """One int32 per device that the tensor-core kernels set when a bounded wait gives up."""
+    key = torch.device(device).index or 0
+    t = _tc_status.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _tc_status[key] = t
+    return t
+
+
+def check_tc_status(device) -> None:
+    """Reads the status word (this synchronises) and raises if a tensor-core kernel gave up a wait."""
+    t = tc_status_word(device)
+    code = int(t.item())
+    if code:
+        t.zero_()
+        raise KernelError(f"a tensor-core kernel timed out: {_TC_STATUS_TEXT.get(code, code)}")
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ w[N, K]^T on the tcgen05 tensor cores; a, w bfloat16, out bfloat16 or float32."""
+    M, K = a.shape
+    N = w.shape[0]
+    _need(a, "a", torch.bfloat16)
+    _need(w, "w", torch.bfloat16, (N, K))
+    _need(out, "out", None, (M, N))
+    if K % 8 or N % 8:
+        raise KernelError(f"gemm_tc: K ({K}) and N ({N}) must be multiples of 8")
+    f = _fn("gemm_tc", "llmie_gemm_tc", [_c_void_p] * 3 + [_c_int] * 5 + [_c_void_p, _c_void_p])
+    _check(f(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, N, _dt(out, "out"),
+             tc_status_word(a.device).data_ptr(), _stream()), "gemm_tc")
+    return out
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """Greedy token per row of float32 logits [R, V] (lowest index wins a tie), many blocks per row."""
     R, V = logits.shape

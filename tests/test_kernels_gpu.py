@@ -337,3 +337,23 @@ def test_gemm_skinny_refuses_other_shapes():
     w = torch.zeros(64, 48, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(Exception, match="not supported"):
         o.gemm_skinny(x, w, torch.zeros(4, 64, dtype=torch.bfloat16, device=DEV), o.SKINNY_STORE_BF16)
+
+
+# ------------------------------------------------------------------------------------------ tcgen05 GEMM
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 128, 256), (256, 384, 2048), (100, 200, 72), (2048, 3072, 2048),
+                                   (1, 128, 64), (333, 1000, 520)])
+def test_gemm_tc(M, N, K):
+    o = ops()
+    g = torch.Generator().manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    ref = a.double() @ w.double().T
+    out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    o.gemm_tc(a.to(DEV), w.to(DEV), out32)
+    o.check_tc_status(DEV)
+    err = float((out32.cpu().double() - ref).abs().max())
+    assert err < 5e-4, err
+    out16 = torch.empty((M, N), dtype=torch.bfloat16, device=DEV)
+    o.gemm_tc(a.to(DEV), w.to(DEV), out16)
+    o.check_tc_status(DEV)
+    assert torch.equal(out16.cpu(), out32.cpu().to(torch.bfloat16))
