@@ -1,0 +1,361 @@
+// Causal attention for prompts on the 5th-generation tensor cores: tcgen05.mma with TMEM
+// accumulators, operands brought in by TMA straight from the paged KV cache.
+//
+// The math is the reference's prefill kernel (src/flash_attn.py:42-82): scores q.k / sqrt(hd),
+// causal mask, online softmax with float32 running max / sum, probabilities rounded to bfloat16
+// for the product with V (:72), output accumulated in float32 and divided by the sum at the end
+// (:82). Unlike the reference, K and V are never expanded to the query heads (:92-94): query head
+// h simply reads key/value head h / (Hq / Hkv) from the cache, and a sequence may start at any
+// position (the reference's mask is only right at position 0).
+//
+// One block = 128 consecutive query tokens of one sequence and one query head, 192 threads:
+//   warp 0      TMA producer: the Q tile once, then for every tile of 128 keys the two cache pages
+//               of K and of V ([64 keys, hd] each) into a ring of stages
+//   warp 1      owns TMEM (512 columns: two score buffers of 128, one P.V buffer of hd); one lane
+//               issues S = Q K^T for the NEXT key tile, then O_j = P_j V_j for the current one
+//   warps 2..5  softmax, one query row per thread: read S from TMEM (tcgen05.ld), mask, running
+//               max and sum, write P as bfloat16 into shared memory in the tensor core's swizzled
+//               operand layout, then add the P.V tile to the output kept in registers
+// V is used as an MN-major B operand (rows of the cache are keys, i.e. the K dimension of P.V),
+// so nothing is transposed. Every barrier wait is bounded (tcgen05.cuh).
+#include "tcgen05.cuh"
+#include <math.h>
+
+namespace llmie {
+using namespace tc;
+
+constexpr int kQTile = 128;       // query rows per block
+constexpr int kKTile = 128;       // keys per step (two cache pages of 64)
+constexpr int kAttnThreads = 192;
+constexpr int kSubTileBytes = 128 * 128;   // [128 rows x 64 bf16], 16 KB
+
+template <int HD> struct AttnCfg {
+  static constexpr int kSub = HD / 64;                       // 64-wide blocks of the head dimension
+  static constexpr int kKvStages = HD == 64 ? 3 : 2;
+  static constexpr int kQBytes = kSub * kSubTileBytes;
+  static constexpr int kKvBytes = kSub * kSubTileBytes;      // one K (or V) tile of 128 keys
+  static constexpr int kPBytes = 2 * kSubTileBytes;          // P: [128 rows x 128 keys] bf16
+  static constexpr int kSmem = kQBytes + 2 * kKvStages * kKvBytes + kPBytes + 1024;
+};
+
+struct AttnShared {
+  uint64_t q_full;
+  uint64_t k_full[3], v_full[3], kv_empty[3];
+  uint64_t s_full[2], s_free[2];
+  uint64_t p_ready, pv_full;
+  uint32_t tmem_base;
+  int abort;
+};
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                            const int* __restrict__ cu_q, const int* __restrict__ seq_slot,
+                            const int* __restrict__ seq_start, const int* __restrict__ block_table, int max_pages,
+                            int scratch_page, int n_q, int n_kv, float scale, int window, int* __restrict__ status) {
+  using Cfg = AttnCfg<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ AttnShared sh;
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* q_smem = base;
+  uint8_t* k_smem = q_smem + Cfg::kQBytes;
+  uint8_t* v_smem = k_smem + Cfg::kKvStages * Cfg::kKvBytes;
+  uint8_t* p_smem = v_smem + Cfg::kKvStages * Cfg::kKvBytes;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seq = blockIdx.z, head = blockIdx.y;
+  const int q_begin = cu_q[seq], q_len = cu_q[seq + 1] - q_begin;
+  const int t0 = blockIdx.x * kQTile;
+  if (t0 >= q_len) return;                         // uniform for the block: nothing was set up yet
+  const int start = seq_start[seq];                // tokens the sequence held before this step
+  const int hk = head / (n_q / n_kv);
+  const int rows_here = min(kQTile, q_len - t0);
+  // keys this tile of queries may see: [first_key, last_key]
+  const int last_key = start + t0 + rows_here - 1;
+  const int first_key = (window > 0 && start + t0 - window + 1 > 0) ? start + t0 - window + 1 : 0;
+  const int tile_lo = first_key / kKTile, tile_hi = last_key / kKTile;
+  const int n_tiles = tile_hi - tile_lo + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&sh.q_full, 1);
+    for (int s = 0; s < 3; ++s) {
+      mbar_init(&sh.k_full[s], 1);
+      mbar_init(&sh.v_full[s], 1);
+      mbar_init(&sh.kv_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sh.s_full[b], 1);
+      mbar_init(&sh.s_free[b], 128);
+    }
+    mbar_init(&sh.p_ready, 128);
+    mbar_init(&sh.pv_full, 1);
+    sh.abort = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sh.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = sh.tmem_base;
+  volatile int* abort = &sh.abort;
+#define LLMIE_FAIL(code) do { if (!*abort) { *abort = 1; atomicExch(status, (code)); } } while (0)
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      tma_prefetch_desc(&map_q);
+      tma_prefetch_desc(&map_k);
+      tma_prefetch_desc(&map_v);
+      mbar_arrive_expect_tx(&sh.q_full, Cfg::kQBytes);
+      for (int sub = 0; sub < Cfg::kSub; ++sub)
+        tma_load_2d(q_smem + sub * kSubTileBytes, &map_q, head * HD + sub * 64, q_begin + t0, &sh.q_full);
+      const int* pages = block_table + (size_t)seq_slot[seq] * max_pages;
+      int issued = 0;
+      for (int jt = 0; jt < n_tiles; ++jt) {
+        const int st = jt % Cfg::kKvStages;
+        if (jt >= Cfg::kKvStages && !mbar_wait(&sh.kv_empty[st], ((jt / Cfg::kKvStages) - 1) & 1, abort)) {
+          LLMIE_FAIL(kStatusTimeoutEmpty);
+          break;
+        }
+        const int lp = (tile_lo + jt) * 2;         // logical pages of this key tile
+        const int last_page = last_key / 64;       // pages beyond the sequence's last key are not mapped
+        const int pg0 = pages[lp];
+        const int pg1 = (lp + 1 <= last_page && lp + 1 < max_pages) ? pages[lp + 1] : scratch_page;
+        uint8_t* kd = k_smem + st * Cfg::kKvBytes;
+        uint8_t* vd = v_smem + st * Cfg::kKvBytes;
+        mbar_arrive_expect_tx(&sh.k_full[st], Cfg::kKvBytes);
+        for (int sub = 0; sub < Cfg::kSub; ++sub) {
+          tma_load_2d(kd + sub * kSubTileBytes, &map_k, sub * 64, (pg0 * n_kv + hk) * 64, &sh.k_full[st]);
+          tma_load_2d(kd + sub * kSubTileBytes + 8192, &map_k, sub * 64, (pg1 * n_kv + hk) * 64, &sh.k_full[st]);
+        }
+        mbar_arrive_expect_tx(&sh.v_full[st], Cfg::kKvBytes);
+        for (int sub = 0; sub < Cfg::kSub; ++sub) {
+          tma_load_2d(vd + sub * kSubTileBytes, &map_v, sub * 64, (pg0 * n_kv + hk) * 64, &sh.v_full[st]);
+          tma_load_2d(vd + sub * kSubTileBytes + 8192, &map_v, sub * 64, (pg1 * n_kv + hk) * 64, &sh.v_full[st]);
+        }
+        issued = jt + 1;
+      }
+      if (*abort) {   // let copies that are still in flight land before the block gives its memory up
+        for (int jt = max(0, issued - Cfg::kKvStages); jt < issued; ++jt) {
+          const int st = jt % Cfg::kKvStages;
+          const uint32_t par = (jt / Cfg::kKvStages) & 1;
+          for (unsigned spin = 0; spin < (1u << 16) && !(mbar_test(&sh.k_full[st], par) && mbar_test(&sh.v_full[st], par)); ++spin)
+            __nanosleep(64);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc_s = make_instr_desc_bf16(kQTile, kKTile, 0, 0);
+      constexpr uint32_t idesc_pv = make_instr_desc_bf16(kQTile, HD, 0, 1);     // V is MN-major
+      const uint32_t q_addr = smem_u32(q_smem), p_addr = smem_u32(p_smem);
+      bool ok = mbar_wait(&sh.q_full, 0, abort);
+      if (!ok) LLMIE_FAIL(kStatusTimeoutFull);
+      auto issue_scores = [&](int jt) -> bool {
+        const int st = jt % Cfg::kKvStages, b = jt & 1;
+        if (!mbar_wait(&sh.k_full[st], (jt / Cfg::kKvStages) & 1, abort)) { LLMIE_FAIL(kStatusTimeoutFull); return false; }
+        if (jt >= 2 && !mbar_wait(&sh.s_free[b], ((jt >> 1) - 1) & 1, abort)) { LLMIE_FAIL(kStatusTimeoutMma); return false; }
+        tc_fence_after_sync();
+        const uint32_t k_addr = smem_u32(k_smem + st * Cfg::kKvBytes);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * kSubTileBytes + (kk & 3) * 32;
+          mma_bf16_ss(tmem + b * 128, make_smem_desc(q_addr + off, 16, 1024), make_smem_desc(k_addr + off, 16, 1024),
+                      idesc_s, kk > 0 ? 1u : 0u);
+        }
+        mma_commit(&sh.s_full[b]);
+        return true;
+      };
+      if (ok) ok = issue_scores(0);
+      for (int jt = 0; ok && jt < n_tiles; ++jt) {
+        if (jt + 1 < n_tiles && !issue_scores(jt + 1)) break;
+        const int st = jt % Cfg::kKvStages;
+        if (!mbar_wait(&sh.p_ready, jt & 1, abort)) { LLMIE_FAIL(kStatusTimeoutMma); break; }
+        if (!mbar_wait(&sh.v_full[st], (jt / Cfg::kKvStages) & 1, abort)) { LLMIE_FAIL(kStatusTimeoutFull); break; }
+        tc_fence_after_sync();
+        const uint32_t v_addr = smem_u32(v_smem + st * Cfg::kKvBytes);
+#pragma unroll
+        for (int kk = 0; kk < kKTile / 16; ++kk) {
+          // A = P, K-major: 16 keys = 32 bytes inside a 64-key sub-tile. B = V, MN-major: 16 keys = 16 rows.
+          const uint64_t dp = make_smem_desc(p_addr + (kk >> 2) * kSubTileBytes + (kk & 3) * 32, 16, 1024);
+          const uint64_t dv = make_smem_desc(v_addr + kk * 2048, kSubTileBytes, 1024);
+          mma_bf16_ss(tmem + 256, dp, dv, idesc_pv, kk > 0 ? 1u : 0u);
+        }
+        mma_commit(&sh.pv_full);
+        mma_commit(&sh.kv_empty[st]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax, one query row per thread
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;                   // row of the tile = TMEM lane
+    const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+    const int qpos = start + t0 + r;                     // absolute position of this query
+    const int lo = (window > 0 && qpos - window + 1 > 0) ? qpos - window + 1 : 0;
+    const float sl2 = scale * 1.4426950408889634f;       // exp(x * scale) = exp2(x * scale * log2 e)
+    float o[HD];
+#pragma unroll
+    for (int d = 0; d < HD; ++d) o[d] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int jt = 0; jt < n_tiles; ++jt) {
+      const int b = jt & 1;
+      if (!mbar_wait(&sh.s_full[b], (jt >> 1) & 1, abort)) { LLMIE_FAIL(kStatusTimeoutMma); ok = false; break; }
+      tc_fence_after_sync();
+      const int kbase = (tile_lo + jt) * kKTile;
+      const bool edge = (kbase + kKTile - 1 > start + t0) || (window > 0 && kbase < start + t0 + kQTile - window);
+      // pass 1: the row's maximum over the keys it may see
+      float m_tile = -INFINITY;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kKTile; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(lane_addr + b * 128 + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(v[i]);
+          if (edge) {
+            const int key = kbase + c0 + i;
+            if (key > qpos || key < lo) s = -INFINITY;
+          }
+          m_tile = fmaxf(m_tile, s);
+        }
+      }
+      const float m_new = fmaxf(m_run, m_tile);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;      // a row that has seen no key yet
+      const float alpha = exp2f((m_run - m_use) * sl2);            // 0 while m_run is -inf
+      const float m_scaled = m_use * sl2;
+      // pass 2: probabilities, their sum, and P in bfloat16 into the swizzled operand tile
+      float l_tile = 0.f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kKTile; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(lane_addr + b * 128 + c0, v);
+        tmem_ld_wait();
+        float p[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(v[i]);
+          if (edge) {
+            const int key = kbase + c0 + i;
+            if (key > qpos || key < lo) s = -INFINITY;
+          }
+          p[i] = exp2f(fmaf(s, sl2, -m_scaled));
+          l_tile += p[i];
+        }
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {                 // four 16-byte chunks of 8 keys
+          const int chunk = (c0 >> 3) + ch;              // 0..15 within the 128 keys
+          uint4 w;
+          w.x = pack_bf16(p[ch * 8 + 0], p[ch * 8 + 1]);
+          w.y = pack_bf16(p[ch * 8 + 2], p[ch * 8 + 3]);
+          w.z = pack_bf16(p[ch * 8 + 4], p[ch * 8 + 5]);
+          w.w = pack_bf16(p[ch * 8 + 6], p[ch * 8 + 7]);
+          *reinterpret_cast<uint4*>(p_smem + (chunk >> 3) * kSubTileBytes + swizzle128_offset(r, chunk & 7)) = w;
+        }
+      }
+      tc_fence_before_sync();                  // our TMEM reads of S are done before the barrier is passed
+      mbar_arrive(&sh.s_free[b]);
+      fence_proxy_async_smem();                // P is visible to the tensor core's reads
+      mbar_arrive(&sh.p_ready);
+      // the P.V tile for these keys
+      if (!mbar_wait(&sh.pv_full, jt & 1, abort)) { LLMIE_FAIL(kStatusTimeoutMma); ok = false; break; }
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c0 = 0; c0 < HD; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(lane_addr + 256 + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha, __uint_as_float(v[i]));
+      }
+      l_run = fmaf(l_run, alpha, l_tile);
+      m_run = m_new;
+      tc_fence_before_sync();                  // ordered before the next arrival on p_ready
+    }
+    if (ok && r < rows_here) {
+      const float inv = 1.f / l_run;
+      __nv_bfloat16* dst = out + ((size_t)(q_begin + t0 + r) * n_q + head) * HD;
+#pragma unroll
+      for (int d = 0; d < HD; d += 8) {
+        float v8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v8[e] = o[d + e] * inv;
+        store8(dst + d, v8);
+      }
+    }
+  }
+#undef LLMIE_FAIL
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+template <int HD>
+static int launch_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* cu_q,
+                          const int* seq_slot, const int* seq_start, const int* block_table, int max_pages,
+                          int n_pages_total, int n_tokens, int n_seqs, int max_q_len, int n_q, int n_kv, float scale,
+                          int window, int* status, cudaStream_t stream) {
+  using Cfg = AttnCfg<HD>;
+  CUtensorMap map_q, map_k, map_v;
+  int rc = tc::make_tmap_bf16_2d(&map_q, q, (uint64_t)n_tokens, (uint64_t)n_q * HD, (uint64_t)n_q * HD, kQTile);
+  if (rc != LLMIE_OK) return rc;
+  const uint64_t kv_rows = (uint64_t)n_pages_total * n_kv * 64;
+  rc = tc::make_tmap_bf16_2d(&map_k, k_cache, kv_rows, HD, HD, 64);
+  if (rc != LLMIE_OK) return rc;
+  rc = tc::make_tmap_bf16_2d(&map_v, v_cache, kv_rows, HD, HD, 64);
+  if (rc != LLMIE_OK) return rc;
+  cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Cfg::kSmem);
+  if (e != cudaSuccess) return (int)e;
+  dim3 grid((max_q_len + kQTile - 1) / kQTile, n_q, n_seqs);
+  attention_prefill_tc_kernel<HD><<<grid, kAttnThreads, Cfg::kSmem, stream>>>(
+      map_q, map_k, map_v, (__nv_bfloat16*)out, cu_q, seq_slot, seq_start, block_table, max_pages, n_pages_total - 1,
+      n_q, n_kv, scale, window, status);
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+}  // namespace llmie
+
+using namespace llmie;
+
+extern "C" int llmie_attention_prefill_tc_supported(int hd, int page_size) {
+  return ((hd == 64 || hd == 128) && page_size == 64) ? 1 : 0;
+}
+
+// q, out: bfloat16 [n_tokens, n_q * hd], sequences packed one after another (cu_q [n_seqs + 1]).
+// caches: bfloat16 [n_pages_total, n_kv, 64, hd]; the LAST page (n_pages_total - 1) is a scratch
+// page that may be read for key positions nobody holds. seq_start[i]: tokens sequence i held
+// before this step (its new keys are already in the cache). max_q_len: longest new run, for the grid.
+extern "C" int llmie_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                          const int* cu_q, const int* seq_slot, const int* seq_start,
+                                          const int* block_table, int max_pages, int n_pages_total, int n_tokens,
+                                          int n_seqs, int max_q_len, int n_q, int n_kv, int hd, float scale, int window,
+                                          int* status, cudaStream_t stream) {
+  if (n_tokens < 0 || n_seqs < 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv || max_pages <= 0 || n_pages_total <= 0)
+    return LLMIE_ERR_BAD_ARG;
+  if (!aligned16(q) || !aligned16(out) || !aligned16(k_cache) || !aligned16(v_cache)) return LLMIE_ERR_ALIGNMENT;
+  if (n_tokens == 0 || n_seqs == 0 || max_q_len <= 0) return LLMIE_OK;
+  if (n_seqs > 65535 || n_q > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (hd == 64)
+    return launch_prefill<64>(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, block_table, max_pages,
+                              n_pages_total, n_tokens, n_seqs, max_q_len, n_q, n_kv, scale, window, status, stream);
+  if (hd == 128)
+    return launch_prefill<128>(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, block_table, max_pages,
+                               n_pages_total, n_tokens, n_seqs, max_q_len, n_q, n_kv, scale, window, status, stream);
+  return LLMIE_ERR_UNSUPPORTED_SIZE;
+}

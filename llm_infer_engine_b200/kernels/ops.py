@@ -307,6 +307,37 @@ def check_tc_status(device) -> None:
         raise KernelError(f"a tensor-core kernel timed out: {_TC_STATUS_TEXT.get(code, code)}")
 
 
+def attention_prefill_tc_supported(head_dim: int, page_size: int, dtype: torch.dtype) -> bool:
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and page_size == 64
+
+
+def attention_prefill_tc(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, block_table, page_size: int,
+                         n_seqs: int, max_q_len: int, n_q: int, n_kv: int, head_dim: int, scale: float,
+                         window: int = 0):
+    """Causal attention for runs of new tokens on the tcgen05 tensor cores, K and V read from the
+    paged cache by TMA. q, out bfloat16 [T, n_q hd] with sequences packed (cu_q int32 [n + 1]);
+    seq_start int32 [n]: tokens each sequence held before this step. The caches' last page must be
+    a scratch page. head_dim 64 or 128, pages of 64."""
+    T = q.shape[0]
+    _need(q, "q", torch.bfloat16, (T, n_q * head_dim))
+    _need(out, "out", torch.bfloat16, (T, n_q * head_dim))
+    _need(k_cache, "k_cache", torch.bfloat16, (None, n_kv, page_size, head_dim))
+    _need(v_cache, "v_cache", torch.bfloat16, tuple(k_cache.shape))
+    for name, t in (("cu_q", cu_q), ("seq_slot", seq_slot), ("seq_start", seq_start), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    if not attention_prefill_tc_supported(head_dim, page_size, q.dtype):
+        raise KernelError(f"attention_prefill_tc: head_dim {head_dim} / page size {page_size} is not supported")
+    if cu_q.numel() < n_seqs + 1 or seq_slot.numel() < n_seqs or seq_start.numel() < n_seqs:
+        raise KernelError("attention_prefill_tc: a per-sequence array is shorter than n_seqs")
+    f = _fn("attention_prefill_tc", "llmie_attention_prefill_tc",
+            [_c_void_p] * 8 + [_c_int] * 8 + [_c_float, _c_int, _c_void_p, _c_void_p])
+    _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), cu_q.data_ptr(),
+             seq_slot.data_ptr(), seq_start.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+             k_cache.shape[0], T, n_seqs, max_q_len, n_q, n_kv, head_dim, float(scale), int(window),
+             tc_status_word(q.device).data_ptr(), _stream()), "attention_prefill_tc")
+    return out
+
+
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[M, N] = a[M, K] @ w[N, K]^T on the tcgen05 tensor cores; a, w bfloat16, out bfloat16 or float32."""
     M, K = a.shape

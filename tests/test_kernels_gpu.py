@@ -357,3 +357,56 @@ def test_gemm_tc(M, N, K):
     o.gemm_tc(a.to(DEV), w.to(DEV), out16)
     o.check_tc_status(DEV)
     assert torch.equal(out16.cpu(), out32.cpu().to(torch.bfloat16))
+
+
+# ------------------------------------------------------------------------------------------ tcgen05 prefill attention
+@pytest.mark.parametrize("n_q,n_kv,hd", [(4, 2, 64), (3, 1, 64), (8, 8, 64), (4, 1, 128), (6, 2, 128)])
+def test_attention_prefill_tc(n_q, n_kv, hd):
+    """Ragged runs of new tokens at nonzero start positions, across key tiles and cache pages,
+    against the plain formula and the plain kernel; with and without a window; a far key made
+    to dominate so that a lost tile cannot hide."""
+    o = ops()
+    dtype = torch.bfloat16
+    assert o.attention_prefill_tc_supported(hd, 64, dtype)
+    starts, news = [0, 70, 3, 200, 0, 130], [50, 9, 300, 129, 1, 128]
+    totals = [s + n for s, n in zip(starts, news)]
+    pg = Paged(totals, n_kv, hd, dtype, seed=hd + n_q)
+    T = sum(news)
+    g = torch.Generator().manual_seed(17)
+    q = torch.randn(T, n_q, hd, generator=g)
+    cu = [0]
+    for n in news:
+        cu.append(cu[-1] + n)
+    # needle: sequence 2 (303 keys, three key tiles): its last query looks hard at key 5
+    G = n_q // n_kv
+    qi = cu[3] - 1
+    qh = q[qi, ::G]
+    pg.dense_k[2][5] = (qh * (24.0 / ((qh * qh).sum(-1, keepdim=True) * hd ** -0.5))).to(dtype)
+    pg.dense_v[2][5] = 5.0
+    pg.fill()
+    k_dev, v_dev, bt = pg.dev()
+    # the kernel wants the last page to be readable scratch: Paged leaves spare pages, the last is unused
+    qd = q.to(dtype).reshape(T, n_q * hd).to(DEV)
+    slots = torch.tensor(pg.slots, dtype=torch.int32, device=DEV)
+    cu_dev = torch.tensor(cu, dtype=torch.int32, device=DEV)
+    st_dev = torch.tensor(starts, dtype=torch.int32, device=DEV)
+    tok_seq = torch.repeat_interleave(torch.arange(len(news)), torch.tensor(news)).int().to(DEV)
+    tok_pos = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, news)]).int().to(DEV)
+    for window in (0, 100):
+        out = torch.full((T, n_q * hd), float("nan"), dtype=dtype, device=DEV)
+        o.attention_prefill_tc(qd, k_dev, v_dev, out, cu_dev, slots, st_dev, bt, 64, len(news), max(news), n_q, n_kv, hd,
+                               hd ** -0.5, window)
+        o.check_tc_status(DEV)
+        plain_out = torch.empty_like(out)
+        o.attention_paged(qd, k_dev, v_dev, plain_out, tok_pos, tok_seq, slots, bt, 64, n_q, n_kv, hd, hd ** -0.5, window)
+        got = out.float().cpu().view(T, n_q, hd)
+        assert not torch.isnan(got).any()
+        for i, n in enumerate(news):
+            ref = ref_attention(qd.float().cpu().view(T, n_q, hd)[cu[i]:cu[i + 1]], pg.dense_k[i].float(),
+                                pg.dense_v[i].float(), list(range(starts[i], starts[i] + n)), hd ** -0.5, window)
+            # outputs are bfloat16: one unit in the last place is 2^-8 of the value's magnitude
+            assert torch.allclose(got[cu[i]:cu[i + 1]], ref, atol=2e-2, rtol=1.6e-2), \
+                (window, i, float((got[cu[i]:cu[i + 1]] - ref).abs().max()))
+        assert torch.allclose(out.float(), plain_out.float(), atol=2e-2, rtol=1.6e-2)
+        if window == 0:
+            assert float(got[qi, ::G].mean()) > 4.5
