@@ -18,6 +18,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 TINY = {
     "a": dict(cfg=plain.TINY_A, seed=0, std=0.02, norm_range=None),
     "b": dict(cfg=plain.TINY_B, seed=1, std=0.03, norm_range=(0.8, 1.2)),
+    # head size 64 (hidden != heads * head_dim), three query heads per KV head, longer sequences
+    "c": dict(cfg=plain.TINY_C, seed=2, std=0.05, norm_range=(0.9, 1.1)),
 }
 
 _folders = {}

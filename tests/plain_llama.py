@@ -205,6 +205,16 @@ TINY_B = {
     "max_position_embeddings": 256, "hidden_act": "silu", "attention_bias": False, "mlp_bias": False,
     "bos_token_id": 1, "eos_token_id": [2, 3], "torch_dtype": "bfloat16",
 }
+TINY_C = {   # head size 64: the bfloat16 engine's tensor-core attention takes this one
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 160, "num_attention_heads": 6, "num_key_value_heads": 2,
+    "head_dim": 64, "intermediate_size": 224, "vocab_size": 512, "rope_theta": 50000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 128},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+    "max_position_embeddings": 1024, "hidden_act": "silu", "attention_bias": False, "mlp_bias": False,
+    "bos_token_id": 1, "eos_token_id": 2, "torch_dtype": "bfloat16",
+}
 
 
 def tensor_shapes(cfg: dict) -> dict:

@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 # bfloat16: activations between kernels are rounded to 8 bits of mantissa; the bound is on the
 # logits' own scale and is the same for every way of cutting the work.
 TOL = {"float32": 2e-5, "bfloat16": 3e-2}
-LENGTHS = {"a": [5, 11, 17, 40, 64, 65, 100], "b": [1, 9, 33, 70, 128, 129, 200]}
+LENGTHS = {"a": [5, 11, 17, 40, 64, 65, 100], "b": [1, 9, 33, 70, 128, 129, 200], "c": [3, 127, 128, 129, 300, 700, 64]}
 
 _engines = {}
 
@@ -22,7 +22,7 @@ def engine_for(tag, dtype):
     from llm_infer_engine_b200 import Engine
     key = (tag, dtype)
     if key not in _engines:
-        _engines[key] = Engine(helpers.model_folder(tag), dtype=dtype, max_batch=8, max_tokens=64 * 24,
+        _engines[key] = Engine(helpers.model_folder(tag), dtype=dtype, max_batch=8, max_tokens=64 * 40,
                                cuda_graph=False)
     return _engines[key]
 
@@ -50,7 +50,7 @@ def check(got, want, tol, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("tag", ["a", "b"])
+@pytest.mark.parametrize("tag", ["a", "b", "c"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "batched"])
 def test_replay_matches_plain(tag, dtype, mode):
     requests = requests_for(tag)
@@ -64,6 +64,9 @@ def test_replay_matches_plain(tag, dtype, mode):
     engine = engine_for(tag, dtype)
     got = helpers.run_plan_engine(engine, steps)
     check(got, want, TOL[dtype], f"{tag}/{dtype}/{mode}")
+    if dtype == "bfloat16":
+        from llm_infer_engine_b200.kernels import ops
+        ops.check_tc_status("cuda")
     assert engine.cache.free_slots() == engine.cache.n_slots
     assert engine.cache.free_pages() == engine.cache.n_pages
 
