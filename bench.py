@@ -222,25 +222,27 @@ def run_ours(args):
     sampler.start()
     results = {}
     launches = 0
-    for batch in (args.batch, 1, 64):
+    batches = (args.batch, 1, 64) if args.only == "all" else ((args.batch,) if args.only == "decode" else ())
+    for batch in batches:
         if batch in results:
             continue
         sec, mean_ctx, n_launch = time_decode(engine, batch, args.steps, args.warmup, seed=10 + batch)
         results[batch] = (sec, mean_ctx)
         if batch == args.batch:
             launches = n_launch
-    prefill_s = time_prefill(engine, PREFILL_TOKENS, warmup=max(3, min(args.warmup, 5)), reps=5, seed=99)
-    e2e_tps, stats = e2e_decode(engine, args.batch, args.steps, seed=10 + args.batch)
+    prefill_s = None
+    if args.only in ("all", "prefill"):
+        prefill_s = time_prefill(engine, PREFILL_TOKENS, warmup=max(3, min(args.warmup, 5)),
+                                 reps=5 if args.only == "all" else 2, seed=99)
+    e2e_tps = None
+    if args.only == "all":
+        e2e_tps, stats = e2e_decode(engine, args.batch, args.steps, seed=10 + args.batch)
     sampler.stop()
 
-    sec, mean_ctx = results[args.batch]
-    value = args.batch * args.steps / sec
-    step_bytes = engine.weight_bytes_per_step() + engine.kv_bytes_per_token() * mean_ctx * args.batch
-    achieved = step_bytes / (sec / args.steps) / 1e9
     flops = prefill_flops(CONFIG_1B, n_layers, PREFILL_TOKENS)
     out = {
-        "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": round(sec / args.steps * 1e3, 4), "higher_is_better": True,
+        "metric": METRIC, "value": None, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), "
         "uniform-random token ids", "impl": "ours",
         "config": {
@@ -252,16 +254,26 @@ def run_ours(args):
             "tied_head": True, "cuda_graph": True, "sampling": "greedy",
             "l2": "weights 2.5 GB per step >> 126 MB L2, no flush needed", "peaks": pk["source"],
         },
-        "e2e": {"value": round(e2e_tps, 1), "unit": "tokens/s", "h2d_bytes_per_step": 4 * args.batch,
-                "d2h_bytes_per_step": 4 * args.batch},
         "gpu_launches": int(launches),
-        "prefill": {"value": round(PREFILL_TOKENS / prefill_s, 1), "tokens": PREFILL_TOKENS,
-                    "ms": round(prefill_s * 1e3, 3), "frac": round(flops / prefill_s / (pk["bf16_tflops"] * 1e12), 4)},
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4)},
-        "points": {f"decode_b{b}": round(b * args.steps / results[b][0], 1) for b in (1, 64)},
-        "clocks": sampler.summary(),
     }
+    if args.batch in results:
+        sec, mean_ctx = results[args.batch]
+        step_bytes = engine.weight_bytes_per_step() + engine.kv_bytes_per_token() * mean_ctx * args.batch
+        achieved = step_bytes / (sec / args.steps) / 1e9
+        out["value"] = round(args.batch * args.steps / sec, 1)
+        out["ms_per_step"] = round(sec / args.steps * 1e3, 4)
+        out["roofline"] = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                           "frac": round(achieved / pk["hbm_gbs"], 4)}
+    if e2e_tps is not None:
+        out["e2e"] = {"value": round(e2e_tps, 1), "unit": "tokens/s", "h2d_bytes_per_step": 4 * args.batch,
+                      "d2h_bytes_per_step": 4 * args.batch}
+    if prefill_s is not None:
+        out["prefill"] = {"value": round(PREFILL_TOKENS / prefill_s, 1), "tokens": PREFILL_TOKENS,
+                          "ms": round(prefill_s * 1e3, 3),
+                          "frac": round(flops / prefill_s / (pk["bf16_tflops"] * 1e12), 4)}
+    if 1 in results and 64 in results:
+        out["points"] = {f"decode_b{b}": round(b * args.steps / results[b][0], 1) for b in (1, 64)}
+    out["clocks"] = sampler.summary()
     print(json.dumps(out))
     return 0
 
@@ -282,6 +294,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0 = all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="measure only one part (for short profiler captures); the JSON line then lacks the rest")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
