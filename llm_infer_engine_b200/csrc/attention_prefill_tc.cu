@@ -10,9 +10,9 @@
 //
 // One block = 128 consecutive query tokens of one sequence and one query head, 192 threads:
 //   warp 0      TMA producer: the Q tile once, then for every tile of 128 keys the two cache pages
-//               of K and of V ([64 keys, hd] each) into a ring of stages
-//   warp 1      owns TMEM (512 columns: two score buffers of 128, one P.V buffer of hd); one lane
-//               issues S = Q K^T for the NEXT key tile, then O_j = P_j V_j for the current one
+//               of K and of V ([64 keys, hd] each) into their stages
+//   warp 1      owns TMEM (score buffer(s) of 128 columns, one P.V buffer of hd); one lane issues
+//               S = Q K^T for the NEXT key tile as soon as its buffer is free, then O_j = P_j V_j
 //   warps 2..5  softmax, one query row per thread: read S from TMEM (tcgen05.ld), mask, running
 //               max and sum, write P as bfloat16 into shared memory in the tensor core's swizzled
 //               operand layout, then add the P.V tile to the output kept in registers
@@ -31,16 +31,24 @@ constexpr int kSubTileBytes = 128 * 128;   // [128 rows x 64 bf16], 16 KB
 
 template <int HD> struct AttnCfg {
   static constexpr int kSub = HD / 64;                       // 64-wide blocks of the head dimension
-  static constexpr int kKvStages = HD == 64 ? 3 : 2;
+  // head size 64: two blocks share an SM (each 256 TMEM columns, 97 KB), so one block's softmax
+  // overlaps the other's MMAs; one score buffer and one V stage per block suffice.
+  // head size 128: one block per SM; two score buffers let S of the next key tile be computed
+  // while the softmax of the current one runs.
+  static constexpr int kSBufs = HD == 64 ? 1 : 2;
+  static constexpr int kKStages = 2;
+  static constexpr int kVStages = HD == 64 ? 1 : 2;
+  static constexpr int kTmemCols = HD == 64 ? 256 : 512;
+  static constexpr int kPvCol = kSBufs * 128;                // TMEM column of the P.V tile
   static constexpr int kQBytes = kSub * kSubTileBytes;
   static constexpr int kKvBytes = kSub * kSubTileBytes;      // one K (or V) tile of 128 keys
   static constexpr int kPBytes = 2 * kSubTileBytes;          // P: [128 rows x 128 keys] bf16
-  static constexpr int kSmem = kQBytes + 2 * kKvStages * kKvBytes + kPBytes + 1024;
+  static constexpr int kSmem = kQBytes + (kKStages + kVStages) * kKvBytes + kPBytes + 1024;
 };
 
 struct AttnShared {
   uint64_t q_full;
-  uint64_t k_full[3], v_full[3], kv_empty[3];
+  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
   uint64_t s_full[2], s_free[2];
   uint64_t p_ready, pv_full;
   uint32_t tmem_base;
@@ -53,7 +61,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 }
 
 template <int HD>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __launch_bounds__(kAttnThreads, (HD == 64 ? 2 : 1))
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                             const int* __restrict__ cu_q, const int* __restrict__ seq_slot,
@@ -65,8 +73,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* q_smem = base;
   uint8_t* k_smem = q_smem + Cfg::kQBytes;
-  uint8_t* v_smem = k_smem + Cfg::kKvStages * Cfg::kKvBytes;
-  uint8_t* p_smem = v_smem + Cfg::kKvStages * Cfg::kKvBytes;
+  uint8_t* v_smem = k_smem + Cfg::kKStages * Cfg::kKvBytes;
+  uint8_t* p_smem = v_smem + Cfg::kVStages * Cfg::kKvBytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seq = blockIdx.z, head = blockIdx.y;
@@ -84,10 +92,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
   if (threadIdx.x == 0) {
     mbar_init(&sh.q_full, 1);
-    for (int s = 0; s < 3; ++s) {
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&sh.k_full[s], 1);
+      mbar_init(&sh.k_empty[s], 1);
       mbar_init(&sh.v_full[s], 1);
-      mbar_init(&sh.kv_empty[s], 1);
+      mbar_init(&sh.v_empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sh.s_full[b], 1);
@@ -99,7 +108,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc(&sh.tmem_base, 512);
+    tmem_alloc(&sh.tmem_base, Cfg::kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -121,35 +130,40 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const int* pages = block_table + (size_t)seq_slot[seq] * max_pages;
       int issued = 0;
       for (int jt = 0; jt < n_tiles; ++jt) {
-        const int st = jt % Cfg::kKvStages;
-        if (jt >= Cfg::kKvStages && !mbar_wait(&sh.kv_empty[st], ((jt / Cfg::kKvStages) - 1) & 1, abort)) {
-          LLMIE_FAIL(kStatusTimeoutEmpty);
-          break;
-        }
+        const int ks = jt % Cfg::kKStages, vs = jt % Cfg::kVStages;
         const int lp = (tile_lo + jt) * 2;         // logical pages of this key tile
         const int last_page = last_key / 64;       // pages beyond the sequence's last key are not mapped
         const int pg0 = pages[lp];
         const int pg1 = (lp + 1 <= last_page && lp + 1 < max_pages) ? pages[lp + 1] : scratch_page;
-        uint8_t* kd = k_smem + st * Cfg::kKvBytes;
-        uint8_t* vd = v_smem + st * Cfg::kKvBytes;
-        mbar_arrive_expect_tx(&sh.k_full[st], Cfg::kKvBytes);
-        for (int sub = 0; sub < Cfg::kSub; ++sub) {
-          tma_load_2d(kd + sub * kSubTileBytes, &map_k, sub * 64, (pg0 * n_kv + hk) * 64, &sh.k_full[st]);
-          tma_load_2d(kd + sub * kSubTileBytes + 8192, &map_k, sub * 64, (pg1 * n_kv + hk) * 64, &sh.k_full[st]);
+        if (jt >= Cfg::kKStages && !mbar_wait(&sh.k_empty[ks], ((jt / Cfg::kKStages) - 1) & 1, abort)) {
+          LLMIE_FAIL(kStatusTimeoutEmpty);
+          break;
         }
-        mbar_arrive_expect_tx(&sh.v_full[st], Cfg::kKvBytes);
+        uint8_t* kd = k_smem + ks * Cfg::kKvBytes;
+        mbar_arrive_expect_tx(&sh.k_full[ks], Cfg::kKvBytes);
         for (int sub = 0; sub < Cfg::kSub; ++sub) {
-          tma_load_2d(vd + sub * kSubTileBytes, &map_v, sub * 64, (pg0 * n_kv + hk) * 64, &sh.v_full[st]);
-          tma_load_2d(vd + sub * kSubTileBytes + 8192, &map_v, sub * 64, (pg1 * n_kv + hk) * 64, &sh.v_full[st]);
+          tma_load_2d(kd + sub * kSubTileBytes, &map_k, sub * 64, (pg0 * n_kv + hk) * 64, &sh.k_full[ks]);
+          tma_load_2d(kd + sub * kSubTileBytes + 8192, &map_k, sub * 64, (pg1 * n_kv + hk) * 64, &sh.k_full[ks]);
+        }
+        if (jt >= Cfg::kVStages && !mbar_wait(&sh.v_empty[vs], ((jt / Cfg::kVStages) - 1) & 1, abort)) {
+          LLMIE_FAIL(kStatusTimeoutEmpty);
+          issued = jt + 1;                         // K of this tile is in flight
+          break;
+        }
+        uint8_t* vd = v_smem + vs * Cfg::kKvBytes;
+        mbar_arrive_expect_tx(&sh.v_full[vs], Cfg::kKvBytes);
+        for (int sub = 0; sub < Cfg::kSub; ++sub) {
+          tma_load_2d(vd + sub * kSubTileBytes, &map_v, sub * 64, (pg0 * n_kv + hk) * 64, &sh.v_full[vs]);
+          tma_load_2d(vd + sub * kSubTileBytes + 8192, &map_v, sub * 64, (pg1 * n_kv + hk) * 64, &sh.v_full[vs]);
         }
         issued = jt + 1;
       }
       if (*abort) {   // let copies that are still in flight land before the block gives its memory up
-        for (int jt = max(0, issued - Cfg::kKvStages); jt < issued; ++jt) {
-          const int st = jt % Cfg::kKvStages;
-          const uint32_t par = (jt / Cfg::kKvStages) & 1;
-          for (unsigned spin = 0; spin < (1u << 16) && !(mbar_test(&sh.k_full[st], par) && mbar_test(&sh.v_full[st], par)); ++spin)
-            __nanosleep(64);
+        for (int jt = max(0, issued - 2); jt < issued; ++jt) {
+          uint64_t* kb = &sh.k_full[jt % Cfg::kKStages];
+          uint64_t* vb = &sh.v_full[jt % Cfg::kVStages];
+          const uint32_t kp = (jt / Cfg::kKStages) & 1, vp = (jt / Cfg::kVStages) & 1;
+          for (unsigned spin = 0; spin < (1u << 16) && !(mbar_test(kb, kp) && mbar_test(vb, vp)); ++spin) __nanosleep(64);
         }
       }
     }
@@ -162,11 +176,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       bool ok = mbar_wait(&sh.q_full, 0, abort);
       if (!ok) LLMIE_FAIL(kStatusTimeoutFull);
       auto issue_scores = [&](int jt) -> bool {
-        const int st = jt % Cfg::kKvStages, b = jt & 1;
-        if (!mbar_wait(&sh.k_full[st], (jt / Cfg::kKvStages) & 1, abort)) { LLMIE_FAIL(kStatusTimeoutFull); return false; }
-        if (jt >= 2 && !mbar_wait(&sh.s_free[b], ((jt >> 1) - 1) & 1, abort)) { LLMIE_FAIL(kStatusTimeoutMma); return false; }
+        const int ks = jt % Cfg::kKStages, b = jt % Cfg::kSBufs, use = jt / Cfg::kSBufs;
+        if (!mbar_wait(&sh.k_full[ks], (jt / Cfg::kKStages) & 1, abort)) { LLMIE_FAIL(kStatusTimeoutFull); return false; }
+        if (use >= 1 && !mbar_wait(&sh.s_free[b], (use - 1) & 1, abort)) { LLMIE_FAIL(kStatusTimeoutMma); return false; }
         tc_fence_after_sync();
-        const uint32_t k_addr = smem_u32(k_smem + st * Cfg::kKvBytes);
+        const uint32_t k_addr = smem_u32(k_smem + ks * Cfg::kKvBytes);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk >> 2) * kSubTileBytes + (kk & 3) * 32;
@@ -174,25 +188,26 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                       idesc_s, kk > 0 ? 1u : 0u);
         }
         mma_commit(&sh.s_full[b]);
+        mma_commit(&sh.k_empty[ks]);             // this K tile is free once the scores are computed
         return true;
       };
       if (ok) ok = issue_scores(0);
       for (int jt = 0; ok && jt < n_tiles; ++jt) {
         if (jt + 1 < n_tiles && !issue_scores(jt + 1)) break;
-        const int st = jt % Cfg::kKvStages;
+        const int vs = jt % Cfg::kVStages;
         if (!mbar_wait(&sh.p_ready, jt & 1, abort)) { LLMIE_FAIL(kStatusTimeoutMma); break; }
-        if (!mbar_wait(&sh.v_full[st], (jt / Cfg::kKvStages) & 1, abort)) { LLMIE_FAIL(kStatusTimeoutFull); break; }
+        if (!mbar_wait(&sh.v_full[vs], (jt / Cfg::kVStages) & 1, abort)) { LLMIE_FAIL(kStatusTimeoutFull); break; }
         tc_fence_after_sync();
-        const uint32_t v_addr = smem_u32(v_smem + st * Cfg::kKvBytes);
+        const uint32_t v_addr = smem_u32(v_smem + vs * Cfg::kKvBytes);
 #pragma unroll
         for (int kk = 0; kk < kKTile / 16; ++kk) {
           // A = P, K-major: 16 keys = 32 bytes inside a 64-key sub-tile. B = V, MN-major: 16 keys = 16 rows.
           const uint64_t dp = make_smem_desc(p_addr + (kk >> 2) * kSubTileBytes + (kk & 3) * 32, 16, 1024);
           const uint64_t dv = make_smem_desc(v_addr + kk * 2048, kSubTileBytes, 1024);
-          mma_bf16_ss(tmem + 256, dp, dv, idesc_pv, kk > 0 ? 1u : 0u);
+          mma_bf16_ss(tmem + Cfg::kPvCol, dp, dv, idesc_pv, kk > 0 ? 1u : 0u);
         }
         mma_commit(&sh.pv_full);
-        mma_commit(&sh.kv_empty[st]);
+        mma_commit(&sh.v_empty[vs]);
       }
     }
   } else {
@@ -209,8 +224,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (int jt = 0; jt < n_tiles; ++jt) {
-      const int b = jt & 1;
-      if (!mbar_wait(&sh.s_full[b], (jt >> 1) & 1, abort)) { LLMIE_FAIL(kStatusTimeoutMma); ok = false; break; }
+      const int b = jt % Cfg::kSBufs;
+      if (!mbar_wait(&sh.s_full[b], (jt / Cfg::kSBufs) & 1, abort)) { LLMIE_FAIL(kStatusTimeoutMma); ok = false; break; }
       tc_fence_after_sync();
       const int kbase = (tile_lo + jt) * kKTile;
       const bool edge = (kbase + kKTile - 1 > start + t0) || (window > 0 && kbase < start + t0 + kQTile - window);
@@ -274,7 +289,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
       for (int c0 = 0; c0 < HD; c0 += 32) {
         uint32_t v[32];
-        tmem_ld_32x32(lane_addr + 256 + c0, v);
+        tmem_ld_32x32(lane_addr + Cfg::kPvCol + c0, v);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha, __uint_as_float(v[i]));
@@ -300,7 +315,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem, 512);
+    tmem_dealloc(tmem, Cfg::kTmemCols);
   }
 }
 

@@ -115,6 +115,24 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
   }
 }
 
+// The same, eight outputs per thread with 16-byte loads (ff % 8 == 0).
+template <typename T>
+__global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int ff8, size_t total8) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total8; i += stride) {
+    const size_t t = i / ff8;
+    const int j = (int)(i - t * ff8) * 8;
+    const T* row = gate_up + t * (size_t)ff8 * 16;
+    float g[8], u[8], o[8];
+    load8(row + j, g);
+    load8(row + (size_t)ff8 * 8 + j, u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = g[e] / (1.f + expf(-g[e])) * u[e];
+    store8(out + i * 8, o);
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // Rotary position encoding fused with the KV-cache write
 // (src/rope.py:74-91 rotate-half, :122-185 the fused K rotation + cache write of the reference).
@@ -177,6 +195,60 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
       }
     } else {
       k_cache[dst + i] = ks[it];
+    }
+  }
+}
+
+// The same for full rotation (rot_dim == hd, hd % 16 == 0): a thread rotates eight pairs at a
+// time with 16-byte loads and stores. Items per token: query heads, then key heads (rotated,
+// to the cache), then value heads (copied to the cache).
+template <typename T>
+__global__ void rope_store_vec_kernel(const T* __restrict__ qkv, T* __restrict__ q_out,
+                                      T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                      const float2* __restrict__ table, const int* __restrict__ tok_pos,
+                                      const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
+                                      const int* __restrict__ block_table, int max_pages, int page_size,
+                                      int n_q, int n_kv, int hd, int table_len, int write_kv) {
+  const int t = blockIdx.x;
+  const int pos = tok_pos[t];
+  const int half = hd >> 1;
+  const int vec_per_half = half >> 3;
+  const T* src = qkv + (size_t)t * (n_q + 2 * n_kv) * hd;
+  const int tpos = pos < table_len ? pos : table_len - 1;
+  const float2* cs = table + (size_t)tpos * half;
+  size_t kv_row = 0;
+  if (write_kv) {
+    const int slot = seq_slot[tok_seq[t]];
+    const int page = block_table[(size_t)slot * max_pages + pos / page_size];
+    kv_row = ((size_t)page * n_kv * page_size + (pos % page_size)) * hd;      // head 0; heads are page_size * hd apart
+  }
+  const int rot_items = (n_q + (write_kv ? n_kv : 0)) * vec_per_half;
+  for (int it = threadIdx.x; it < rot_items; it += blockDim.x) {
+    const int head = it / vec_per_half;
+    const int i = (it - head * vec_per_half) * 8;
+    const T* x = src + (size_t)head * hd;                     // k heads follow the q heads in qkv
+    float x1[8], x2[8], y1[8], y2[8];
+    load8(x + i, x1);
+    load8(x + i + half, x2);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float2 c = cs[i + e];
+      y1[e] = x1[e] * c.x - x2[e] * c.y;
+      y2[e] = x2[e] * c.x + x1[e] * c.y;
+    }
+    T* dst = head < n_q ? q_out + ((size_t)t * n_q + head) * hd
+                        : k_cache + kv_row + (size_t)(head - n_q) * page_size * hd;
+    store8(dst + i, y1);
+    store8(dst + i + half, y2);
+  }
+  if (write_kv) {
+    const int v_items = n_kv * (hd >> 3);
+    const T* vs = src + (size_t)(n_q + n_kv) * hd;
+    for (int it = threadIdx.x; it < v_items; it += blockDim.x) {
+      const int head = it / (hd >> 3);
+      const int i = (it - head * (hd >> 3)) * 8;
+      *reinterpret_cast<uint4*>(v_cache + kv_row + (size_t)head * page_size * hd + i) =
+          *reinterpret_cast<const uint4*>(vs + (size_t)head * hd + i);
     }
   }
 }
@@ -285,6 +357,20 @@ extern "C" int llmie_swiglu(const void* gate_up, void* out, int n_tokens, int ff
   if (n_tokens < 0 || ff <= 0) return LLMIE_ERR_BAD_ARG;
   const size_t total = (size_t)n_tokens * ff;
   if (total == 0) return LLMIE_OK;
+  if (ff % 8 == 0 && aligned16(gate_up) && aligned16(out)) {
+    const size_t total8 = total / 8;
+    size_t nb = (total8 + 255) / 256;
+    if (nb > 148 * 16) nb = 148 * 16;
+    if (dtype == LLMIE_F32)
+      swiglu_vec_kernel<float><<<(int)nb, 256, 0, stream>>>((const float*)gate_up, (float*)out, ff / 8, total8);
+    else if (dtype == LLMIE_BF16)
+      swiglu_vec_kernel<__nv_bfloat16><<<(int)nb, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out,
+                                                                    ff / 8, total8);
+    else
+      return LLMIE_ERR_DTYPE;
+    LLMIE_LAUNCH_CHECK();
+    return LLMIE_OK;
+  }
   const int threads = 256;
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 32) blocks = 148 * 32;
@@ -311,6 +397,16 @@ extern "C" int llmie_rope_store(const void* qkv, void* q_out, void* k_cache, voi
   int threads = ((n_q * hd / 2 + 31) / 32) * 32;
   threads = threads < 64 ? 64 : (threads > 512 ? 512 : threads);
   const float2* tab = reinterpret_cast<const float2*>(table);
+  if (dtype == LLMIE_BF16 && table && rot_dim == hd && hd % 16 == 0 && aligned16(qkv) && aligned16(q_out) &&
+      (!write_kv || (aligned16(k_cache) && aligned16(v_cache)))) {
+    int vt = (((n_q + n_kv) * (hd / 16) + 31) / 32) * 32;
+    vt = vt < 32 ? 32 : (vt > 256 ? 256 : vt);
+    rope_store_vec_kernel<__nv_bfloat16><<<n_tokens, vt, 0, stream>>>(
+        (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tab, tok_pos,
+        tok_seq, seq_slot, block_table, max_pages, page_size, n_q, n_kv, hd, table_len, write_kv);
+    LLMIE_LAUNCH_CHECK();
+    return LLMIE_OK;
+  }
   if (dtype == LLMIE_F32)
     rope_store_kernel<float><<<n_tokens, threads, 0, stream>>>(
         (const float*)qkv, (float*)q_out, (float*)k_cache, (float*)v_cache, tab, tok_pos, tok_seq, seq_slot,
