@@ -55,6 +55,14 @@ struct AttnShared {
   int abort;
 };
 
+// 2^x by the special-function unit (about 2 units in the last place; the probabilities are then
+// rounded to bfloat16, whose last place is 2^16 times coarser)
+__device__ __forceinline__ float exp2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -79,7 +87,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seq = blockIdx.z, head = blockIdx.y;
   const int q_begin = cu_q[seq], q_len = cu_q[seq + 1] - q_begin;
-  const int t0 = blockIdx.x * kQTile;
+  // late query tiles see the most keys: they are handed out first so that the long blocks start early
+  const int t0 = (gridDim.x - 1 - blockIdx.x) * kQTile;
   if (t0 >= q_len) return;                         // uniform for the block: nothing was set up yet
   const int start = seq_start[seq];                // tokens the sequence held before this step
   const int hk = head / (n_q / n_kv);
@@ -231,43 +240,48 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const bool edge = (kbase + kKTile - 1 > start + t0) || (window > 0 && kbase < start + t0 + kQTile - window);
       // pass 1: the row's maximum over the keys it may see
       float m_tile = -INFINITY;
-#pragma unroll 1
+#pragma unroll
       for (int c0 = 0; c0 < kKTile; c0 += 32) {
         uint32_t v[32];
         tmem_ld_32x32(lane_addr + b * 128 + c0, v);
         tmem_ld_wait();
+        if (edge) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]);
-          if (edge) {
+          for (int i = 0; i < 32; ++i) {
             const int key = kbase + c0 + i;
-            if (key > qpos || key < lo) s = -INFINITY;
+            const float s = (key > qpos || key < lo) ? -INFINITY : __uint_as_float(v[i]);
+            m_tile = fmaxf(m_tile, s);
           }
-          m_tile = fmaxf(m_tile, s);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, __uint_as_float(v[i]));
         }
       }
       const float m_new = fmaxf(m_run, m_tile);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;      // a row that has seen no key yet
-      const float alpha = exp2f((m_run - m_use) * sl2);            // 0 while m_run is -inf
+      const float alpha = exp2_approx((m_run - m_use) * sl2);      // 0 while m_run is -inf
       const float m_scaled = m_use * sl2;
       // pass 2: probabilities, their sum, and P in bfloat16 into the swizzled operand tile
       float l_tile = 0.f;
-#pragma unroll 1
+#pragma unroll
       for (int c0 = 0; c0 < kKTile; c0 += 32) {
         uint32_t v[32];
         tmem_ld_32x32(lane_addr + b * 128 + c0, v);
         tmem_ld_wait();
         float p[32];
+        if (edge) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]);
-          if (edge) {
+          for (int i = 0; i < 32; ++i) {
             const int key = kbase + c0 + i;
-            if (key > qpos || key < lo) s = -INFINITY;
+            const float e = exp2_approx(fmaf(__uint_as_float(v[i]), sl2, -m_scaled));
+            p[i] = (key > qpos || key < lo) ? 0.f : e;
           }
-          p[i] = exp2f(fmaf(s, sl2, -m_scaled));
-          l_tile += p[i];
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) p[i] = exp2_approx(fmaf(__uint_as_float(v[i]), sl2, -m_scaled));
         }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) l_tile += p[i];
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {                 // four 16-byte chunks of 8 keys
           const int chunk = (c0 >> 3) + ch;              // 0..15 within the 128 keys
