@@ -48,6 +48,8 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, cons
                     const int* __restrict__ seq_slot, const int* __restrict__ seq_kvlen,
                     const int* __restrict__ block_table, int max_pages, int page_size, int n_q, int n_kv,
                     float scale, int window, int run_len, int n_runs) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int E = Vec16<T>::E;
   constexpr int LPK = HD / E;          // lanes per key
   constexpr int KPW = 32 / LPK;        // keys per warp per iteration
@@ -183,6 +185,8 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_m, const floa
                                     const float* __restrict__ part_acc, T* __restrict__ out,
                                     const int* __restrict__ seq_kvlen, int n_q, int hd, int window, int run_len,
                                     int n_runs) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int seq = blockIdx.y, h = blockIdx.x;
   const int len = seq_kvlen[seq];
   const int lo = first_visible(len, window);
@@ -215,7 +219,7 @@ static int launch_split(const void* q, const void* k_cache, const void* v_cache,
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid(n_runs, n_kv * chunks, n_seqs);
-  decode_split_kernel<T, HD, GMAX><<<grid, kDecThreads, smem, stream>>>(
+  launch_k(decode_split_kernel<T, HD, GMAX>, dim3(grid), dim3(kDecThreads), smem, stream, 
       (const T*)q, (const T*)k_cache, (const T*)v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen, block_table,
       max_pages, page_size, n_q, n_kv, scale, window, run_len, n_runs);
   LLMIE_LAUNCH_CHECK();
@@ -294,10 +298,10 @@ extern "C" int llmie_attention_decode(const void* q, const void* k_cache, const 
   dim3 grid(n_q, n_seqs);
   const int threads = hd < 32 ? 32 : (hd > 256 ? 256 : ((hd + 31) / 32) * 32);
   if (dtype == LLMIE_F32)
-    decode_merge_kernel<float><<<grid, threads, 0, stream>>>(part_m, part_l, part_acc, (float*)out, seq_kvlen, n_q, hd,
+    launch_k(decode_merge_kernel<float>, dim3(grid), dim3(threads), 0, stream, part_m, part_l, part_acc, (float*)out, seq_kvlen, n_q, hd,
                                                              window, run_len, n_runs);
   else
-    decode_merge_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(part_m, part_l, part_acc, (__nv_bfloat16*)out,
+    launch_k(decode_merge_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, stream, part_m, part_l, part_acc, (__nv_bfloat16*)out,
                                                                      seq_kvlen, n_q, hd, window, run_len, n_runs);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;

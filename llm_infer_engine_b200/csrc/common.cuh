@@ -8,6 +8,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define LLMIE_OK 0
 #define LLMIE_ERR_BAD_ARG (-1)
@@ -89,5 +90,41 @@ __device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
 }
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Programmatic dependent launch: a kernel launched through launch_k may begin while the kernel
+// before it in the stream is still draining. Each such kernel calls pdl_launch_dependents() at
+// its top (the next kernel may be scheduled) and pdl_wait() before it touches anything an
+// earlier kernel wrote (the wait returns when all earlier kernels have completed and their
+// writes are visible). What a kernel does before pdl_wait() - index arithmetic, loads of
+// weights that no kernel writes - overlaps the previous kernel's tail. Both calls are no-ops
+// in a kernel launched the ordinary way. LLMIE_PDL=0 in the environment turns the attribute off.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("LLMIE_PDL");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on != 0;
+}
+
+template <typename... KArgs, typename... Args>
+static inline void launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                            Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  const bool pdl = pdl_enabled();
+  cfg.attrs = pdl ? attr : nullptr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);   // errors surface in cudaGetLastError()
+}
 
 }  // namespace llmie

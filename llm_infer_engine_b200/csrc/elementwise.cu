@@ -11,6 +11,8 @@ namespace llmie {
 template <typename W>
 __global__ void embedding_kernel(const int* __restrict__ tokens, const W* __restrict__ table,
                                  float* __restrict__ h, int d, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   int id = tokens[t];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // the host refuses such ids; never read outside
@@ -30,6 +32,8 @@ template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ delta,
                                    const float* __restrict__ w, T* __restrict__ y,
                                    const int* __restrict__ rows, int d, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float row_buf[];
   __shared__ float red[32];
   const int b = blockIdx.x;
@@ -58,6 +62,8 @@ template <typename T>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const T* __restrict__ delta,
                                        const float* __restrict__ w, T* __restrict__ y,
                                        const int* __restrict__ rows, int d, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[32];
   const int b = blockIdx.x;
   const int r = rows ? rows[b] : b;
@@ -94,6 +100,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const T* __restric
 // h += delta, no norm (used when a block arrangement needs the bare sum)
 template <typename T>
 __global__ void residual_add_kernel(float* __restrict__ h, const T* __restrict__ delta, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; i < n; i += stride) h[i] += to_f32(delta[i]);
@@ -103,6 +111,8 @@ __global__ void residual_add_kernel(float* __restrict__ h, const T* __restrict__
 // out[t, j] = silu(gate_up[t, j]) * gate_up[t, ff + j]      (src/model.py:23 of the reference)
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int ff, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; i < total; i += stride) {
@@ -118,6 +128,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 // The same, eight outputs per thread with 16-byte loads (ff % 8 == 0).
 template <typename T>
 __global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int ff8, size_t total8) {
+  pdl_launch_dependents();
+  pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; i < total8; i += stride) {
@@ -148,6 +160,8 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
                                   const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
                                   const int* __restrict__ block_table, int max_pages, int page_size,
                                   int n_q, int n_kv, int hd, int rot_dim, int table_len, int write_kv) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   int pos = tok_pos[t];
   const int half = rot_dim >> 1;
@@ -209,6 +223,8 @@ __global__ void rope_store_vec_kernel(const T* __restrict__ qkv, T* __restrict__
                                       const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
                                       const int* __restrict__ block_table, int max_pages, int page_size,
                                       int n_q, int n_kv, int hd, int table_len, int write_kv) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int pos = tok_pos[t];
   const int half = hd >> 1;
@@ -260,6 +276,8 @@ __global__ void prepare_decode_kernel(const int* __restrict__ slots, const int* 
                                       int* __restrict__ tok_pos, int* __restrict__ tok_seq,
                                       int* __restrict__ cu_q, int* __restrict__ seq_start,
                                       int* __restrict__ seq_kvlen, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) {
     const int len = seq_lens[slots[i]];
@@ -275,6 +293,8 @@ __global__ void prepare_decode_kernel(const int* __restrict__ slots, const int* 
 // seq_lens[slot] = kv length after the step, except for the scratch slot that padding lanes use.
 __global__ void advance_lengths_kernel(const int* __restrict__ slots, const int* __restrict__ seq_kvlen,
                                        int* __restrict__ seq_lens, int n, int scratch_slot) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) {
     const int s = slots[i];
@@ -298,9 +318,9 @@ extern "C" int llmie_embedding(const int* tokens, const void* table, int table_d
   if (n_tokens == 0) return LLMIE_OK;
   const int threads = norm_threads(d);
   if (table_dtype == LLMIE_F32)
-    embedding_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, h, d, vocab);
+    launch_k(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table, h, d, vocab);
   else if (table_dtype == LLMIE_BF16)
-    embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, h, d, vocab);
+    launch_k(embedding_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const __nv_bfloat16*)table, h, d, vocab);
   else
     return LLMIE_ERR_DTYPE;
   LLMIE_LAUNCH_CHECK();
@@ -312,7 +332,7 @@ static int add_rmsnorm_launch(float* h, const void* delta, const float* w, void*
                               int d, float eps, cudaStream_t stream) {
   if (d % 8 == 0 && d <= 8 * 1024 && aligned16(h) && aligned16(w) && aligned16(y) && (!delta || aligned16(delta))) {
     const int threads = ((d / 8 + 31) / 32) * 32;
-    add_rmsnorm_vec_kernel<T><<<n_out, threads, 0, stream>>>(h, (const T*)delta, w, (T*)y, rows, d, eps);
+    launch_k(add_rmsnorm_vec_kernel<T>, dim3(n_out), dim3(threads), 0, stream, h, (const T*)delta, w, (T*)y, rows, d, eps);
     LLMIE_LAUNCH_CHECK();
     return LLMIE_OK;
   }
@@ -322,7 +342,7 @@ static int add_rmsnorm_launch(float* h, const void* delta, const float* w, void*
     cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  add_rmsnorm_kernel<T><<<n_out, norm_threads(d), smem, stream>>>(h, (const T*)delta, w, (T*)y, rows, d, eps);
+  launch_k(add_rmsnorm_kernel<T>, dim3(n_out), dim3(norm_threads(d)), smem, stream, h, (const T*)delta, w, (T*)y, rows, d, eps);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }
@@ -344,9 +364,9 @@ extern "C" int llmie_residual_add(float* h, const void* delta, long long n, int 
   long long blocks = (n + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (dtype == LLMIE_F32)
-    residual_add_kernel<float><<<(int)blocks, threads, 0, stream>>>(h, (const float*)delta, (size_t)n);
+    launch_k(residual_add_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, h, (const float*)delta, (size_t)n);
   else if (dtype == LLMIE_BF16)
-    residual_add_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>(h, (const __nv_bfloat16*)delta, (size_t)n);
+    launch_k(residual_add_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, stream, h, (const __nv_bfloat16*)delta, (size_t)n);
   else
     return LLMIE_ERR_DTYPE;
   LLMIE_LAUNCH_CHECK();
@@ -362,9 +382,9 @@ extern "C" int llmie_swiglu(const void* gate_up, void* out, int n_tokens, int ff
     size_t nb = (total8 + 255) / 256;
     if (nb > 148 * 16) nb = 148 * 16;
     if (dtype == LLMIE_F32)
-      swiglu_vec_kernel<float><<<(int)nb, 256, 0, stream>>>((const float*)gate_up, (float*)out, ff / 8, total8);
+      launch_k(swiglu_vec_kernel<float>, dim3((int)nb), dim3(256), 0, stream, (const float*)gate_up, (float*)out, ff / 8, total8);
     else if (dtype == LLMIE_BF16)
-      swiglu_vec_kernel<__nv_bfloat16><<<(int)nb, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out,
+      launch_k(swiglu_vec_kernel<__nv_bfloat16>, dim3((int)nb), dim3(256), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out,
                                                                     ff / 8, total8);
     else
       return LLMIE_ERR_DTYPE;
@@ -375,9 +395,9 @@ extern "C" int llmie_swiglu(const void* gate_up, void* out, int n_tokens, int ff
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 32) blocks = 148 * 32;
   if (dtype == LLMIE_F32)
-    swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, ff, total);
+    launch_k(swiglu_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, ff, total);
   else if (dtype == LLMIE_BF16)
-    swiglu_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up,
+    launch_k(swiglu_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)gate_up,
                                                                      (__nv_bfloat16*)out, ff, total);
   else
     return LLMIE_ERR_DTYPE;
@@ -401,18 +421,18 @@ extern "C" int llmie_rope_store(const void* qkv, void* q_out, void* k_cache, voi
       (!write_kv || (aligned16(k_cache) && aligned16(v_cache)))) {
     int vt = (((n_q + n_kv) * (hd / 16) + 31) / 32) * 32;
     vt = vt < 32 ? 32 : (vt > 256 ? 256 : vt);
-    rope_store_vec_kernel<__nv_bfloat16><<<n_tokens, vt, 0, stream>>>(
+    launch_k(rope_store_vec_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(vt), 0, stream, 
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tab, tok_pos,
         tok_seq, seq_slot, block_table, max_pages, page_size, n_q, n_kv, hd, table_len, write_kv);
     LLMIE_LAUNCH_CHECK();
     return LLMIE_OK;
   }
   if (dtype == LLMIE_F32)
-    rope_store_kernel<float><<<n_tokens, threads, 0, stream>>>(
+    launch_k(rope_store_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, 
         (const float*)qkv, (float*)q_out, (float*)k_cache, (float*)v_cache, tab, tok_pos, tok_seq, seq_slot,
         block_table, max_pages, page_size, n_q, n_kv, hd, rot_dim, table_len, write_kv);
   else if (dtype == LLMIE_BF16)
-    rope_store_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+    launch_k(rope_store_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, 
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tab,
         tok_pos, tok_seq, seq_slot, block_table, max_pages, page_size, n_q, n_kv, hd, rot_dim, table_len, write_kv);
   else
@@ -424,7 +444,7 @@ extern "C" int llmie_rope_store(const void* qkv, void* q_out, void* k_cache, voi
 extern "C" int llmie_prepare_decode(const int* slots, const int* seq_lens, int* tok_pos, int* tok_seq, int* cu_q,
                                     int* seq_start, int* seq_kvlen, int n, cudaStream_t stream) {
   if (n <= 0) return LLMIE_ERR_BAD_ARG;
-  prepare_decode_kernel<<<(n + 127) / 128, 128, 0, stream>>>(slots, seq_lens, tok_pos, tok_seq, cu_q, seq_start,
+  launch_k(prepare_decode_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, slots, seq_lens, tok_pos, tok_seq, cu_q, seq_start,
                                                              seq_kvlen, n);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
@@ -433,7 +453,7 @@ extern "C" int llmie_prepare_decode(const int* slots, const int* seq_lens, int* 
 extern "C" int llmie_advance_lengths(const int* slots, const int* seq_kvlen, int* seq_lens, int n, int scratch_slot,
                                      cudaStream_t stream) {
   if (n <= 0) return LLMIE_ERR_BAD_ARG;
-  advance_lengths_kernel<<<(n + 127) / 128, 128, 0, stream>>>(slots, seq_kvlen, seq_lens, n, scratch_slot);
+  launch_k(advance_lengths_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, slots, seq_kvlen, seq_lens, n, scratch_slot);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }

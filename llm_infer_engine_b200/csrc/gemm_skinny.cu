@@ -43,6 +43,7 @@ template <int NB, int EPI, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W, void* __restrict__ out,
                    int batch, int K, int ldo, int tile_stride, int hi_delta) {
+  pdl_launch_dependents();
   __shared__ float red[WARPS][NB][16][8 + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -74,6 +75,9 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       wb[u] = ldg16(w_hi + c * 4);
     }
   }
+  // The weights are written by no kernel, so their first loads are already on their way while
+  // the kernel before this one finishes; x (and out, for the add) are its results: wait for it here.
+  pdl_wait();
   for (int c0 = warp; c0 < n_chunks; c0 += kStep) {
 #pragma unroll
     for (int u = 0; u < kSkUnroll; ++u) {           // request the next round
@@ -159,16 +163,16 @@ static int launch_epi(int epi, const void* x, const void* W, void* out, int batc
   const __nv_bfloat16* wp = (const __nv_bfloat16*)W;
   switch (epi) {
     case kStoreBf16:
-      skinny_gemm_kernel<NB, kStoreBf16, WARPS><<<tiles, WARPS * 32, 0, stream>>>(xp, wp, out, batch, K, ldo, tile_stride, hi_delta);
+      launch_k(skinny_gemm_kernel<NB, kStoreBf16, WARPS>, dim3(tiles), dim3(WARPS * 32), 0, stream, xp, wp, out, batch, K, ldo, tile_stride, hi_delta);
       break;
     case kStoreF32:
-      skinny_gemm_kernel<NB, kStoreF32, WARPS><<<tiles, WARPS * 32, 0, stream>>>(xp, wp, out, batch, K, ldo, tile_stride, hi_delta);
+      launch_k(skinny_gemm_kernel<NB, kStoreF32, WARPS>, dim3(tiles), dim3(WARPS * 32), 0, stream, xp, wp, out, batch, K, ldo, tile_stride, hi_delta);
       break;
     case kAddF32:
-      skinny_gemm_kernel<NB, kAddF32, WARPS><<<tiles, WARPS * 32, 0, stream>>>(xp, wp, out, batch, K, ldo, tile_stride, hi_delta);
+      launch_k(skinny_gemm_kernel<NB, kAddF32, WARPS>, dim3(tiles), dim3(WARPS * 32), 0, stream, xp, wp, out, batch, K, ldo, tile_stride, hi_delta);
       break;
     case kSwiGLU:
-      skinny_gemm_kernel<NB, kSwiGLU, WARPS><<<tiles, WARPS * 32, 0, stream>>>(xp, wp, out, batch, K, ldo, tile_stride, hi_delta);
+      launch_k(skinny_gemm_kernel<NB, kSwiGLU, WARPS>, dim3(tiles), dim3(WARPS * 32), 0, stream, xp, wp, out, batch, K, ldo, tile_stride, hi_delta);
       break;
     default:
       return LLMIE_ERR_BAD_ARG;

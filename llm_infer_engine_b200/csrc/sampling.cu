@@ -61,6 +61,8 @@ __global__ void __launch_bounds__(kSampleThreads)
 sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature, float top_p,
               unsigned long long seed, const int* __restrict__ seq_ids, int* __restrict__ counters,
               int* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ MaxIdx arg_scratch[32];
   __shared__ float red[32];
   __shared__ float chunk_sum[kSampleThreads];
@@ -151,6 +153,8 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature
 __global__ void __launch_bounds__(256)
 argmax_partial_kernel(const float* __restrict__ logits, int ld, int V, int slices, float* __restrict__ part_val,
                       int* __restrict__ part_idx) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ MaxIdx scratch[32];
   const int s = blockIdx.x, r = blockIdx.y;
   const int chunk = (V + slices - 1) / slices;
@@ -182,6 +186,8 @@ argmax_partial_kernel(const float* __restrict__ logits, int ld, int V, int slice
 
 __global__ void argmax_merge_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int slices,
                                     int* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x, lane = threadIdx.x;
   MaxIdx best{-INFINITY, 0x7fffffff};
   for (int s = lane; s < slices; s += 32) best = better(best, MaxIdx{part_val[r * slices + s], part_idx[r * slices + s]});
@@ -195,6 +201,8 @@ __global__ void argmax_merge_kernel(const float* __restrict__ part_val, const in
 
 // tokens[i] = sampled[i] for the lanes of a decode step (feeds the next step on the device)
 __global__ void copy_int_kernel(const int* __restrict__ src, int* __restrict__ dst, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) dst[i] = src[i];
 }
@@ -211,7 +219,7 @@ extern "C" int llmie_sample(const float* logits, int n_rows, int V, int ld, floa
   if (n_rows < 0 || V <= 0 || ld < V) return LLMIE_ERR_BAD_ARG;
   if (temperature > 0.f && (!seq_ids || !counters)) return LLMIE_ERR_BAD_ARG;
   if (n_rows == 0) return LLMIE_OK;
-  sample_kernel<<<n_rows, kSampleThreads, 0, stream>>>(logits, ld, V, temperature, top_p, seed, seq_ids, counters,
+  launch_k(sample_kernel, dim3(n_rows), dim3(kSampleThreads), 0, stream, logits, ld, V, temperature, top_p, seed, seq_ids, counters,
                                                        out);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
@@ -220,7 +228,7 @@ extern "C" int llmie_sample(const float* logits, int n_rows, int V, int ld, floa
 extern "C" int llmie_copy_int(const int* src, int* dst, int n, cudaStream_t stream) {
   if (n < 0) return LLMIE_ERR_BAD_ARG;
   if (n == 0) return LLMIE_OK;
-  copy_int_kernel<<<(n + 255) / 256, 256, 0, stream>>>(src, dst, n);
+  launch_k(copy_int_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, src, dst, n);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }
@@ -231,9 +239,9 @@ extern "C" int llmie_argmax(const float* logits, int n_rows, int V, int ld, int 
   if (n_rows < 0 || V <= 0 || ld < V || slices <= 0 || slices > 1024) return LLMIE_ERR_BAD_ARG;
   if (n_rows == 0) return LLMIE_OK;
   if (n_rows > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
-  argmax_partial_kernel<<<dim3(slices, n_rows), 256, 0, stream>>>(logits, ld, V, slices, part_val, part_idx);
+  launch_k(argmax_partial_kernel, dim3(dim3(slices, n_rows)), dim3(256), 0, stream, logits, ld, V, slices, part_val, part_idx);
   LLMIE_LAUNCH_CHECK();
-  argmax_merge_kernel<<<n_rows, 32, 0, stream>>>(part_val, part_idx, slices, out);
+  launch_k(argmax_merge_kernel, dim3(n_rows), dim3(32), 0, stream, part_val, part_idx, slices, out);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }
