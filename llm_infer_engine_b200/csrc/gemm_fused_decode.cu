@@ -1,0 +1,377 @@
+// One-token steps, first product of a branch: RMSNorm -> weight-streaming product -> the
+// branch's next elementwise step, in ONE kernel, for up to 8 rows.
+//
+//   variant "qkv":   x = rmsnorm(h) ; [q k v] = x Wqkv^T ; rotate q and k by position ;
+//                    q -> activation buffer, rotated k and v -> the paged KV cache
+//   variant "gate":  x = rmsnorm(h) ; act = silu(x Wg^T) * (x Wu^T)
+//   variant "f32":   x = rmsnorm(h) ; out = x W^T in float32 (the LM head after the final norm)
+//
+// In the reference these are 5, 5 and 2 launches (src/model.py:114,54,62,69-74; :127,23; :183).
+// In a one-token step every launch costs a few microseconds of latency whatever it computes,
+// and the layer is a chain of dependent launches, so fewer launches is what shortens it.
+//
+// The norm costs no extra pass: with w the norm weight, rmsnorm(h) W^T = rstd * ((h * w) W^T),
+// so the block turns h * w into bfloat16 operands while it adds up h^2, multiplies as in
+// gemm_skinny.cu (weights as the 16-row MMA operand, 16-byte loads straight into fragments,
+// warps splitting K), and applies rstd = rsqrt(mean(h^2) + eps) to the finished sums. The rows
+// of h * w are staged in shared memory once per block and reused for every tile of weight rows
+// the block owns; the first weights of the first tile are requested before anything else, even
+// before the wait for the previous kernel (no kernel writes weights).
+#include "common.cuh"
+#include <math.h>
+
+namespace llmie {
+
+constexpr int kFdUnroll = 4;
+constexpr int kFdPad = 32;          // bfloat16 elements of padding per staged row: 16-byte reads do not collide
+
+enum FusedVariant { kVarQkvRope = 0, kVarGateSwiGLU = 1, kVarF32 = 2 };
+
+struct RopeStoreArgs {
+  __nv_bfloat16* q_out;          // [batch, n_q * hd]
+  __nv_bfloat16* k_cache;        // [pages, n_kv, page_size, hd]
+  __nv_bfloat16* v_cache;
+  const float2* table;           // [table_len, hd / 2] of (cos, sin)
+  const int* tok_pos;            // [batch]
+  const int* tok_seq;            // [batch]
+  const int* seq_slot;
+  const int* block_table;
+  int max_pages, page_size, n_q, n_kv, hd, table_len, write_kv;
+};
+
+__device__ __forceinline__ void fd_mma(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                       unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint4 fd_ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ unsigned fd_pack(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Weight rows of tile `tile`: low rows lo..lo+7 and high rows hi..hi+7.
+template <int VAR>
+__device__ __forceinline__ void tile_rows(int tile, int hd, int half_n, int& lo, int& hi) {
+  if (VAR == kVarQkvRope) {                 // rows i0..i0+7 and i0+hd/2.. of one head: rotation partners
+    const int per_head = hd >> 4;
+    const int head = tile / per_head, i0 = (tile - head * per_head) << 3;
+    lo = head * hd + i0;
+    hi = lo + (hd >> 1);
+  } else if (VAR == kVarGateSwiGLU) {       // gate rows j..j+7 and the up rows of the same j
+    lo = tile << 3;
+    hi = half_n + lo;
+  } else {
+    lo = tile << 4;
+    hi = lo + 8;
+  }
+}
+
+template <int VAR, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
+norm_gemm_kernel(const float* __restrict__ h, const float* __restrict__ norm_w, float eps,
+                 const __nv_bfloat16* __restrict__ W, void* __restrict__ out, int batch, int K, int ldo, int tiles,
+                 int half_n, RopeStoreArgs rope) {
+  pdl_launch_dependents();
+  extern __shared__ __align__(16) unsigned char fd_smem[];
+  const int xs_stride = K + kFdPad;                                        // elements
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(fd_smem);           // [8][K + pad]
+  float* red = reinterpret_cast<float*>(fd_smem + (size_t)8 * xs_stride * 2);   // [WARPS][16][9]
+  float* ssw = red + WARPS * 16 * 9;                                       // [WARPS][8]
+  float* rstd = ssw + WARPS * 8;                                           // [8]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int n_chunks = K >> 5;
+  constexpr int kStep = WARPS * kFdUnroll;
+  const int hd = rope.hd;
+
+  int tile = blockIdx.x;
+  int lo, hi;
+  tile_rows<VAR>(tile, hd, half_n, lo, hi);
+  const uint4* w_lo = reinterpret_cast<const uint4*>(W + (size_t)(lo + g) * K) + t;
+  const uint4* w_hi = reinterpret_cast<const uint4*>(W + (size_t)(hi + g) * K) + t;
+  uint4 wa[kFdUnroll], wb[kFdUnroll], na[kFdUnroll], nb2[kFdUnroll];
+#pragma unroll
+  for (int u = 0; u < kFdUnroll; ++u) {
+    const int c = warp + u * WARPS;
+    if (c < n_chunks) {
+      wa[u] = fd_ldg16(w_lo + c * 4);
+      wb[u] = fd_ldg16(w_hi + c * 4);
+    }
+  }
+  pdl_wait();      // h is the previous kernels' result
+
+  // ---- h * w as bfloat16 rows in shared memory, and the sum of squares of every row
+  {
+    float ssq[8];
+#pragma unroll
+    for (int b = 0; b < 8; ++b) ssq[b] = 0.f;
+    for (int k = threadIdx.x * 8; k < K; k += WARPS * 32 * 8) {
+      float wv[8];
+      load8(norm_w + k, wv);
+#pragma unroll
+      for (int b = 0; b < 8; ++b) {
+        float hv[8];
+        if (b < batch) {
+          load8(h + (size_t)b * K + k, hv);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) hv[e] = 0.f;
+        }
+        uint4 packed;
+        packed.x = fd_pack(hv[0] * wv[0], hv[1] * wv[1]);
+        packed.y = fd_pack(hv[2] * wv[2], hv[3] * wv[3]);
+        packed.z = fd_pack(hv[4] * wv[4], hv[5] * wv[5]);
+        packed.w = fd_pack(hv[6] * wv[6], hv[7] * wv[7]);
+        *reinterpret_cast<uint4*>(xs + (size_t)b * xs_stride + k) = packed;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ssq[b] = fmaf(hv[e], hv[e], ssq[b]);
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      const float s = warp_sum(ssq[b]);
+      if (lane == 0) ssw[warp * 8 + b] = s;
+    }
+    __syncthreads();
+    if (threadIdx.x < 8) {
+      float s = 0.f;
+      for (int w = 0; w < WARPS; ++w) s += ssw[w * 8 + threadIdx.x];
+      rstd[threadIdx.x] = rsqrtf(s / (float)K + eps);
+    }
+    __syncthreads();
+  }
+  const uint4* x_row = reinterpret_cast<const uint4*>(xs + (size_t)g * xs_stride) + t;   // this lane's batch row
+
+  // ---- tiles of 16 weight rows
+  while (tile < tiles) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const int next_tile = tile + gridDim.x;
+    int nlo = 0, nhi = 0;
+    const uint4* nw_lo = w_lo;
+    const uint4* nw_hi = w_hi;
+    if (next_tile < tiles) {
+      tile_rows<VAR>(next_tile, hd, half_n, nlo, nhi);
+      nw_lo = reinterpret_cast<const uint4*>(W + (size_t)(nlo + g) * K) + t;
+      nw_hi = reinterpret_cast<const uint4*>(W + (size_t)(nhi + g) * K) + t;
+    }
+    for (int c0 = warp; c0 < n_chunks; c0 += kStep) {
+      // request what comes next: the next round of this tile, or the first round of the next tile
+      const bool last_round = c0 + kStep >= n_chunks;
+#pragma unroll
+      for (int u = 0; u < kFdUnroll; ++u) {
+        if (!last_round) {
+          const int c = c0 + kStep + u * WARPS;
+          if (c < n_chunks) {
+            na[u] = fd_ldg16(w_lo + c * 4);
+            nb2[u] = fd_ldg16(w_hi + c * 4);
+          }
+        } else if (next_tile < tiles) {
+          const int c = warp + u * WARPS;
+          if (c < n_chunks) {
+            na[u] = fd_ldg16(nw_lo + c * 4);
+            nb2[u] = fd_ldg16(nw_hi + c * 4);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kFdUnroll; ++u) {
+        const int c = c0 + u * WARPS;
+        if (c < n_chunks) {
+          const uint4 xv = x_row[c * 4];
+          fd_mma(acc, wa[u].x, wb[u].x, wa[u].y, wb[u].y, xv.x, xv.y);
+          fd_mma(acc, wa[u].z, wb[u].z, wa[u].w, wb[u].w, xv.z, xv.w);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kFdUnroll; ++u) {
+        wa[u] = na[u];
+        wb[u] = nb2[u];
+      }
+    }
+    float* my = red + warp * 16 * 9;
+    my[g * 9 + 2 * t] = acc[0];
+    my[g * 9 + 2 * t + 1] = acc[1];
+    my[(g + 8) * 9 + 2 * t] = acc[2];
+    my[(g + 8) * 9 + 2 * t + 1] = acc[3];
+    __syncthreads();
+
+    if (VAR == kVarF32) {
+      for (int idx = threadIdx.x; idx < 128; idx += WARPS * 32) {
+        const int r = idx & 15, b = idx >> 4;
+        if (b >= batch) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) v += red[(w * 16 + r) * 9 + b];
+        reinterpret_cast<float*>(out)[(size_t)b * ldo + (r < 8 ? lo + r : hi + r - 8)] = v * rstd[b];
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < 64; idx += WARPS * 32) {
+        const int j = idx & 7, b = idx >> 3;
+        if (b >= batch) continue;
+        float x1 = 0.f, x2 = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+          x1 += red[(w * 16 + j) * 9 + b];
+          x2 += red[(w * 16 + j + 8) * 9 + b];
+        }
+        x1 *= rstd[b];
+        x2 *= rstd[b];
+        if (VAR == kVarGateSwiGLU) {
+          const float act = x1 / (1.f + expf(-x1)) * x2;
+          reinterpret_cast<__nv_bfloat16*>(out)[(size_t)b * ldo + lo + j] = __float2bfloat16_rn(act);
+        } else {
+          // rows lo + j and lo + j + hd/2 of one head: elements i and i + hd/2
+          const int head = lo / hd, i = lo - head * hd + j, half = hd >> 1;
+          const int pos = rope.tok_pos[b];
+          if (head < rope.n_q + rope.n_kv) {
+            const float2 cs = rope.table[(size_t)min(pos, rope.table_len - 1) * half + i];
+            const float y1 = x1 * cs.x - x2 * cs.y, y2 = x2 * cs.x + x1 * cs.y;
+            x1 = y1;
+            x2 = y2;
+          }
+          __nv_bfloat16* dst;
+          if (head < rope.n_q) {
+            dst = rope.q_out + ((size_t)b * rope.n_q + head) * hd;
+          } else if (rope.write_kv) {
+            const int slot = rope.seq_slot[rope.tok_seq[b]];
+            const int page = rope.block_table[(size_t)slot * rope.max_pages + pos / rope.page_size];
+            const bool is_k = head < rope.n_q + rope.n_kv;
+            const int hk = head - rope.n_q - (is_k ? 0 : rope.n_kv);
+            dst = (is_k ? rope.k_cache : rope.v_cache) +
+                  (((size_t)page * rope.n_kv + hk) * rope.page_size + (pos % rope.page_size)) * hd;
+          } else {
+            dst = nullptr;
+          }
+          if (dst) {
+            dst[i] = __float2bfloat16_rn(x1);
+            dst[i + half] = __float2bfloat16_rn(x2);
+          }
+        }
+      }
+    }
+    __syncthreads();          // `red` is written again by the next tile
+    tile = next_tile;
+    lo = nlo;
+    hi = nhi;
+    w_lo = nw_lo;
+    w_hi = nw_hi;
+  }
+}
+
+template <int VAR, int WARPS>
+static int launch_fused(const float* h, const float* norm_w, float eps, const void* W, void* out, int batch, int K,
+                        int ldo, int tiles, int half_n, const RopeStoreArgs& rope, cudaStream_t stream) {
+  const size_t smem = (size_t)8 * (K + kFdPad) * 2 + (size_t)(WARPS * 16 * 9 + WARPS * 8 + 8) * sizeof(float);
+  if (smem > 200 * 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(norm_gemm_kernel<VAR, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  // as many blocks as stay resident together, evenly loaded: a block walks its tiles with the
+  // staged rows in place
+  static int per_sm_cached = 0;           // one value per template instance
+  static size_t per_sm_smem = 0;
+  if (per_sm_cached == 0 || per_sm_smem != smem) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, norm_gemm_kernel<VAR, WARPS>, WARPS * 32, smem) !=
+            cudaSuccess || n < 1)
+      n = 1;
+    per_sm_cached = n;
+    per_sm_smem = smem;
+  }
+  const int resident = 148 * per_sm_cached;
+  const int waves = (tiles + resident - 1) / resident;
+  const int blocks = (tiles + waves - 1) / waves;
+  launch_k(norm_gemm_kernel<VAR, WARPS>, dim3(blocks), dim3(WARPS * 32), smem, stream, h, norm_w, eps,
+           (const __nv_bfloat16*)W, out, batch, K, ldo, tiles, half_n, rope);
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+template <int VAR>
+static int launch_fused_w(const float* h, const float* norm_w, float eps, const void* W, void* out, int batch, int K,
+                          int ldo, int tiles, int half_n, const RopeStoreArgs& rope, cudaStream_t stream) {
+  const int chunks = K / 32;
+  int warps = 4;
+  while (warps < 16 && tiles * warps < 148 * 16 && chunks >= warps * 2 * kFdUnroll) warps *= 2;
+  if (warps >= 16) return launch_fused<VAR, 16>(h, norm_w, eps, W, out, batch, K, ldo, tiles, half_n, rope, stream);
+  if (warps >= 8) return launch_fused<VAR, 8>(h, norm_w, eps, W, out, batch, K, ldo, tiles, half_n, rope, stream);
+  return launch_fused<VAR, 4>(h, norm_w, eps, W, out, batch, K, ldo, tiles, half_n, rope, stream);
+}
+
+static int check_common(const float* h, const float* norm_w, const void* W, int batch, int N, int K) {
+  if (batch < 0 || N <= 0 || K <= 0) return LLMIE_ERR_BAD_ARG;
+  if (batch > 8 || K % 32) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (!aligned16(h) || !aligned16(norm_w) || !aligned16(W)) return LLMIE_ERR_ALIGNMENT;
+  return LLMIE_OK;
+}
+
+}  // namespace llmie
+
+using namespace llmie;
+
+// 1 when the fused kernels take this (batch, K): up to 8 rows, K a multiple of 32 that fits shared memory.
+extern "C" int llmie_norm_gemm_supported(int batch, int K) {
+  return (batch >= 1 && batch <= 8 && K % 32 == 0 && (size_t)8 * (K + kFdPad) * 2 + 12 * 1024 <= 200 * 1024) ? 1 : 0;
+}
+
+// act[batch, ff] = silu(x Wg^T) * (x Wu^T), x = rmsnorm(h) with weight norm_w; W = [gate rows; up rows] (2 ff rows).
+extern "C" int llmie_norm_gate_swiglu(const float* h, const float* norm_w, float eps, const void* W, void* act,
+                                      int batch, int ff, int K, cudaStream_t stream) {
+  int rc = check_common(h, norm_w, W, batch, ff, K);
+  if (rc != LLMIE_OK) return rc;
+  if (ff % 8) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (batch == 0) return LLMIE_OK;
+  RopeStoreArgs none = {};
+  none.hd = 16;
+  return launch_fused_w<kVarGateSwiGLU>(h, norm_w, eps, W, act, batch, K, ff, ff / 8, ff, none, stream);
+}
+
+// out[batch, N] float32 = rmsnorm(h) W^T.
+extern "C" int llmie_norm_gemm_f32(const float* h, const float* norm_w, float eps, const void* W, float* out, int batch,
+                                   int N, int K, cudaStream_t stream) {
+  int rc = check_common(h, norm_w, W, batch, N, K);
+  if (rc != LLMIE_OK) return rc;
+  if (N % 16) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (batch == 0) return LLMIE_OK;
+  RopeStoreArgs none = {};
+  none.hd = 16;
+  return launch_fused_w<kVarF32>(h, norm_w, eps, W, out, batch, K, N, N / 16, 0, none, stream);
+}
+
+// [q k v] = rmsnorm(h) Wqkv^T, q and k rotated by table[tok_pos]; q -> q_out, k and v -> the paged cache
+// (only q when write_kv == 0). Wqkv rows: n_q heads of q, n_kv of k, n_kv of v, each hd wide; full rotation.
+extern "C" int llmie_norm_qkv_rope(const float* h, const float* norm_w, float eps, const void* W, void* q_out,
+                                   void* k_cache, void* v_cache, const float* table, const int* tok_pos,
+                                   const int* tok_seq, const int* seq_slot, const int* block_table, int max_pages,
+                                   int page_size, int batch, int n_q, int n_kv, int hd, int K, int table_len,
+                                   int write_kv, cudaStream_t stream) {
+  int rc = check_common(h, norm_w, W, batch, (n_q + 2 * n_kv) * hd, K);
+  if (rc != LLMIE_OK) return rc;
+  if (hd % 16 || n_q <= 0 || n_kv <= 0 || page_size <= 0 || max_pages <= 0 || table_len <= 0 || !table)
+    return LLMIE_ERR_BAD_ARG;
+  if (batch == 0) return LLMIE_OK;
+  RopeStoreArgs r;
+  r.q_out = (__nv_bfloat16*)q_out;
+  r.k_cache = (__nv_bfloat16*)k_cache;
+  r.v_cache = (__nv_bfloat16*)v_cache;
+  r.table = reinterpret_cast<const float2*>(table);
+  r.tok_pos = tok_pos;
+  r.tok_seq = tok_seq;
+  r.seq_slot = seq_slot;
+  r.block_table = block_table;
+  r.max_pages = max_pages;
+  r.page_size = page_size;
+  r.n_q = n_q;
+  r.n_kv = n_kv;
+  r.hd = hd;
+  r.table_len = table_len;
+  r.write_kv = write_kv;
+  const int tiles = (n_q + 2 * n_kv) * (hd / 16);
+  return launch_fused_w<kVarQkvRope>(h, norm_w, eps, W, nullptr, batch, K, 0, tiles, 0, r, stream);
+}

@@ -38,6 +38,7 @@ class StepContext:
     dtype: torch.dtype
     device: torch.device
     kernels: Optional[object] = None     # the engine's kernel choices (KernelPlan)
+    all_rows: bool = False               # logit_rows is 0..n_tokens-1: every row's logits are wanted
 
     def attention(self, q, kv, out, n_q: int, n_kv: int, head_dim: int, scale: float, window: int) -> None:
         """softmax(q k^T * scale) v over the cache unit `kv`, each token seeing the keys of its own

@@ -145,7 +145,8 @@ class Engine:
         ctx = StepContext(
             n_tokens=T, n_seqs=n, decode=max(lens) == 1, max_q_len=max(lens), max_kv_len=int(kvlen.max()),
             tokens=view[0], tok_pos=view[1], tok_seq=view[2], cu_q=view[3], seq_slot=view[4], seq_start=view[5],
-            seq_kvlen=view[6], logit_rows=view[7], dtype=self.dtype, device=self.device, kernels=self.kernels)
+            seq_kvlen=view[6], logit_rows=view[7], dtype=self.dtype, device=self.device, kernels=self.kernels,
+            all_rows=rows == list(range(T)))
         logits = self.model.forward(ctx, cache)
         ops.advance_lengths(ctx.seq_slot, ctx.seq_kvlen, cache.seq_lens, n, cache.scratch_slot)
         for s, new_len in zip(slots, kvlen):
@@ -217,7 +218,8 @@ class DecodeGraph:
         ctx = StepContext(
             n_tokens=self.n, n_seqs=self.n, decode=True, max_q_len=1, max_kv_len=e.max_seq_len, tokens=self.tokens,
             tok_pos=self.tok_pos, tok_seq=self.tok_seq, cu_q=self.cu_q, seq_slot=self.slots, seq_start=self.seq_start,
-            seq_kvlen=self.seq_kvlen, logit_rows=self.rows, dtype=e.dtype, device=e.device, kernels=e.kernels)
+            seq_kvlen=self.seq_kvlen, logit_rows=self.rows, dtype=e.dtype, device=e.device, kernels=e.kernels,
+            all_rows=True)
         logits = e.model.forward(ctx, e.cache)
         ops.advance_lengths(self.slots, self.seq_kvlen, e.cache.seq_lens, self.n, e.cache.scratch_slot)
         return logits

@@ -283,6 +283,75 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
     return out
 
 
+def norm_gemm_supported(batch: int, k: int) -> bool:
+    """Whether the fused norm + product kernels of one-token steps take this many rows and this width."""
+    return 1 <= batch <= 8 and k % 32 == 0 and 8 * (k + 32) * 2 + 12 * 1024 <= 200 * 1024
+
+
+def _norm_gemm_common(h, norm_w, w, what):
+    batch, K = h.shape
+    _need(h, "h", torch.float32)
+    _need(norm_w, "norm_w", torch.float32, (K,))
+    _need(w, "w", torch.bfloat16, (None, K))
+    if not norm_gemm_supported(batch, K):
+        raise KernelError(f"{what}: {batch} rows of width {K} are not supported")
+    return batch, K
+
+
+def norm_gate_swiglu(h, norm_w, eps: float, w_gate_up, act):
+    """act[b, j] = silu(x Wg^T) * (x Wu^T) with x = rmsnorm(h) * norm_w, in one kernel.
+    h float32 [batch <= 8, K]; w_gate_up bfloat16 [2 ff, K] = [gate rows; up rows]; act bfloat16 [batch, ff]."""
+    batch, K = _norm_gemm_common(h, norm_w, w_gate_up, "norm_gate_swiglu")
+    ff = w_gate_up.shape[0] // 2
+    _need(act, "act", torch.bfloat16, (batch, ff))
+    if w_gate_up.shape[0] % 2 or ff % 8:
+        raise KernelError("norm_gate_swiglu: the feed-forward width must be a multiple of 8")
+    f = _fn("gemm_fused_decode", "llmie_norm_gate_swiglu",
+            [_c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(h.data_ptr(), norm_w.data_ptr(), float(eps), w_gate_up.data_ptr(), act.data_ptr(), batch, ff, K,
+             _stream()), "norm_gate_swiglu")
+    return act
+
+
+def norm_gemm_f32(h, norm_w, eps: float, w, out):
+    """out[batch, N] float32 = (rmsnorm(h) * norm_w) w^T in one kernel (final norm + LM head)."""
+    batch, K = _norm_gemm_common(h, norm_w, w, "norm_gemm_f32")
+    N = w.shape[0]
+    _need(out, "out", torch.float32, (batch, N))
+    if N % 16:
+        raise KernelError("norm_gemm_f32: N must be a multiple of 16")
+    f = _fn("gemm_fused_decode", "llmie_norm_gemm_f32",
+            [_c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(h.data_ptr(), norm_w.data_ptr(), float(eps), w.data_ptr(), out.data_ptr(), batch, N, K, _stream()),
+           "norm_gemm_f32")
+    return out
+
+
+def norm_qkv_rope(h, norm_w, eps: float, w_qkv, q_out, k_cache, v_cache, table, tok_pos, tok_seq, seq_slot,
+                  block_table, page_size: int, n_q: int, n_kv: int, head_dim: int, write_kv: bool = True):
+    """RMSNorm, the packed q/k/v product, rotation of q and k and the KV-cache write in one kernel.
+    h float32 [batch <= 8, K]; w_qkv bfloat16 [(n_q + 2 n_kv) hd, K]; q_out bfloat16 [batch, n_q hd];
+    table float32 [max_pos, hd / 2, 2] (the whole head is rotated)."""
+    batch, K = _norm_gemm_common(h, norm_w, w_qkv, "norm_qkv_rope")
+    if w_qkv.shape[0] != (n_q + 2 * n_kv) * head_dim or head_dim % 16:
+        raise KernelError("norm_qkv_rope: weight rows do not match the head layout")
+    _need(q_out, "q_out", torch.bfloat16, (batch, n_q * head_dim))
+    _need(table, "table", torch.float32, (None, head_dim // 2, 2))
+    for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("seq_slot", seq_slot), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    if write_kv:
+        _need(k_cache, "k_cache", torch.bfloat16, (None, n_kv, page_size, head_dim))
+        _need(v_cache, "v_cache", torch.bfloat16, tuple(k_cache.shape))
+    f = _fn("gemm_fused_decode", "llmie_norm_qkv_rope",
+            [_c_void_p, _c_void_p, _c_float] + [_c_void_p] * 9 + [_c_int] * 9 + [_c_void_p])
+    _check(f(h.data_ptr(), norm_w.data_ptr(), float(eps), w_qkv.data_ptr(), q_out.data_ptr(),
+             _ptr(k_cache) if write_kv else None, _ptr(v_cache) if write_kv else None, table.data_ptr(),
+             tok_pos.data_ptr(), tok_seq.data_ptr(), seq_slot.data_ptr(), block_table.data_ptr(),
+             block_table.shape[1], page_size, batch, n_q, n_kv, head_dim, K, table.shape[0], 1 if write_kv else 0,
+             _stream()), "norm_qkv_rope")
+    return q_out
+
+
 _tc_status = {}
 _TC_STATUS_TEXT = {1: "a TMA load did not arrive", 2: "the tensor cores did not release a stage",
                    3: "the accumulators were not completed"}

@@ -93,5 +93,12 @@ class DecoderModel:
         for pos, call in enumerate(self.spec.schedule):
             unit = cache.unit(self.unit_of_entry[pos])
             h, pending = self.blocks[call.layer].forward(h, pending, ctx, unit, call.cache_of is None)
+        if pending is None and ctx.all_rows and self.head.weight.dtype == torch.bfloat16 \
+                and self.vocab_size % 16 == 0:
+            x = self.final_norm.defer(h)
+            if x is not None and x.kind == "rmsnorm":
+                # one-token steps: final norm and head in one kernel
+                logits = torch.empty((h.shape[0], self.vocab_size), dtype=torch.float32, device=h.device)
+                return ops.norm_gemm_f32(x.h, x.weight, x.eps, self.head.weight, logits)
         x = self.final_norm.forward(h, pending, rows=ctx.logit_rows)
         return self.head(x, out_dtype=torch.float32)

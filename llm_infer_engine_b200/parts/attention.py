@@ -14,7 +14,7 @@ import torch
 
 from ..cache.cache import KVRequest
 from ..kernels import ops
-from .base import Mixer, ParamSpec, build_part, register_mixer
+from .base import DeferredNorm, Mixer, ParamSpec, build_part, register_mixer
 from .linear import Linear
 
 
@@ -23,6 +23,7 @@ class GroupedQueryAttention(Mixer):
     window (0 = every earlier key), scale (None = 1/sqrt(head_dim))."""
 
     adds_to_residual = True
+    accepts_deferred_norm = True
 
     def __init__(self, params, runtime):
         super().__init__(params, runtime)
@@ -61,8 +62,22 @@ class GroupedQueryAttention(Mixer):
 
     def forward(self, x, ctx, unit, owns_cache, residual=None):
         kv = unit.kv
-        qkv = self.qkv(x)
-        q = self.position.encode_and_store(qkv, ctx, kv, self.n_heads, self.n_kv_heads, self.head_dim, owns_cache)
+        q = None
+        if isinstance(x, DeferredNorm):
+            table = getattr(self.position, "fused_table", lambda hd: None)(self.head_dim)
+            w = self.qkv.weight
+            if x.kind == "rmsnorm" and table is not None and w.dtype == torch.bfloat16 and kv.k.dtype == torch.bfloat16:
+                # one-token steps: norm, the three projections, rotation and the cache write in one kernel
+                q = torch.empty((x.shape[0], self.n_heads * self.head_dim), dtype=torch.bfloat16, device=w.device)
+                ops.norm_qkv_rope(x.h, x.weight, x.eps, w, q, kv.k, kv.v, table, ctx.tok_pos, ctx.tok_seq,
+                                  ctx.seq_slot, kv.block_table, kv.page_size, self.n_heads, self.n_kv_heads,
+                                  self.head_dim, owns_cache)
+            else:
+                x = x.apply()
+        if q is None:
+            qkv = self.qkv(x)
+            q = self.position.encode_and_store(qkv, ctx, kv, self.n_heads, self.n_kv_heads, self.head_dim,
+                                               owns_cache)
         out = torch.empty_like(q)
         ctx.attention(q, kv, out, self.n_heads, self.n_kv_heads, self.head_dim, self.scale, self.window)
         if residual is not None and self.o.add_into(out, residual):

@@ -64,6 +64,27 @@ class Norm(Part):
         activation dtype. With `rows`, only those rows are produced and h is untouched."""
         raise NotImplementedError
 
+    def defer(self, h: torch.Tensor) -> Optional["DeferredNorm"]:
+        """A promise of norm(h) for a consumer that can fold the norm into its own first kernel,
+        or None when this norm (or this shape) cannot be folded."""
+        return None
+
+
+class DeferredNorm:
+    """norm(h) that has not been computed. A part that declares `accepts_deferred_norm = True`
+    may receive one instead of a tensor; it either folds the norm into its first kernel (using
+    `kind`, `weight`, `eps`) or calls `apply()` and goes on with the tensor."""
+
+    def __init__(self, norm: Norm, h: torch.Tensor, kind: str, weight: torch.Tensor, eps: float):
+        self.norm, self.h, self.kind, self.weight, self.eps = norm, h, kind, weight, eps
+
+    @property
+    def shape(self):
+        return self.h.shape
+
+    def apply(self) -> torch.Tensor:
+        return self.norm.forward(self.h, None)
+
 
 class PositionEncoding(Part):
     def encode_and_store(self, qkv: torch.Tensor, ctx, kv, n_q: int, n_kv: int, head_dim: int,
@@ -146,6 +167,11 @@ def lookup(group: str, kind: str) -> type:
     if kind not in reg:
         raise KeyError(f"no {group} of kind {kind!r} is registered (known: {sorted(reg)})")
     return reg[kind]
+
+
+def undefer(x):
+    """The tensor behind x, applying a deferred norm if x is one."""
+    return x.apply() if isinstance(x, DeferredNorm) else x
 
 
 def build_part(group: str, spec, runtime: Runtime):

@@ -8,15 +8,25 @@ from .base import Block, register_block
 
 class PreNormBlock(Block):
     """A part that sets `adds_to_residual = True` accepts `residual=h` and may add its output into
-    h itself (in float32, inside its last kernel); it then returns None instead of a branch output."""
+    h itself (in float32, inside its last kernel); it then returns None instead of a branch output.
+    A part that sets `accepts_deferred_norm = True` may be handed a `DeferredNorm` instead of the
+    normalised tensor and folds the norm into its first kernel."""
 
     def forward(self, h, pending, ctx, unit, owns_cache):
-        x = self.mixer_norm.forward(h, pending)
+        x = None
+        if pending is None and getattr(self.mixer, "accepts_deferred_norm", False):
+            x = self.mixer_norm.defer(h)              # the mixer's first kernel applies the norm
+        if x is None:
+            x = self.mixer_norm.forward(h, pending)
         if getattr(self.mixer, "adds_to_residual", False):
             mixed = self.mixer.forward(x, ctx, unit, owns_cache, residual=h)
         else:
             mixed = self.mixer.forward(x, ctx, unit, owns_cache)
-        x = self.feed_forward_norm.forward(h, mixed)
+        x = None
+        if mixed is None and getattr(self.feed_forward, "accepts_deferred_norm", False):
+            x = self.feed_forward_norm.defer(h)
+        if x is None:
+            x = self.feed_forward_norm.forward(h, mixed)
         if getattr(self.feed_forward, "adds_to_residual", False):
             return h, self.feed_forward.forward(x, ctx, residual=h)
         return h, self.feed_forward.forward(x, ctx)

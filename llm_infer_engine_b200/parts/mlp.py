@@ -8,7 +8,7 @@ from typing import Dict
 import torch
 
 from ..kernels import ops
-from .base import FeedForward, ParamSpec, register_feed_forward
+from .base import DeferredNorm, FeedForward, ParamSpec, register_feed_forward
 from .linear import Linear
 
 
@@ -16,6 +16,7 @@ class SwiGLU(FeedForward):
     """params: hidden, intermediate."""
 
     adds_to_residual = True
+    accepts_deferred_norm = True
 
     def __init__(self, params, runtime):
         super().__init__(params, runtime)
@@ -39,7 +40,17 @@ class SwiGLU(FeedForward):
         return self.gate_up.nbytes() + self.down.nbytes()
 
     def forward(self, x, ctx, residual=None):
-        act = self.gate_up.swiglu(x)                 # one-token steps: product, activation and gate in one kernel
+        act = None
+        if isinstance(x, DeferredNorm):
+            w = self.gate_up.weight
+            if x.kind == "rmsnorm" and w.dtype == torch.bfloat16 and self.intermediate % 8 == 0:
+                # one-token steps: norm, product, activation and gate in one kernel
+                act = torch.empty((x.shape[0], self.intermediate), dtype=torch.bfloat16, device=w.device)
+                ops.norm_gate_swiglu(x.h, x.weight, x.eps, w, act)
+            else:
+                x = x.apply()
+        if act is None:
+            act = self.gate_up.swiglu(x)             # product, activation and gate in one kernel
         if act is None:
             gu = self.gate_up(x)
             act = torch.empty((x.shape[0], self.intermediate), dtype=gu.dtype, device=x.device)

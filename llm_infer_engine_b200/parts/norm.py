@@ -10,7 +10,7 @@ from typing import Dict, Optional
 import torch
 
 from ..kernels import ops
-from .base import Norm, ParamSpec, register_norm
+from .base import DeferredNorm, Norm, ParamSpec, register_norm
 
 
 class RMSNorm(Norm):
@@ -30,6 +30,12 @@ class RMSNorm(Norm):
 
     def weight_bytes(self) -> int:
         return self.size * 4
+
+    def defer(self, h):
+        """One-token steps of the bfloat16 engine: the next product's kernel applies this norm itself."""
+        if self.runtime.dtype != torch.bfloat16 or not ops.norm_gemm_supported(h.shape[0], self.size):
+            return None
+        return DeferredNorm(self, h, "rmsnorm", self.weight, self.eps)
 
     def forward(self, h, delta, out=None, rows=None):
         n_out = h.shape[0] if rows is None else rows.shape[0]

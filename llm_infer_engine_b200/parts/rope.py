@@ -60,6 +60,11 @@ class RotaryEncoding(PositionEncoding):
         table = torch.stack([torch.cos(angle), torch.sin(angle)], dim=-1)       # [P, rot/2, 2]
         self.table = table.contiguous().to(runtime.device)
 
+    def fused_table(self, head_dim: int):
+        """The (cos, sin) table, if a product kernel may apply this encoding in its own epilogue:
+        that needs the whole head to be rotated."""
+        return self.table if self.rot_dim == head_dim else None
+
     def encode_and_store(self, qkv, ctx, kv, n_q, n_kv, head_dim, write_kv):
         q = torch.empty((qkv.shape[0], n_q * head_dim), dtype=qkv.dtype, device=qkv.device)
         ops.rope_store(qkv, q, kv.k if kv is not None else None, kv.v if kv is not None else None, self.table,

@@ -410,3 +410,71 @@ def test_attention_prefill_tc(n_q, n_kv, hd):
         assert torch.allclose(out.float(), plain_out.float(), atol=2e-2, rtol=1.6e-2)
         if window == 0:
             assert float(got[qi, ::G].mean()) > 4.5
+
+
+# ------------------------------------------------------------------------------------------ fused one-token kernels
+@pytest.mark.parametrize("batch", [1, 3, 8])
+@pytest.mark.parametrize("K,ff", [(64, 96), (160, 224), (2048, 8192), (96, 256)])
+def test_norm_gate_swiglu(batch, K, ff):
+    o = ops()
+    g = torch.Generator().manual_seed(batch + K)
+    h = torch.randn(batch, K, generator=g) * 2
+    nw = torch.rand(K, generator=g) + 0.5
+    w = (torch.randn(2 * ff, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    eps = 1e-5
+    assert o.norm_gemm_supported(batch, K)
+    act = torch.full((batch, ff), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o.norm_gate_swiglu(h.to(DEV), nw.to(DEV), eps, w.to(DEV), act)
+    x = plain.rms_norm(h, nw, eps)
+    y = x.double() @ w.double().T
+    want = (y[:, :ff] * torch.sigmoid(y[:, :ff]) * y[:, ff:]).float()
+    assert torch.allclose(act.float().cpu(), want, atol=3e-2, rtol=3e-2), float((act.float().cpu() - want).abs().max())
+
+
+@pytest.mark.parametrize("batch,N,K", [(1, 256, 64), (5, 384, 96), (8, 128256, 2048), (2, 512, 160)])
+def test_norm_gemm_f32(batch, N, K):
+    o = ops()
+    g = torch.Generator().manual_seed(batch + N)
+    h = torch.randn(batch, K, generator=g) * 3
+    nw = torch.rand(K, generator=g) + 0.5
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    out = torch.full((batch, N), float("nan"), dtype=torch.float32, device=DEV)
+    o.norm_gemm_f32(h.to(DEV), nw.to(DEV), 1e-6, w.to(DEV), out)
+    want = (plain.rms_norm(h, nw, 1e-6).double() @ w.double().T).float()
+    assert torch.allclose(out.cpu(), want, atol=2e-2, rtol=2e-2), float((out.cpu() - want).abs().max())
+
+
+@pytest.mark.parametrize("batch", [1, 4, 8])
+@pytest.mark.parametrize("n_q,n_kv,hd,K", [(4, 2, 16, 64), (3, 1, 32, 96), (6, 2, 64, 160), (32, 8, 64, 2048), (4, 1, 128, 256)])
+def test_norm_qkv_rope(batch, n_q, n_kv, hd, K):
+    """Against the unfused pair: norm kernel + product + rotary/cache-write kernel."""
+    o = ops()
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(batch * 7 + hd)
+    starts = [int(x) for x in torch.randint(0, 150, (batch,), generator=g)]
+    pg = Paged([s + 1 for s in starts], n_kv, hd, dtype, seed=hd)
+    k_dev, v_dev, bt = pg.dev()
+    k2, v2 = k_dev.clone(), v_dev.clone()
+    h = torch.randn(batch, K, generator=g) * 2
+    nw = torch.rand(K, generator=g) + 0.5
+    w = (torch.randn((n_q + 2 * n_kv) * hd, K, generator=g) / math.sqrt(K)).to(dtype)
+    inv = plain.inv_frequencies(hd, 10000.0, None)
+    cos, sin = plain.rotation_tables(torch.arange(256), inv)
+    table = torch.stack([cos, sin], dim=-1).contiguous().to(DEV)
+    tok_pos = torch.tensor(starts, dtype=torch.int32, device=DEV)
+    tok_seq = torch.arange(batch, dtype=torch.int32, device=DEV)
+    slots = torch.tensor(pg.slots, dtype=torch.int32, device=DEV)
+    q = torch.full((batch, n_q * hd), float("nan"), dtype=dtype, device=DEV)
+    o.norm_qkv_rope(h.to(DEV), nw.to(DEV), 1e-5, w.to(DEV), q, k_dev, v_dev, table, tok_pos, tok_seq, slots, bt, 64,
+                    n_q, n_kv, hd)
+    # the unfused path
+    xn = torch.empty(batch, K, dtype=dtype, device=DEV)
+    o.add_rmsnorm(h.clone().to(DEV), None, nw.to(DEV), 1e-5, xn)
+    qkv = (xn.float() @ w.to(DEV).float().T).to(dtype)
+    q2 = torch.empty_like(q)
+    o.rope_store(qkv, q2, k2, v2, table, tok_pos, tok_seq, slots, bt, 64, n_q, n_kv, hd, hd)
+    assert torch.allclose(q.float(), q2.float(), atol=3e-2, rtol=3e-2), float((q.float() - q2.float()).abs().max())
+    assert torch.allclose(k_dev.float(), k2.float(), atol=3e-2, rtol=3e-2)
+    assert torch.allclose(v_dev.float(), v2.float(), atol=3e-2, rtol=3e-2)
+    # and it wrote exactly the cache rows the unfused path wrote
+    assert torch.equal((k_dev != pg.dev()[0]).any(-1), (k2 != pg.dev()[0]).any(-1))
