@@ -1,6 +1,6 @@
 // Split-KV attention for one-token steps over the paged cache.
 //
-// The reference splits the keys of a sequence into runs of 256, computes a partial
+// The reference splits the keys of a sequence into runs of 256 (here: runs of one cache page, 64 keys), computes a partial
 // (max, sum, accumulator) per (sequence, query head, run) and merges the runs with a
 // log-sum-exp (src/flash_decode.py:8-137 and :140-212); every query head re-reads its KV head.
 // Here one block serves ALL query heads of a KV head for its run of keys, so the cache is
@@ -41,6 +41,10 @@ __device__ __forceinline__ int first_visible(int len, int window) {
   return (window > 0 && len - window > 0) ? len - window : 0;
 }
 
+// One block = one cache page (64 keys) of one KV head of one sequence, for all its query heads.
+// The page's K and V rows are contiguous in the cache, so the block asks for all of both at once
+// (every 16-byte load of the page is issued before anything is computed): one memory latency per
+// block instead of one per key. run_len must equal the page size.
 template <typename T, int HD, int GMAX>
 __global__ void __launch_bounds__(kDecThreads)
 decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
@@ -53,8 +57,11 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, cons
   constexpr int E = Vec16<T>::E;
   constexpr int LPK = HD / E;          // lanes per key
   constexpr int KPW = 32 / LPK;        // keys per warp per iteration
-  static_assert(LPK >= 1 && LPK <= 32 && 32 % LPK == 0, "head size not supported by this kernel");
-  extern __shared__ float smem[];      // scores [GMAX][run_len], then reduction [kDecWarps][GMAX][HD]
+  constexpr int kRun = 64;             // keys per block = one page
+  constexpr int kIter = kRun / (kDecWarps * KPW);
+  static_assert(LPK >= 1 && LPK <= 32 && 32 % LPK == 0 && kIter >= 1, "head size not supported by this kernel");
+  __shared__ float scores[GMAX][kRun];
+  __shared__ float red[kDecWarps][GMAX][HD];
 
   const int run = blockIdx.x, seq = blockIdx.z;
   const int G = n_q / n_kv;
@@ -65,18 +72,32 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, cons
 
   const int len = seq_kvlen[seq];
   const int lo = first_visible(len, window);
-  const int begin = max(run * run_len, lo);
-  const int end = min(len, (run + 1) * run_len);
+  const int begin = max(run * kRun, lo);
+  const int end = min(len, (run + 1) * kRun);
   if (begin >= end) return;
-  const int n_keys = end - begin;
+  const int first = begin - run * kRun, n_keys = end - begin;      // keys [first, first + n_keys) of the page
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane / LPK;          // which of the warp's KPW keys
   const int e0 = (lane % LPK) * E;     // first element of this lane's slice
-  const int* pages = block_table + (size_t)seq_slot[seq] * max_pages;
-  float* scores = smem;                                  // [GMAX][run_len]
-  float* red = smem + GMAX * run_len;                    // [kDecWarps][GMAX][HD]
+  const int page = block_table[(size_t)seq_slot[seq] * max_pages + run];
+  const size_t page_base = ((size_t)page * n_kv + hk) * (size_t)page_size * HD;
+  const T* kp = k_cache + page_base;
+  const T* vp = v_cache + page_base;
 
+  // every load of this block, K and V, is requested here; rows outside [first, first + n_keys) hold
+  // other positions of the page (never another sequence's) and are simply not used
+  float kv[kIter][E], vv[kIter][E];
+#pragma unroll
+  for (int it = 0; it < kIter; ++it) {
+    const int row = (it * kDecWarps + warp) * KPW + sub;
+    load_vec<T, E>(kp + (size_t)row * HD + e0, kv[it]);
+  }
+#pragma unroll
+  for (int it = 0; it < kIter; ++it) {
+    const int row = (it * kDecWarps + warp) * KPW + sub;
+    load_vec<T, E>(vp + (size_t)row * HD + e0, vv[it]);
+  }
   // this lane's slice of each query head, pre-scaled
   float qv[GMAX][E];
 #pragma unroll
@@ -93,37 +114,35 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, cons
     }
   }
 
-  // ---- phase 1: scores
-  // the loop bound is the same for every lane of a warp (the shuffles below need all of them)
-  for (int jb = warp * KPW; jb < n_keys; jb += kDecWarps * KPW) {
-    const int j = jb + sub;
-    const bool valid = j < n_keys;
-    const int pos = begin + (valid ? j : 0);
-    const int page = pages[pos / page_size];
-    const T* kp = k_cache + (((size_t)page * n_kv + hk) * page_size + (pos % page_size)) * HD + e0;
-    float kv[E];
-    load_vec<T, E>(kp, kv);
+  // ---- phase 1: scores of the page's rows
+#pragma unroll
+  for (int it = 0; it < kIter; ++it) {
+    const int row = (it * kDecWarps + warp) * KPW + sub;
 #pragma unroll
     for (int g = 0; g < GMAX; ++g) {
       float dot = 0.f;
 #pragma unroll
-      for (int e = 0; e < E; ++e) dot = fmaf(qv[g][e], kv[e], dot);
+      for (int e = 0; e < E; ++e) dot = fmaf(qv[g][e], kv[it][e], dot);
 #pragma unroll
       for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      if (valid && (lane % LPK) == 0 && g < ng) scores[g * run_len + j] = dot;
+      if ((lane % LPK) == 0 && g < ng) scores[g][row] = dot;
     }
   }
   __syncthreads();
 
-  // ---- phase 2: softmax statistics per head; scores become probabilities
+  // ---- phase 2: softmax statistics per head over the visible rows; scores become probabilities
   for (int g = warp; g < ng; g += kDecWarps) {
-    float* s = scores + g * run_len;
+    float* s = scores[g];
     float m = -INFINITY;
-    for (int j = lane; j < n_keys; j += 32) m = fmaxf(m, s[j]);
+    for (int j = lane; j < kRun; j += 32) {
+      const bool vis = j >= first && j < first + n_keys;
+      m = fmaxf(m, vis ? s[j] : -INFINITY);
+    }
     m = warp_max(m);
     float l = 0.f;
-    for (int j = lane; j < n_keys; j += 32) {
-      const float p = expf(s[j] - m);
+    for (int j = lane; j < kRun; j += 32) {
+      const bool vis = j >= first && j < first + n_keys;
+      const float p = vis ? expf(s[j] - m) : 0.f;
       s[j] = p;
       l += p;
     }
@@ -142,17 +161,14 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, cons
   for (int g = 0; g < GMAX; ++g)
 #pragma unroll
     for (int e = 0; e < E; ++e) acc[g][e] = 0.f;
-  for (int j = warp * KPW + sub; j < n_keys; j += kDecWarps * KPW) {
-    const int pos = begin + j;
-    const int page = pages[pos / page_size];
-    const T* vp = v_cache + (((size_t)page * n_kv + hk) * page_size + (pos % page_size)) * HD + e0;
-    float vv[E];
-    load_vec<T, E>(vp, vv);
+#pragma unroll
+  for (int it = 0; it < kIter; ++it) {
+    const int row = (it * kDecWarps + warp) * KPW + sub;
 #pragma unroll
     for (int g = 0; g < GMAX; ++g) {
-      const float p = (g < ng) ? scores[g * run_len + j] : 0.f;
+      const float p = (g < ng) ? scores[g][row] : 0.f;
 #pragma unroll
-      for (int e = 0; e < E; ++e) acc[g][e] = fmaf(p, vv[e], acc[g][e]);
+      for (int e = 0; e < E; ++e) acc[g][e] = fmaf(p, vv[it][e], acc[g][e]);
     }
   }
   // lanes with the same element slice (same lane % LPK) hold different keys: add them up
@@ -166,14 +182,14 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, cons
 #pragma unroll
     for (int g = 0; g < GMAX; ++g)
 #pragma unroll
-      for (int e = 0; e < E; ++e) red[(warp * GMAX + g) * HD + e0 + e] = acc[g][e];
+      for (int e = 0; e < E; ++e) red[warp][g][e0 + e] = acc[g][e];
   }
   __syncthreads();
   for (int i = threadIdx.x; i < ng * HD; i += kDecThreads) {
     const int g = i / HD, d = i % HD;
     float sum = 0.f;
 #pragma unroll
-    for (int w = 0; w < kDecWarps; ++w) sum += red[(w * GMAX + g) * HD + d];
+    for (int w = 0; w < kDecWarps; ++w) sum += red[w][g][d];
     part_acc[(((size_t)seq * n_q + (size_t)hk * G + g0 + g) * n_runs + run) * HD + d] = sum;
   }
 }
@@ -211,13 +227,7 @@ static int launch_split(const void* q, const void* k_cache, const void* v_cache,
                         int run_len, int n_runs, cudaStream_t stream) {
   const int G = n_q / n_kv;
   const int chunks = (G + GMAX - 1) / GMAX;
-  const size_t smem = ((size_t)GMAX * run_len + (size_t)kDecWarps * GMAX * HD) * sizeof(float);
-  if (smem > 200 * 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(decode_split_kernel<T, HD, GMAX>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  const size_t smem = 0;
   dim3 grid(n_runs, n_kv * chunks, n_seqs);
   launch_k(decode_split_kernel<T, HD, GMAX>, dim3(grid), dim3(kDecThreads), smem, stream, 
       (const T*)q, (const T*)k_cache, (const T*)v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen, block_table,
@@ -278,7 +288,8 @@ extern "C" int llmie_attention_decode(const void* q, const void* k_cache, const 
                                       int n_seqs, int n_q, int n_kv, int hd, float scale, int window, int run_len,
                                       int n_runs, int dtype, cudaStream_t stream) {
   if (n_seqs < 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv || page_size <= 0 || max_pages <= 0) return LLMIE_ERR_BAD_ARG;
-  if (run_len <= 0 || n_runs <= 0 || run_len % 32) return LLMIE_ERR_BAD_ARG;
+  if (n_runs <= 0) return LLMIE_ERR_BAD_ARG;
+  if (run_len != 64 || page_size != 64) return LLMIE_ERR_UNSUPPORTED_SIZE;     // a run is one cache page
   if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache)) return LLMIE_ERR_ALIGNMENT;
   if (n_seqs == 0) return LLMIE_OK;
   if (n_seqs > 65535 || n_runs > 0x7fffffff / 1) return LLMIE_ERR_UNSUPPORTED_SIZE;

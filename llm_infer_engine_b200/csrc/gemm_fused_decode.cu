@@ -263,44 +263,56 @@ norm_gemm_kernel(const float* __restrict__ h, const float* __restrict__ norm_w, 
 }
 
 template <int VAR, int WARPS>
+static size_t fused_smem(int K) {
+  return (size_t)8 * (K + kFdPad) * 2 + (size_t)(WARPS * 16 * 9 + WARPS * 8 + 8) * sizeof(float);
+}
+
+// Blocks of this instance that one SM holds at once (0 if it cannot run at all with this K).
+template <int VAR, int WARPS>
+static int fused_blocks_per_sm(int K) {
+  static int cached_k = -1, cached = 0;
+  if (cached_k != K) {
+    const size_t smem = fused_smem<VAR, WARPS>(K);
+    int n = 0;
+    if (smem <= 200 * 1024) {
+      if (smem > 48 * 1024)
+        cudaFuncSetAttribute(norm_gemm_kernel<VAR, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, norm_gemm_kernel<VAR, WARPS>, WARPS * 32, smem) != cudaSuccess)
+        n = 0;
+    }
+    cached = n;
+    cached_k = K;
+  }
+  return cached;
+}
+
+template <int VAR, int WARPS>
 static int launch_fused(const float* h, const float* norm_w, float eps, const void* W, void* out, int batch, int K,
                         int ldo, int tiles, int half_n, const RopeStoreArgs& rope, cudaStream_t stream) {
-  const size_t smem = (size_t)8 * (K + kFdPad) * 2 + (size_t)(WARPS * 16 * 9 + WARPS * 8 + 8) * sizeof(float);
-  if (smem > 200 * 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(norm_gemm_kernel<VAR, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  const int per_sm = fused_blocks_per_sm<VAR, WARPS>(K);
+  if (per_sm < 1) return LLMIE_ERR_UNSUPPORTED_SIZE;
   // as many blocks as stay resident together, evenly loaded: a block walks its tiles with the
   // staged rows in place
-  static int per_sm_cached = 0;           // one value per template instance
-  static size_t per_sm_smem = 0;
-  if (per_sm_cached == 0 || per_sm_smem != smem) {
-    int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, norm_gemm_kernel<VAR, WARPS>, WARPS * 32, smem) !=
-            cudaSuccess || n < 1)
-      n = 1;
-    per_sm_cached = n;
-    per_sm_smem = smem;
-  }
-  const int resident = 148 * per_sm_cached;
+  const int resident = 148 * per_sm;
   const int waves = (tiles + resident - 1) / resident;
   const int blocks = (tiles + waves - 1) / waves;
-  launch_k(norm_gemm_kernel<VAR, WARPS>, dim3(blocks), dim3(WARPS * 32), smem, stream, h, norm_w, eps,
-           (const __nv_bfloat16*)W, out, batch, K, ldo, tiles, half_n, rope);
+  launch_k(norm_gemm_kernel<VAR, WARPS>, dim3(blocks), dim3(WARPS * 32), fused_smem<VAR, WARPS>(K), stream, h, norm_w,
+           eps, (const __nv_bfloat16*)W, out, batch, K, ldo, tiles, half_n, rope);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }
 
+// Warps per block: the most (16, 8, 4) with which every tile still gets a block of its own in one
+// wave and every warp has work; matrices with more tiles than that take 8 warps and several tiles
+// per block.
 template <int VAR>
 static int launch_fused_w(const float* h, const float* norm_w, float eps, const void* W, void* out, int batch, int K,
                           int ldo, int tiles, int half_n, const RopeStoreArgs& rope, cudaStream_t stream) {
   const int chunks = K / 32;
-  int warps = 4;
-  while (warps < 16 && tiles * warps < 148 * 16 && chunks >= warps * 2 * kFdUnroll) warps *= 2;
-  if (warps >= 16) return launch_fused<VAR, 16>(h, norm_w, eps, W, out, batch, K, ldo, tiles, half_n, rope, stream);
-  if (warps >= 8) return launch_fused<VAR, 8>(h, norm_w, eps, W, out, batch, K, ldo, tiles, half_n, rope, stream);
+  if (chunks >= 16 * kFdUnroll && tiles <= 148 * fused_blocks_per_sm<VAR, 16>(K))
+    return launch_fused<VAR, 16>(h, norm_w, eps, W, out, batch, K, ldo, tiles, half_n, rope, stream);
+  if (chunks >= 8 * kFdUnroll && (tiles <= 148 * fused_blocks_per_sm<VAR, 8>(K) || chunks >= 16 * kFdUnroll))
+    return launch_fused<VAR, 8>(h, norm_w, eps, W, out, batch, K, ldo, tiles, half_n, rope, stream);
   return launch_fused<VAR, 4>(h, norm_w, eps, W, out, batch, K, ldo, tiles, half_n, rope, stream);
 }
 

@@ -16,14 +16,10 @@ class KernelPlan:
 
     @staticmethod
     def decode_run_length(n_seqs: int, n_kv_heads: int, max_kv_len: int) -> int:
-        """Keys per block of the split-KV kernel: short runs when few (sequence, kv head) pairs
-        exist, so that the GPU still fills; 256 as in the reference otherwise
-        (src/flash_decode.py:271-272). Depends only on the step's shape, never on its data."""
-        pairs = max(1, n_seqs * n_kv_heads)
-        run = 256
-        while run > 64 and pairs * ((max_kv_len + run - 1) // run) < 2 * 148:
-            run //= 2
-        return run
+        """Keys per block of the split-KV kernel: one cache page. A page's keys and values are
+        contiguous, so a block requests all of them at once; the reference uses runs of 256
+        (src/flash_decode.py:271-272). Depends on nothing in the step's data."""
+        return 64
 
     def attention(self, ctx, q, kv, out, n_q, n_kv, head_dim, scale, window) -> bool:
         """Returns True when a specialised kernel ran."""

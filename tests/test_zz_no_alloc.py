@@ -45,7 +45,7 @@ def test_no_alloc_matches_ordinary_entry_point_twice(dtype):
     from llm_infer_engine_b200.kernels import ops
     fn, capacity = _symbol()
     assert capacity == 16 * 1024 * 1024
-    n_q, n_kv, hd, run_len = 12, 4, 64, 128
+    n_q, n_kv, hd, run_len = 12, 4, 64, 64
     code = 0 if dtype == torch.float32 else 1
     # two calls in a row with different data and different shapes: the second finds the first's
     # leftovers in the shared array and must not be disturbed by them
