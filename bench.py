@@ -135,7 +135,7 @@ def time_decode(engine, batch: int, steps: int, warmup: int, seed: int):
         logits = engine.step(slots, prompts, "last")
         sampled = torch.empty(batch, dtype=torch.int32, device=engine.device)
         ops.sample(logits, sampled)
-        graph = engine.decode_graph(bucket_for(batch))
+        graph = engine.decode_graph(bucket_for(batch), PROMPT_LEN + warmup + steps + 1)
         graph.set_lanes(slots)
         graph.tokens[:batch].copy_(sampled)
 

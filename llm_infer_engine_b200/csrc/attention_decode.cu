@@ -51,13 +51,15 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, cons
                     float* __restrict__ part_m, float* __restrict__ part_l, float* __restrict__ part_acc,
                     const int* __restrict__ seq_slot, const int* __restrict__ seq_kvlen,
                     const int* __restrict__ block_table, int max_pages, int page_size, int n_q, int n_kv,
-                    float scale, int window, int run_len, int n_runs) {
+                    float scale, int window, int run_len, int n_runs, int* __restrict__ counters,
+                    T* __restrict__ out) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int E = Vec16<T>::E;
   constexpr int LPK = HD / E;          // lanes per key
   constexpr int KPW = 32 / LPK;        // keys per warp per iteration
   constexpr int kRun = 64;             // keys per block = one page
+  __shared__ int is_last;
   constexpr int kIter = kRun / (kDecWarps * KPW);
   static_assert(LPK >= 1 && LPK <= 32 && 32 % LPK == 0 && kIter >= 1, "head size not supported by this kernel");
   __shared__ float scores[GMAX][kRun];
@@ -192,6 +194,73 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, cons
     for (int w = 0; w < kDecWarps; ++w) sum += red[w][g][d];
     part_acc[(((size_t)seq * n_q + (size_t)hk * G + g0 + g) * n_runs + run) * HD + d] = sum;
   }
+  if (counters == nullptr) return;     // a separate kernel merges the runs
+
+  // ---- the block that finishes last for this (sequence, head group) merges the runs
+  // (src/flash_decode.py:182-205): M = max m_r, w_r = exp(m_r - M), out = sum w_r acc_r / sum w_r l_r,
+  // over the runs that hold a visible key, in run order, whichever block does it.
+  const int r0 = lo / kRun, r1 = (len - 1) / kRun;
+  __threadfence();                     // this block's partials are visible before it is counted
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* c = counters + (size_t)seq * gridDim.y + blockIdx.y;
+    const int done = atomicAdd(c, 1) + 1;
+    is_last = (done == r1 - r0 + 1);
+    if (is_last) *c = 0;               // left clean for the next launch
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // weights of the runs, 64 runs at a time (they sit where the scores were), then every thread
+  // owns output elements and walks the runs with independent loads
+  __shared__ float head_max[GMAX], head_inv[GMAX];
+  for (int g = warp; g < ng; g += kDecWarps) {
+    const size_t base = ((size_t)seq * n_q + (size_t)hk * G + g0 + g) * n_runs;
+    float M = -INFINITY;
+    for (int r = r0 + lane; r <= r1; r += 32) M = fmaxf(M, part_m[base + r]);
+    M = warp_max(M);
+    float denom = 0.f;
+    for (int r = r0 + lane; r <= r1; r += 32) denom += expf(part_m[base + r] - M) * part_l[base + r];
+    denom = warp_sum(denom);
+    if (lane == 0) {
+      head_max[g] = M;
+      head_inv[g] = 1.f / denom;
+    }
+  }
+  constexpr int kItems = (GMAX * HD + kDecThreads - 1) / kDecThreads;
+  float num[kItems];
+#pragma unroll
+  for (int i = 0; i < kItems; ++i) num[i] = 0.f;
+  for (int c0 = r0; c0 <= r1; c0 += kRun) {
+    const int n_here = min(kRun, r1 - c0 + 1);
+    __syncthreads();
+    for (int i = threadIdx.x; i < ng * n_here; i += kDecThreads) {
+      const int g = i / n_here, r = i - g * n_here;
+      const size_t base = ((size_t)seq * n_q + (size_t)hk * G + g0 + g) * n_runs;
+      scores[g][r] = expf(part_m[base + c0 + r] - head_max[g]);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+      const int item = threadIdx.x + i * kDecThreads;
+      if (item < ng * HD) {
+        const int g = item / HD, d = item - g * HD;
+        const float* pa = part_acc + (((size_t)seq * n_q + (size_t)hk * G + g0 + g) * n_runs + c0) * HD + d;
+        float a = num[i];
+#pragma unroll 8
+        for (int r = 0; r < n_here; ++r) a = fmaf(scores[g][r], pa[(size_t)r * HD], a);
+        num[i] = a;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kItems; ++i) {
+    const int item = threadIdx.x + i * kDecThreads;
+    if (item < ng * HD) {
+      const int g = item / HD, d = item - g * HD;
+      out[((size_t)seq * n_q + (size_t)hk * G + g0 + g) * HD + d] = from_f32<T>(num[i] * head_inv[g]);
+    }
+  }
 }
 
 // Merge of the runs (src/flash_decode.py:182-205): M = max m_r, w_r = exp(m_r - M),
@@ -224,14 +293,14 @@ template <typename T, int HD, int GMAX>
 static int launch_split(const void* q, const void* k_cache, const void* v_cache, float* part_m, float* part_l,
                         float* part_acc, const int* seq_slot, const int* seq_kvlen, const int* block_table,
                         int max_pages, int page_size, int n_seqs, int n_q, int n_kv, float scale, int window,
-                        int run_len, int n_runs, cudaStream_t stream) {
+                        int run_len, int n_runs, int* counters, void* out, cudaStream_t stream) {
   const int G = n_q / n_kv;
   const int chunks = (G + GMAX - 1) / GMAX;
   const size_t smem = 0;
   dim3 grid(n_runs, n_kv * chunks, n_seqs);
   launch_k(decode_split_kernel<T, HD, GMAX>, dim3(grid), dim3(kDecThreads), smem, stream, 
       (const T*)q, (const T*)k_cache, (const T*)v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen, block_table,
-      max_pages, page_size, n_q, n_kv, scale, window, run_len, n_runs);
+      max_pages, page_size, n_q, n_kv, scale, window, run_len, n_runs, counters, (T*)out);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }
@@ -240,24 +309,28 @@ template <typename T, int HD>
 static int launch_split_g(int G, const void* q, const void* k_cache, const void* v_cache, float* part_m,
                           float* part_l, float* part_acc, const int* seq_slot, const int* seq_kvlen,
                           const int* block_table, int max_pages, int page_size, int n_seqs, int n_q, int n_kv,
-                          float scale, int window, int run_len, int n_runs, cudaStream_t stream) {
+                          float scale, int window, int run_len, int n_runs, int* counters, void* out,
+                          cudaStream_t stream) {
   if (G <= 4)
     return launch_split<T, HD, 4>(q, k_cache, v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen, block_table,
-                                  max_pages, page_size, n_seqs, n_q, n_kv, scale, window, run_len, n_runs, stream);
+                                  max_pages, page_size, n_seqs, n_q, n_kv, scale, window, run_len, n_runs, counters,
+                                  out, stream);
   return launch_split<T, HD, 8>(q, k_cache, v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen, block_table,
-                                max_pages, page_size, n_seqs, n_q, n_kv, scale, window, run_len, n_runs, stream);
+                                max_pages, page_size, n_seqs, n_q, n_kv, scale, window, run_len, n_runs, counters, out,
+                                stream);
 }
 
 template <typename T>
 static int launch_split_hd(int hd, int G, const void* q, const void* k_cache, const void* v_cache, float* part_m,
                            float* part_l, float* part_acc, const int* seq_slot, const int* seq_kvlen,
                            const int* block_table, int max_pages, int page_size, int n_seqs, int n_q, int n_kv,
-                           float scale, int window, int run_len, int n_runs, cudaStream_t stream) {
+                           float scale, int window, int run_len, int n_runs, int* counters, void* out,
+                           cudaStream_t stream) {
 #define LLMIE_CASE(HD)                                                                                          \
   case HD:                                                                                                      \
     return launch_split_g<T, HD>(G, q, k_cache, v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen,          \
                                  block_table, max_pages, page_size, n_seqs, n_q, n_kv, scale, window, run_len,  \
-                                 n_runs, stream);
+                                 n_runs, counters, out, stream);
   switch (hd) {
     LLMIE_CASE(16)
     LLMIE_CASE(32)
@@ -298,11 +371,11 @@ extern "C" int llmie_attention_decode(const void* q, const void* k_cache, const 
   if (dtype == LLMIE_F32)
     rc = launch_split_hd<float>(hd, G, q, k_cache, v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen,
                                 block_table, max_pages, page_size, n_seqs, n_q, n_kv, scale, window, run_len, n_runs,
-                                stream);
+                                nullptr, nullptr, stream);
   else if (dtype == LLMIE_BF16)
     rc = launch_split_hd<__nv_bfloat16>(hd, G, q, k_cache, v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen,
                                         block_table, max_pages, page_size, n_seqs, n_q, n_kv, scale, window, run_len,
-                                        n_runs, stream);
+                                        n_runs, nullptr, nullptr, stream);
   else
     return LLMIE_ERR_DTYPE;
   if (rc != LLMIE_OK) return rc;
@@ -316,6 +389,34 @@ extern "C" int llmie_attention_decode(const void* q, const void* k_cache, const 
                                                                      seq_kvlen, n_q, hd, window, run_len, n_runs);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
+}
+
+// The same in ONE launch: the block that finishes last for a (sequence, KV head) merges its runs.
+// counters: int32 [n_seqs * n_kv * ceil(G / 4 or 8)], all zero before the first call; every launch
+// leaves them zero again. Launches that share `counters` must not overlap on the GPU.
+extern "C" int llmie_attention_decode_fused(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                            float* part_m, float* part_l, float* part_acc, int* counters,
+                                            const int* seq_slot, const int* seq_kvlen, const int* block_table,
+                                            int max_pages, int page_size, int n_seqs, int n_q, int n_kv, int hd,
+                                            float scale, int window, int run_len, int n_runs, int dtype,
+                                            cudaStream_t stream) {
+  if (n_seqs < 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv || page_size <= 0 || max_pages <= 0 || !counters)
+    return LLMIE_ERR_BAD_ARG;
+  if (n_runs <= 0) return LLMIE_ERR_BAD_ARG;
+  if (run_len != 64 || page_size != 64) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache)) return LLMIE_ERR_ALIGNMENT;
+  if (n_seqs == 0) return LLMIE_OK;
+  if (n_seqs > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  const int G = n_q / n_kv;
+  if (dtype == LLMIE_F32)
+    return launch_split_hd<float>(hd, G, q, k_cache, v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen,
+                                  block_table, max_pages, page_size, n_seqs, n_q, n_kv, scale, window, run_len, n_runs,
+                                  counters, out, stream);
+  if (dtype == LLMIE_BF16)
+    return launch_split_hd<__nv_bfloat16>(hd, G, q, k_cache, v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen,
+                                          block_table, max_pages, page_size, n_seqs, n_q, n_kv, scale, window, run_len,
+                                          n_runs, counters, out, stream);
+  return LLMIE_ERR_DTYPE;
 }
 
 // ------------------------------------------------------------------------------------------

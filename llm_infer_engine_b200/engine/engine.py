@@ -69,7 +69,7 @@ class Engine:
         self.use_cuda_graph = bool(cuda_graph)
         from .plan import KernelPlan
         self.kernels = KernelPlan(self)
-        self._graphs: Dict[int, "DecodeGraph"] = {}
+        self._graphs: Dict[tuple, "DecodeGraph"] = {}
         self.launches = 0
 
     # ---------------------------------------------------------------- sequences
@@ -154,11 +154,15 @@ class Engine:
         return logits
 
     # ---------------------------------------------------------------- captured one-token step
-    def decode_graph(self, n_lanes: int) -> "DecodeGraph":
-        g = self._graphs.get(n_lanes)
+    def decode_graph(self, n_lanes: int, kv_len: Optional[int] = None) -> "DecodeGraph":
+        """The captured one-token step for `n_lanes` sequences none of which holds more than `kv_len`
+        tokens after the step (default: the engine's limit). Kept per (lanes, length bucket): the
+        attention grid of a captured step is sized for the bucket, not for the longest possible sequence."""
+        limit = kv_bucket_for(self.max_seq_len if kv_len is None else kv_len, self.max_seq_len)
+        g = self._graphs.get((n_lanes, limit))
         if g is None:
-            g = DecodeGraph(self, n_lanes)
-            self._graphs[n_lanes] = g
+            g = DecodeGraph(self, n_lanes, limit)
+            self._graphs[(n_lanes, limit)] = g
         return g
 
     def weight_bytes_per_step(self) -> int:
@@ -186,15 +190,24 @@ def bucket_for(n: int) -> int:
     return n
 
 
+def kv_bucket_for(kv_len: int, limit: int) -> int:
+    """Length buckets of captured steps: 512, 1024, 2048, ... capped by the engine's limit."""
+    b = 512
+    while b < kv_len:
+        b *= 2
+    return min(b, limit)
+
+
 class DecodeGraph:
     """One captured one-token step for `n_lanes` sequences. Inputs live in device buffers:
     `tokens[n_lanes]`, `slots[n_lanes]` (padding lanes name the scratch slot), and the lengths in
     the cache's `seq_lens`; the step derives positions from them, so replaying needs no host
     writes beyond the two buffers when the set of sequences changes. `logits` is [n_lanes, vocab]."""
 
-    def __init__(self, engine: Engine, n_lanes: int):
+    def __init__(self, engine: Engine, n_lanes: int, kv_limit: Optional[int] = None):
         self.engine = engine
         self.n = n_lanes
+        self.kv_limit = engine.max_seq_len if kv_limit is None else kv_limit     # lengths this capture serves
         dev = engine.device
         cache = engine.cache
         i32 = dict(dtype=torch.int32, device=dev)
@@ -216,7 +229,7 @@ class DecodeGraph:
         ops.prepare_decode(self.slots, e.cache.seq_lens, self.tok_pos, self.tok_seq, self.cu_q, self.seq_start,
                            self.seq_kvlen, self.n)
         ctx = StepContext(
-            n_tokens=self.n, n_seqs=self.n, decode=True, max_q_len=1, max_kv_len=e.max_seq_len, tokens=self.tokens,
+            n_tokens=self.n, n_seqs=self.n, decode=True, max_q_len=1, max_kv_len=self.kv_limit, tokens=self.tokens,
             tok_pos=self.tok_pos, tok_seq=self.tok_seq, cu_q=self.cu_q, seq_slot=self.slots, seq_start=self.seq_start,
             seq_kvlen=self.seq_kvlen, logit_rows=self.rows, dtype=e.dtype, device=e.device, kernels=e.kernels,
             all_rows=True)

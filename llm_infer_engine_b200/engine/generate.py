@@ -151,8 +151,9 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
             host_tokens[:n] = torch.tensor(still_tokens, dtype=torch.int32)
             if engine.use_cuda_graph:
                 lanes = bucket_for(n)
-                if graph is None or graph.n != lanes:
-                    graph = engine.decode_graph(lanes)
+                longest = max(cache.lengths[s] for s in live_slots) + 1
+                if graph is None or graph.n != lanes or longest > graph.kv_limit:
+                    graph = engine.decode_graph(lanes, longest)
                     changed = True
                 for s in live_slots:
                     cache.reserve(s, cache.lengths[s] + 1)

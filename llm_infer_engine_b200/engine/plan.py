@@ -13,6 +13,12 @@ class KernelPlan:
     def __init__(self, engine):
         self.engine = engine
         self.bf16 = engine.dtype == torch.bfloat16
+        self._counters = None          # zeroed once; the decode attention kernel leaves them zero
+
+    def _decode_counters(self, need: int, device) -> torch.Tensor:
+        if self._counters is None or self._counters.numel() < need:
+            self._counters = torch.zeros(max(need, 1024), dtype=torch.int32, device=device)
+        return self._counters
 
     @staticmethod
     def decode_run_length(n_seqs: int, n_kv_heads: int, max_kv_len: int) -> int:
@@ -23,11 +29,12 @@ class KernelPlan:
 
     def attention(self, ctx, q, kv, out, n_q, n_kv, head_dim, scale, window) -> bool:
         """Returns True when a specialised kernel ran."""
-        if ctx.decode and ops.attention_decode_supported(head_dim, q.dtype):
+        if ctx.decode and kv.page_size == 64 and ops.attention_decode_supported(head_dim, q.dtype):
             run = self.decode_run_length(ctx.n_seqs, n_kv, ctx.max_kv_len)
-            n_runs = (ctx.max_kv_len + run - 1) // run
+            n_runs = min((ctx.max_kv_len + run - 1) // run, kv.block_table.shape[1])
+            counters = self._decode_counters(ops.decode_counter_ints(ctx.n_seqs, n_q, n_kv), q.device)
             ops.attention_decode(q, kv.k, kv.v, out, ctx.seq_slot, ctx.seq_kvlen, kv.block_table, kv.page_size,
-                                 n_q, n_kv, head_dim, scale, window, run, n_runs)
+                                 n_q, n_kv, head_dim, scale, window, run, n_runs, counters=counters)
             return True
         if not ctx.decode and ops.attention_prefill_tc_supported(head_dim, kv.page_size, q.dtype):
             ops.attention_prefill_tc(q, kv.k, kv.v, out, ctx.cu_q, ctx.seq_slot, ctx.seq_start, kv.block_table,

@@ -204,14 +204,22 @@ def decode_scratch_floats(n_seqs: int, n_q: int, head_dim: int, n_runs: int) -> 
     return n_seqs * n_q * n_runs * (head_dim + 2)
 
 
+def decode_counter_ints(n_seqs: int, n_q: int, n_kv: int) -> int:
+    """int32 counters that the one-launch form of attention_decode needs (all zero, left zero)."""
+    g = n_q // n_kv
+    return n_seqs * n_kv * ((g + 3) // 4 if g <= 4 else (g + 7) // 8)
+
+
 def attention_decode(q, k_cache, v_cache, out, seq_slot, seq_kvlen, block_table, page_size: int, n_q: int,
                      n_kv: int, head_dim: int, scale: float, window: int, run_len: int, n_runs: int,
-                     scratch: Optional[torch.Tensor] = None):
+                     scratch: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None):
     """Split-KV attention for a step in which every sequence brings one token.
 
     q, out [n, n_q hd]; seq_kvlen int32 [n] = keys each sequence holds INCLUDING this step's;
-    n_runs * run_len must be at least the longest length that seq_kvlen can name.
-    scratch: float32 with decode_scratch_floats(...) elements (allocated here if None)."""
+    n_runs * run_len must be at least the longest length that seq_kvlen can name; run_len is the
+    page size. scratch: float32 with decode_scratch_floats(...) elements (allocated here if None).
+    With `counters` (int32 zeros, decode_counter_ints(...) of them) the runs are merged by the last
+    block of the same launch instead of a second kernel."""
     n = q.shape[0]
     _need(q, "q", None, (n, n_q * head_dim))
     _need(out, "out", q.dtype, (n, n_q * head_dim))
@@ -229,6 +237,17 @@ def attention_decode(q, k_cache, v_cache, out, seq_slot, seq_kvlen, block_table,
         raise KernelError(f"attention_decode: scratch holds {scratch.numel()} floats, {need} are needed")
     n_ml = n * n_q * n_runs
     base = scratch.data_ptr()
+    if counters is not None:
+        _need(counters, "counters", torch.int32)
+        if counters.numel() < decode_counter_ints(n, n_q, n_kv):
+            raise KernelError("attention_decode: too few counters")
+        f = _fn("attention_decode", "llmie_attention_decode_fused",
+                [_c_void_p] * 11 + [_c_int] * 6 + [_c_float] + [_c_int] * 4 + [_c_void_p])
+        _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), base, base + 4 * n_ml,
+                 base + 8 * n_ml, counters.data_ptr(), seq_slot.data_ptr(), seq_kvlen.data_ptr(),
+                 block_table.data_ptr(), block_table.shape[1], page_size, n, n_q, n_kv, head_dim, float(scale),
+                 int(window), int(run_len), int(n_runs), _dt(q, "q"), _stream()), "attention_decode")
+        return out
     f = _fn("attention_decode", "llmie_attention_decode",
             [_c_void_p] * 10 + [_c_int] * 6 + [_c_float] + [_c_int] * 4 + [_c_void_p])
     _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), base, base + 4 * n_ml,
