@@ -45,7 +45,7 @@ __device__ __forceinline__ int first_visible(int len, int window) {
 // The page's K and V rows are contiguous in the cache, so the block asks for all of both at once
 // (every 16-byte load of the page is issued before anything is computed): one memory latency per
 // block instead of one per key. run_len must equal the page size.
-template <typename T, int HD, int GMAX>
+template <typename T, int HD, int GMAX, bool STAGED>
 __global__ void __launch_bounds__(kDecThreads)
 decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                     float* __restrict__ part_m, float* __restrict__ part_l, float* __restrict__ part_acc,
@@ -87,18 +87,37 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, cons
   const T* kp = k_cache + page_base;
   const T* vp = v_cache + page_base;
 
-  // every load of this block, K and V, is requested here; rows outside [first, first + n_keys) hold
-  // other positions of the page (never another sequence's) and are simply not used
-  float kv[kIter][E], vv[kIter][E];
+  // Every byte of this block's K and V page is requested here, before anything is computed. Rows
+  // outside [first, first + n_keys) hold other positions of the page (never another sequence's)
+  // and are simply not used.
+  //   STAGED (many sequences): asynchronous 16-byte copies into shared memory; no registers are
+  //   tied up, so many blocks per SM keep their pages in flight at once.
+  //   otherwise (few sequences, latency matters most): straight into registers.
+  extern __shared__ __align__(16) unsigned char page_smem[];
+  T* ks = reinterpret_cast<T*>(page_smem);                  // [kRun][HD]
+  T* vs = ks + kRun * HD;
+  float kreg[STAGED ? 1 : kIter][E], vreg[STAGED ? 1 : kIter][E];
+  if constexpr (STAGED) {
+    constexpr int kVecs = kRun * HD / E;                    // 16-byte pieces per page
+    const unsigned ks_addr = (unsigned)__cvta_generic_to_shared(ks), vs_addr = (unsigned)__cvta_generic_to_shared(vs);
+    for (int i = threadIdx.x; i < kVecs; i += kDecThreads) {
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ks_addr + i * 16), "l"(kp + (size_t)i * E) : "memory");
+    }
+    for (int i = threadIdx.x; i < kVecs; i += kDecThreads) {
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vs_addr + i * 16), "l"(vp + (size_t)i * E) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  } else {
 #pragma unroll
-  for (int it = 0; it < kIter; ++it) {
-    const int row = (it * kDecWarps + warp) * KPW + sub;
-    load_vec<T, E>(kp + (size_t)row * HD + e0, kv[it]);
-  }
+    for (int it = 0; it < kIter; ++it) {
+      const int row = (it * kDecWarps + warp) * KPW + sub;
+      load_vec<T, E>(kp + (size_t)row * HD + e0, kreg[it]);
+    }
 #pragma unroll
-  for (int it = 0; it < kIter; ++it) {
-    const int row = (it * kDecWarps + warp) * KPW + sub;
-    load_vec<T, E>(vp + (size_t)row * HD + e0, vv[it]);
+    for (int it = 0; it < kIter; ++it) {
+      const int row = (it * kDecWarps + warp) * KPW + sub;
+      load_vec<T, E>(vp + (size_t)row * HD + e0, vreg[it]);
+    }
   }
   // this lane's slice of each query head, pre-scaled
   float qv[GMAX][E];
@@ -116,15 +135,27 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, cons
     }
   }
 
+  if constexpr (STAGED) {
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    __syncthreads();
+  }
+
   // ---- phase 1: scores of the page's rows
 #pragma unroll
   for (int it = 0; it < kIter; ++it) {
     const int row = (it * kDecWarps + warp) * KPW + sub;
+    float kv[E];
+    if constexpr (STAGED) {
+      load_vec<T, E>(ks + (size_t)row * HD + e0, kv);
+    } else {
+#pragma unroll
+      for (int e = 0; e < E; ++e) kv[e] = kreg[it][e];
+    }
 #pragma unroll
     for (int g = 0; g < GMAX; ++g) {
       float dot = 0.f;
 #pragma unroll
-      for (int e = 0; e < E; ++e) dot = fmaf(qv[g][e], kv[it][e], dot);
+      for (int e = 0; e < E; ++e) dot = fmaf(qv[g][e], kv[e], dot);
 #pragma unroll
       for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
       if ((lane % LPK) == 0 && g < ng) scores[g][row] = dot;
@@ -166,11 +197,18 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, cons
 #pragma unroll
   for (int it = 0; it < kIter; ++it) {
     const int row = (it * kDecWarps + warp) * KPW + sub;
+    float vv[E];
+    if constexpr (STAGED) {
+      load_vec<T, E>(vs + (size_t)row * HD + e0, vv);
+    } else {
+#pragma unroll
+      for (int e = 0; e < E; ++e) vv[e] = vreg[it][e];
+    }
 #pragma unroll
     for (int g = 0; g < GMAX; ++g) {
       const float p = (g < ng) ? scores[g][row] : 0.f;
 #pragma unroll
-      for (int e = 0; e < E; ++e) acc[g][e] = fmaf(p, vv[it][e], acc[g][e]);
+      for (int e = 0; e < E; ++e) acc[g][e] = fmaf(p, vv[e], acc[g][e]);
     }
   }
   // lanes with the same element slice (same lane % LPK) hold different keys: add them up
@@ -296,11 +334,22 @@ static int launch_split(const void* q, const void* k_cache, const void* v_cache,
                         int run_len, int n_runs, int* counters, void* out, cudaStream_t stream) {
   const int G = n_q / n_kv;
   const int chunks = (G + GMAX - 1) / GMAX;
-  const size_t smem = 0;
   dim3 grid(n_runs, n_kv * chunks, n_seqs);
-  launch_k(decode_split_kernel<T, HD, GMAX>, dim3(grid), dim3(kDecThreads), smem, stream, 
-      (const T*)q, (const T*)k_cache, (const T*)v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen, block_table,
-      max_pages, page_size, n_q, n_kv, scale, window, run_len, n_runs, counters, (T*)out);
+  if (n_seqs >= 32) {
+    const size_t smem = (size_t)2 * 64 * HD * sizeof(T);      // the K and the V page
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(decode_split_kernel<T, HD, GMAX, true>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    launch_k(decode_split_kernel<T, HD, GMAX, true>, dim3(grid), dim3(kDecThreads), smem, stream, (const T*)q,
+             (const T*)k_cache, (const T*)v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen, block_table,
+             max_pages, page_size, n_q, n_kv, scale, window, run_len, n_runs, counters, (T*)out);
+  } else {
+    launch_k(decode_split_kernel<T, HD, GMAX, false>, dim3(grid), dim3(kDecThreads), 0, stream, (const T*)q,
+             (const T*)k_cache, (const T*)v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen, block_table,
+             max_pages, page_size, n_q, n_kv, scale, window, run_len, n_runs, counters, (T*)out);
+  }
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }

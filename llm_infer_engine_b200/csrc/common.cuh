@@ -101,6 +101,13 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Asks the memory system to bring `bytes` (a multiple of 16, from a 16-byte aligned address) into
+// L2. No register, no shared memory and no waiting on the issuing thread: a block can ask for all
+// the weights it is going to stream, long before its loads of them, even before pdl_wait().
+__device__ __forceinline__ void l2_prefetch(const void* p, unsigned bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
 static inline bool pdl_enabled() {
   static int on = -1;
   if (on < 0) {

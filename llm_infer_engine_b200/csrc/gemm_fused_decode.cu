@@ -90,6 +90,15 @@ norm_gemm_kernel(const float* __restrict__ h, const float* __restrict__ norm_w, 
 
   int tile = blockIdx.x;
   int lo, hi;
+  // every weight row this block will stream, for all of its tiles, is asked into L2 right away
+  for (int i = threadIdx.x; ; i += WARPS * 32) {
+    const int tl = blockIdx.x + (i >> 4) * gridDim.x;
+    if (tl >= tiles) break;
+    int plo, phi;
+    tile_rows<VAR>(tl, hd, half_n, plo, phi);
+    const int r = i & 15;
+    l2_prefetch(W + (size_t)(r < 8 ? plo + r : phi + r - 8) * K, (unsigned)K * 2u);
+  }
   tile_rows<VAR>(tile, hd, half_n, lo, hi);
   const uint4* w_lo = reinterpret_cast<const uint4*>(W + (size_t)(lo + g) * K) + t;
   const uint4* w_hi = reinterpret_cast<const uint4*>(W + (size_t)(hi + g) * K) + t;

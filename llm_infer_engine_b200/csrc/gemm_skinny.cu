@@ -48,6 +48,11 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int lo = blockIdx.x * tile_stride, hi = lo + hi_delta;
+  // the 16 weight rows of this block are asked into L2 at once, before anything else
+  if (threadIdx.x < 16) {
+    const int row = threadIdx.x < 8 ? lo + threadIdx.x : hi + threadIdx.x - 8;
+    l2_prefetch(W + (size_t)row * K, (unsigned)K * 2u);
+  }
   const uint4* w_lo = reinterpret_cast<const uint4*>(W + (size_t)(lo + g) * K) + t;
   const uint4* w_hi = reinterpret_cast<const uint4*>(W + (size_t)(hi + g) * K) + t;
   const uint4* xr[NB];
