@@ -21,17 +21,17 @@ class KernelPlan:
         return self._counters
 
     @staticmethod
-    def decode_run_length(n_seqs: int, n_kv_heads: int, max_kv_len: int) -> int:
-        """Keys per block of the split-KV kernel: one cache page. A page's keys and values are
-        contiguous, so a block requests all of them at once; the reference uses runs of 256
-        (src/flash_decode.py:271-272). Depends on nothing in the step's data."""
-        return 64
+    def decode_run_length(n_seqs: int, head_dim: int, dtype) -> int:
+        """Keys per block of the split-KV kernel: one cache page for few sequences (latency), up to
+        four pages staged in shared memory for many (bandwidth); the reference uses runs of 256
+        (src/flash_decode.py:271-272). Depends only on the step's shape, never on its data."""
+        return ops.attention_decode_run_len(n_seqs, head_dim, dtype)
 
     def attention(self, ctx, q, kv, out, n_q, n_kv, head_dim, scale, window) -> bool:
         """Returns True when a specialised kernel ran."""
         if ctx.decode and kv.page_size == 64 and ops.attention_decode_supported(head_dim, q.dtype):
-            run = self.decode_run_length(ctx.n_seqs, n_kv, ctx.max_kv_len)
-            n_runs = min((ctx.max_kv_len + run - 1) // run, kv.block_table.shape[1])
+            run = self.decode_run_length(ctx.n_seqs, head_dim, q.dtype)
+            n_runs = (ctx.max_kv_len + run - 1) // run
             counters = self._decode_counters(ops.decode_counter_ints(ctx.n_seqs, n_q, n_kv), q.device)
             ops.attention_decode(q, kv.k, kv.v, out, ctx.seq_slot, ctx.seq_kvlen, kv.block_table, kv.page_size,
                                  n_q, n_kv, head_dim, scale, window, run, n_runs, counters=counters)

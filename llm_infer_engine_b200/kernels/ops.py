@@ -199,6 +199,14 @@ def attention_decode_supported(head_dim: int, dtype: torch.dtype) -> bool:
     return bool(lib.llmie_attention_decode_supported(head_dim, code))
 
 
+def attention_decode_run_len(n_seqs: int, head_dim: int, dtype: torch.dtype) -> int:
+    """Keys per block that attention_decode wants for this many sequences (a multiple of the page size)."""
+    lib = build.load("attention_decode")
+    lib.llmie_attention_decode_run_len.argtypes = [_c_int, _c_int, _c_int]
+    lib.llmie_attention_decode_run_len.restype = _c_int
+    return int(lib.llmie_attention_decode_run_len(n_seqs, head_dim, _DT[dtype]))
+
+
 def decode_scratch_floats(n_seqs: int, n_q: int, head_dim: int, n_runs: int) -> int:
     """float32 elements of scratch that attention_decode needs."""
     return n_seqs * n_q * n_runs * (head_dim + 2)

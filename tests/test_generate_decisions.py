@@ -2,7 +2,6 @@
 which captured step serves a batch, how keys are split."""
 from llm_infer_engine_b200.engine.engine import bucket_for, kv_bucket_for
 from llm_infer_engine_b200.engine.generate import finished_reason, plan_batch
-from llm_infer_engine_b200.engine.plan import KernelPlan
 from llm_infer_engine_b200.sampling import SamplingParams, uniform_for
 
 
@@ -33,7 +32,6 @@ def test_buckets_and_runs():
     assert [bucket_for(n) for n in (1, 2, 3, 5, 8, 9, 33, 64, 65, 300)] == [1, 2, 4, 8, 8, 16, 64, 64, 128, 300]
     assert [kv_bucket_for(n, 4096) for n in (1, 512, 513, 3000, 9000)] == [512, 512, 1024, 4096, 4096]
     assert kv_bucket_for(100, 256) == 256
-    assert KernelPlan.decode_run_length(1, 8, 4096) == KernelPlan.decode_run_length(64, 8, 1024) == 64    # one page
 
 
 def test_sampling_params_and_uniforms():

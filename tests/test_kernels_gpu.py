@@ -478,3 +478,36 @@ def test_norm_qkv_rope(batch, n_q, n_kv, hd, K):
     assert torch.allclose(v_dev.float(), v2.float(), atol=3e-2, rtol=3e-2)
     # and it wrote exactly the cache rows the unfused path wrote
     assert torch.equal((k_dev != pg.dev()[0]).any(-1), (k2 != pg.dev()[0]).any(-1))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q,n_kv,hd", [(32, 8, 64), (6, 2, 128), (4, 4, 16)])
+def test_attention_decode_many_sequences(dtype, n_q, n_kv, hd):
+    """From 32 sequences on the kernel stages several pages per block in shared memory."""
+    o = ops()
+    g = torch.Generator().manual_seed(3 + hd)
+    lens = [int(x) for x in torch.randint(1, 700, (40,), generator=g)]
+    lens[0], lens[1], lens[2] = 1, 256, 257
+    pg = Paged(lens, n_kv, hd, dtype, seed=hd)
+    pg.fill()
+    q = torch.randn(len(lens), n_q, hd, generator=g)
+    k_dev, v_dev, bt = pg.dev()
+    qd = q.to(dtype).reshape(len(lens), n_q * hd).to(DEV)
+    slots = torch.tensor(pg.slots, dtype=torch.int32, device=DEV)
+    kvlen = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    run_len = o.attention_decode_run_len(len(lens), hd, dtype)
+    assert run_len % 64 == 0 and run_len >= 64
+    n_runs = (768 + run_len - 1) // run_len
+    counters = torch.zeros(o.decode_counter_ints(len(lens), n_q, n_kv), dtype=torch.int32, device=DEV)
+    for window in (0, 90):
+        for fused in (True, False):
+            out = torch.full((len(lens), n_q * hd), float("nan"), dtype=dtype, device=DEV)
+            o.attention_decode(qd, k_dev, v_dev, out, slots, kvlen, bt, 64, n_q, n_kv, hd, hd ** -0.5, window, run_len,
+                               n_runs, counters=counters if fused else None)
+            got = out.float().cpu().view(len(lens), n_q, hd)
+            assert not torch.isnan(got).any()
+            for i in (0, 1, 2, 7, 23, 39):
+                ref = ref_attention(qd.float().cpu().view(len(lens), n_q, hd)[i:i + 1], pg.dense_k[i].float(),
+                                    pg.dense_v[i].float(), [lens[i] - 1], hd ** -0.5, window)[0]
+                assert torch.allclose(got[i], ref, atol=tol(dtype, 2e-5, 3e-2)), (window, fused, i)
+        assert int(counters.abs().sum()) == 0          # left clean
