@@ -1,0 +1,68 @@
+"""The layer shapes of real Llama models (1B, 3B, 8B), a few layers each, random weights:
+the float32 engine must match the plain implementation closely however the work is cut, and the
+bfloat16 engine (tensor-core attention, fused one-token kernels, head size 128, 128256-token
+vocabulary) must stay within bfloat16 rounding of it."""
+import copy
+import tempfile
+
+import pytest
+import torch
+
+import helpers
+import plain_llama as plain
+
+pytestmark = pytest.mark.gpu
+
+LLAMA3 = {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+          "original_max_position_embeddings": 8192}
+BASE = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "rope_theta": 500000.0, "rope_scaling": LLAMA3,
+        "rms_norm_eps": 1e-5, "max_position_embeddings": 131072, "hidden_act": "silu", "attention_bias": False,
+        "mlp_bias": False, "eos_token_id": 128001, "torch_dtype": "bfloat16", "vocab_size": 128256}
+SHAPES = {
+    "1b": dict(BASE, num_hidden_layers=2, hidden_size=2048, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
+               intermediate_size=8192, tie_word_embeddings=True),
+    "3b": dict(BASE, num_hidden_layers=1, hidden_size=3072, num_attention_heads=24, num_key_value_heads=8, head_dim=128,
+               intermediate_size=8192, tie_word_embeddings=True),
+    "8b": dict(BASE, num_hidden_layers=1, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+               intermediate_size=14336, tie_word_embeddings=False,
+               rope_scaling=dict(LLAMA3, factor=8.0)),
+}
+_cache = {}
+
+
+def setup(tag):
+    if tag not in _cache:
+        from llm_infer_engine_b200 import write_random_model
+        folder = tempfile.mkdtemp(prefix=f"llmie_{tag}_")
+        write_random_model(SHAPES[tag], folder, seed=2, std=0.02)
+        w = helpers.plain_weights(folder)
+        requests = {f"q{i}": helpers.random_tokens(128256, n, seed=900 + i) for i, n in enumerate([70, 9, 150])}
+        want = {rid: plain.logits(w, SHAPES[tag], toks) for rid, toks in requests.items()}
+        _cache[tag] = (folder, requests, want)
+    return _cache[tag]
+
+
+@pytest.mark.parametrize("tag", ["1b", "3b", "8b"])
+# float32: BASELINE's bound (1e-3 absolute). bfloat16: rounding grows with the width of the sums and the
+# size of the logits, so the bound is relative to the largest logit of the request (1.5 %).
+@pytest.mark.parametrize("dtype,tol", [("float32", 1e-3), ("bfloat16", 0.015)])
+def test_real_shapes(tag, dtype, tol):
+    from llm_infer_engine_b200 import Engine
+    from llm_infer_engine_b200.kernels import ops
+    folder, requests, want = setup(tag)
+    engine = Engine(folder, dtype=dtype, max_batch=4, max_seq_len=512, max_tokens=64 * 12, cuda_graph=False)
+    for plan in (helpers.plan_whole(requests), helpers.plan_tail(requests, 32), helpers.plan_batched(requests, 3)):
+        got = helpers.run_plan_engine(engine, plan)
+        for rid in requests:
+            err = float((got[rid] - want[rid]).abs().max())
+            bound = tol if dtype == "float32" else tol * float(want[rid].abs().max())
+            assert err <= bound, (tag, dtype, rid, err, bound)
+            if dtype == "float32":      # identical greedy tokens, except where the plain top two nearly tie
+                a, b = got[rid].argmax(-1), want[rid].argmax(-1)
+                for t in (a != b).nonzero().flatten().tolist():
+                    top2 = want[rid][t].topk(2).values
+                    assert float(top2[0] - top2[1]) < 1e-5, (tag, rid, t)
+    if dtype == "bfloat16":
+        ops.check_tc_status("cuda")
+    del engine
+    torch.cuda.empty_cache()
