@@ -302,20 +302,6 @@ __global__ void advance_lengths_kernel(const int* __restrict__ slots, const int*
   }
 }
 
-// Asks for a range of memory (weights that a later kernel will stream) to be brought into L2.
-// A handful of threads issue bulk prefetches of 4 KB each and the kernel ends at once; the copies
-// proceed in the background while other kernels run. Launched WITHOUT a dependency wait on purpose:
-// it reads nothing and writes nothing.
-__global__ void l2_prefetch_kernel(const char* __restrict__ base, size_t bytes) {
-  const size_t chunk = 4096;
-  const size_t n_chunks = (bytes + chunk - 1) / chunk;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_chunks; i += (size_t)gridDim.x * blockDim.x) {
-    const size_t off = i * chunk;
-    const size_t len = bytes - off < chunk ? ((bytes - off) & ~(size_t)15) : chunk;
-    if (len) l2_prefetch(base + off, (unsigned)len);
-  }
-}
-
 static inline int norm_threads(int d) {
   int t = (d + 7) / 8;
   t = ((t + 31) / 32) * 32;
@@ -472,14 +458,3 @@ extern "C" int llmie_advance_lengths(const int* slots, const int* seq_kvlen, int
   return LLMIE_OK;
 }
 
-// Starts bringing [ptr, ptr + bytes) into L2 (ptr 16-byte aligned). Returns at once.
-extern "C" int llmie_l2_prefetch(const void* ptr, long long bytes, cudaStream_t stream) {
-  if (bytes < 0 || !aligned16(ptr)) return LLMIE_ERR_BAD_ARG;
-  if (bytes < 16) return LLMIE_OK;
-  const long long chunks = (bytes + 4095) / 4096;
-  int blocks = (int)((chunks + 63) / 64);
-  if (blocks > 148) blocks = 148;
-  l2_prefetch_kernel<<<blocks, 64, 0, stream>>>((const char*)ptr, (size_t)bytes);
-  LLMIE_LAUNCH_CHECK();
-  return LLMIE_OK;
-}

@@ -502,13 +502,6 @@ def copy_int(src: torch.Tensor, dst: torch.Tensor, n: int) -> None:
     _check(f(src.data_ptr(), dst.data_ptr(), n, _stream()), "copy_int")
 
 
-def l2_prefetch(t: torch.Tensor) -> None:
-    """Starts bringing a tensor (weights a later kernel will stream) into L2; returns at once."""
-    _need(t, "t")
-    f = _fn("elementwise", "llmie_l2_prefetch", [_c_void_p, ctypes.c_longlong, _c_void_p])
-    _check(f(t.data_ptr(), t.numel() * t.element_size(), _stream()), "l2_prefetch")
-
-
 def prepare_decode(slots, seq_lens, tok_pos, tok_seq, cu_q, seq_start, seq_kvlen, n: int) -> None:
     """Per-lane metadata of a one-token step from the device-resident lengths."""
     for name, t in (("slots", slots), ("seq_lens", seq_lens), ("tok_pos", tok_pos), ("tok_seq", tok_seq),
