@@ -85,7 +85,9 @@ norm_gemm_kernel(const float* __restrict__ h, const float* __restrict__ norm_w, 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n_chunks = K >> 5;
-  constexpr int kStep = WARPS * kFdUnroll;
+  // each warp takes a contiguous run of K, so that a row is read in long pieces
+  const int per_warp = (n_chunks + WARPS - 1) / WARPS;
+  const int c_begin = warp * per_warp, c_end = min(n_chunks, c_begin + per_warp);
   const int hd = rope.hd;
 
   int tile = blockIdx.x;
@@ -105,8 +107,8 @@ norm_gemm_kernel(const float* __restrict__ h, const float* __restrict__ norm_w, 
   uint4 wa[kFdUnroll], wb[kFdUnroll], na[kFdUnroll], nb2[kFdUnroll];
 #pragma unroll
   for (int u = 0; u < kFdUnroll; ++u) {
-    const int c = warp + u * WARPS;
-    if (c < n_chunks) {
+    const int c = c_begin + u;
+    if (c < c_end) {
       wa[u] = fd_ldg16(w_lo + c * 4);
       wb[u] = fd_ldg16(w_hi + c * 4);
     }
@@ -167,20 +169,20 @@ norm_gemm_kernel(const float* __restrict__ h, const float* __restrict__ norm_w, 
       nw_lo = reinterpret_cast<const uint4*>(W + (size_t)(nlo + g) * K) + t;
       nw_hi = reinterpret_cast<const uint4*>(W + (size_t)(nhi + g) * K) + t;
     }
-    for (int c0 = warp; c0 < n_chunks; c0 += kStep) {
+    for (int c0 = c_begin; c0 < c_end; c0 += kFdUnroll) {
       // request what comes next: the next round of this tile, or the first round of the next tile
-      const bool last_round = c0 + kStep >= n_chunks;
+      const bool last_round = c0 + kFdUnroll >= c_end;
 #pragma unroll
       for (int u = 0; u < kFdUnroll; ++u) {
         if (!last_round) {
-          const int c = c0 + kStep + u * WARPS;
-          if (c < n_chunks) {
+          const int c = c0 + kFdUnroll + u;
+          if (c < c_end) {
             na[u] = fd_ldg16(w_lo + c * 4);
             nb2[u] = fd_ldg16(w_hi + c * 4);
           }
         } else if (next_tile < tiles) {
-          const int c = warp + u * WARPS;
-          if (c < n_chunks) {
+          const int c = c_begin + u;
+          if (c < c_end) {
             na[u] = fd_ldg16(nw_lo + c * 4);
             nb2[u] = fd_ldg16(nw_hi + c * 4);
           }
@@ -188,8 +190,8 @@ norm_gemm_kernel(const float* __restrict__ h, const float* __restrict__ norm_w, 
       }
 #pragma unroll
       for (int u = 0; u < kFdUnroll; ++u) {
-        const int c = c0 + u * WARPS;
-        if (c < n_chunks) {
+        const int c = c0 + u;
+        if (c < c_end) {
           const uint4 xv = x_row[c * 4];
           fd_mma(acc, wa[u].x, wb[u].x, wa[u].y, wb[u].y, xv.x, xv.y);
           fd_mma(acc, wa[u].z, wb[u].z, wa[u].w, wb[u].w, xv.z, xv.w);

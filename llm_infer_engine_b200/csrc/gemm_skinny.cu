@@ -70,12 +70,14 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     for (int i = 0; i < 4; ++i) acc[nb][i] = 0.f;
 
   const int n_chunks = K >> 5;                      // chunks of 32 k; 4 uint4 per row per chunk
-  constexpr int kStep = WARPS * kSkUnroll;
+  // each warp takes a contiguous run of K, so that a row is read in long pieces
+  const int per_warp = (n_chunks + WARPS - 1) / WARPS;
+  const int c_begin = warp * per_warp, c_end = min(n_chunks, c_begin + per_warp);
   uint4 wa[kSkUnroll], wb[kSkUnroll], na[kSkUnroll], nbuf[kSkUnroll];
 #pragma unroll
   for (int u = 0; u < kSkUnroll; ++u) {
-    const int c = warp + u * WARPS;
-    if (c < n_chunks) {
+    const int c = c_begin + u;
+    if (c < c_end) {
       wa[u] = ldg16(w_lo + c * 4);
       wb[u] = ldg16(w_hi + c * 4);
     }
@@ -83,11 +85,11 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   // The weights are written by no kernel, so their first loads are already on their way while
   // the kernel before this one finishes; x (and out, for the add) are its results: wait for it here.
   pdl_wait();
-  for (int c0 = warp; c0 < n_chunks; c0 += kStep) {
+  for (int c0 = c_begin; c0 < c_end; c0 += kSkUnroll) {
 #pragma unroll
     for (int u = 0; u < kSkUnroll; ++u) {           // request the next round
-      const int c = c0 + kStep + u * WARPS;
-      if (c < n_chunks) {
+      const int c = c0 + kSkUnroll + u;
+      if (c < c_end) {
         na[u] = ldg16(w_lo + c * 4);
         nbuf[u] = ldg16(w_hi + c * 4);
       }
@@ -95,17 +97,17 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     uint4 xv[kSkUnroll][NB];
 #pragma unroll
     for (int u = 0; u < kSkUnroll; ++u) {
-      const int c = c0 + u * WARPS;
+      const int c = c0 + u;
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) {
         xv[u][nb] = make_uint4(0u, 0u, 0u, 0u);
-        if (c < n_chunks && xok[nb]) xv[u][nb] = ldg16(xr[nb] + c * 4);
+        if (c < c_end && xok[nb]) xv[u][nb] = ldg16(xr[nb] + c * 4);
       }
     }
 #pragma unroll
     for (int u = 0; u < kSkUnroll; ++u) {
-      const int c = c0 + u * WARPS;
-      if (c < n_chunks) {
+      const int c = c0 + u;
+      if (c < c_end) {
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
           mma_bf16_16x8x16(acc[nb], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xv[u][nb].x, xv[u][nb].y);

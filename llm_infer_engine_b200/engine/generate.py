@@ -184,6 +184,7 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
         d1.record()
         d1.synchronize()
         stats.decode_seconds += d0.elapsed_time(d1) / 1e3
+        ops.check_tc_status(dev)         # a kernel that gave up a bounded wait leaves a code here
     finally:
         for s in slots:
             if s >= 0 and cache.slots.is_held(s):

@@ -60,6 +60,13 @@ class GroupedQueryAttention(Mixer):
     def cache_requests(self):
         return [KVRequest(self.n_kv_heads, self.head_dim, self.window)]
 
+    def stack_view(self):
+        table = getattr(self.position, "fused_table", lambda hd: None)(self.head_dim)
+        if table is None or self.window:
+            return None
+        return dict(kind="gqa_rope", qkv=self.qkv.weight, o=self.o.weight, hidden=self.hidden, n_heads=self.n_heads,
+                    n_kv_heads=self.n_kv_heads, head_dim=self.head_dim, scale=self.scale, rope_table=table)
+
     def forward(self, x, ctx, unit, owns_cache, residual=None):
         kv = unit.kv
         q = None

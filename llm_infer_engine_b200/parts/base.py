@@ -56,6 +56,13 @@ class Part:
         """Bytes of weights that one step reads (for roofline accounting)."""
         return 0
 
+    def stack_view(self) -> Optional[dict]:
+        """What a kernel that runs a whole stack of layers by itself needs of this part: a dict with
+        "kind" and the part's tensors and constants, or None when the part can only be run through
+        forward(). The engine uses such a kernel only when every part of every layer gives a view
+        that the kernel knows; anything else runs part by part."""
+        return None
+
 
 class Norm(Part):
     def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
@@ -132,6 +139,10 @@ class Block:
 
     def forward(self, h, pending, ctx, unit, owns_cache):
         raise NotImplementedError
+
+    def stack_view(self) -> Optional[dict]:
+        """As Part.stack_view, for the arrangement: "kind" plus the views of the four parts."""
+        return None
 
 
 _REGISTRIES: Dict[str, Dict[str, type]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position_encoding": {},

@@ -31,5 +31,11 @@ class PreNormBlock(Block):
             return h, self.feed_forward.forward(x, ctx, residual=h)
         return h, self.feed_forward.forward(x, ctx)
 
+    def stack_view(self):
+        views = {role: part.stack_view() for role, part in self.parts().items()}
+        if any(v is None for v in views.values()):
+            return None
+        return dict(kind="pre_norm", **views)
+
 
 register_block("pre_norm", PreNormBlock)
