@@ -16,7 +16,6 @@ import json
 import os
 import subprocess
 import sys
-import tempfile
 import threading
 import time
 
@@ -107,9 +106,10 @@ class ClockSampler:
 
 def make_model_folder(n_layers: int, seed: int = 2) -> str:
     from llm_infer_engine_b200 import write_random_model
+    from llm_infer_engine_b200.weights import scratch_folder
     cfg = dict(CONFIG_1B)
     cfg["num_hidden_layers"] = n_layers
-    folder = tempfile.mkdtemp(prefix="llmie_bench_1b_")
+    folder = scratch_folder("llmie_bench_1b_")          # deleted at exit: a 16-layer folder is 2.5 GB
     t0 = time.time()
     write_random_model(cfg, folder, seed=seed, std=0.02)
     print(f"[bench] wrote a random {n_layers}-layer model folder in {time.time() - t0:.1f}s", file=sys.stderr)

@@ -14,7 +14,6 @@ import argparse
 import json
 import os
 import sys
-import tempfile
 import time
 from pathlib import Path
 from typing import List, Optional
@@ -141,7 +140,7 @@ def config_from_flags(opts: dict) -> dict:
 
 def prepare_model_folder(opts: dict, log=print) -> str:
     """Returns a folder with config.json and model.safetensors for the engine to load."""
-    from ..weights import write_random_model
+    from ..weights import scratch_folder, write_random_model
     config_dir = next((d for d in (opts["model"], opts["tokenizer"])
                        if d and os.path.isfile(os.path.join(d, "config.json"))), None)
     if opts["weights"]:
@@ -149,7 +148,7 @@ def prepare_model_folder(opts: dict, log=print) -> str:
             raise FileNotFoundError(f"weights file not found: {opts['weights']}")
         if config_dir is None:
             raise ValueError("--weights needs a config.json in --model or --tokenizer")
-        folder = tempfile.mkdtemp(prefix="llmie_model_")
+        folder = scratch_folder("llmie_model_")
         os.symlink(os.path.abspath(os.path.join(config_dir, "config.json")), os.path.join(folder, "config.json"))
         os.symlink(os.path.abspath(opts["weights"]), os.path.join(folder, "model.safetensors"))
         return folder
@@ -162,7 +161,7 @@ def prepare_model_folder(opts: dict, log=print) -> str:
             config_json = json.load(f)
     else:
         config_json = config_from_flags(opts)
-    folder = tempfile.mkdtemp(prefix="llmie_random_")
+    folder = scratch_folder("llmie_random_")
     t0 = time.time()
     write_random_model(config_json, folder, seed=opts["seed"] or 0)
     log(f"    Random init: {time.time() - t0:.4f}s")

@@ -1,0 +1,421 @@
+// Attention for one-token steps on the tensor cores: a warp per cache page.
+//
+// One block serves one (sequence, KV head) - or one run of its pages - for up to 16 of the query
+// heads that share the KV head. The 16 x head_dim block of queries is the A operand of
+// mma.sync.m16n8k16; a WARP takes a whole page (64 keys) at a time: it copies the page's K and V
+// rows into its own shared-memory tiles (cp.async, the next page's K while this page's softmax
+// and P V run), computes S = Q K^T with 8 x head_dim/16 tensor-core products, keeps a running
+// maximum and sum per query head in registers (the online softmax of src/flash_attn.py:118-134
+// for one query row per head), converts P to bfloat16 in registers (the accumulator layout of two
+// neighbouring 8-key tiles is the A layout of one 16-key step) and adds P V. Warps of a block take
+// pages in turn and never wait for one another until the end, where their (max, sum, accumulator)
+// triples meet in shared memory (src/flash_decode.py:182-205 is the same merge). A sequence whose
+// pages all belong to one block is written straight to the output; otherwise each block leaves a
+// partial result per run and the block that finishes last merges them, as in attention_decode.cu.
+//
+// Against the split-KV kernel on CUDA cores (attention_decode.cu): no block-wide barrier per
+// page, no shuffle reductions per key, and a sequence is merged inside its block instead of
+// through global memory. bfloat16 only (the float32 engine keeps the CUDA-core kernel), pages of
+// 64 keys, head size 64 or 128. Scores, softmax statistics and accumulators are float32; the
+// probabilities enter the second product as bfloat16, as the reference's do (src/flash_attn.py:131).
+// Rows of a page beyond a sequence's length get probability zero; the cache holds finite numbers
+// there (it starts as zeros and only ever receives keys and values).
+#include "common.cuh"
+#include <math.h>
+
+namespace llmie {
+
+constexpr int kMdPage = 64;
+
+__device__ __forceinline__ int md_first_visible(int len, int window) {
+  return (window > 0 && len - window > 0) ? len - window : 0;
+}
+__device__ __forceinline__ void md_mma(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                       unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void md_ldmatrix(unsigned (&r)[4], unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void md_ldmatrix_trans(unsigned (&r)[4], unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ unsigned md_pack(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Merge of the runs of one (sequence, query head) by one warp.
+template <int HD>
+__device__ __forceinline__ void md_merge_head(const float* part_m, const float* part_l, const float* part_acc,
+                                              __nv_bfloat16* out_row, size_t base, int r0, int r1) {
+  const int lane = threadIdx.x & 31;
+  float M = -INFINITY;
+  for (int r = r0 + lane; r <= r1; r += 32) M = fmaxf(M, __ldcg(part_m + base + r));
+  M = warp_max(M);
+  float denom = 0.f;
+  float num[HD / 32];
+#pragma unroll
+  for (int i = 0; i < HD / 32; ++i) num[i] = 0.f;
+  for (int c0 = r0; c0 <= r1; c0 += 32) {
+    const int r = c0 + lane;
+    float w = 0.f;
+    if (r <= r1) {
+      w = expf(__ldcg(part_m + base + r) - M);
+      denom = fmaf(w, __ldcg(part_l + base + r), denom);
+    }
+    const int n_here = min(32, r1 - c0 + 1);
+#pragma unroll 4
+    for (int i = 0; i < n_here; ++i) {
+      const float wi = __shfl_sync(0xffffffffu, w, i);
+#pragma unroll
+      for (int k = 0; k < HD / 32; ++k) num[k] = fmaf(wi, __ldcg(part_acc + (base + c0 + i) * HD + lane + 32 * k), num[k]);
+    }
+  }
+  denom = warp_sum(denom);
+  const float inv = 1.f / denom;
+#pragma unroll
+  for (int k = 0; k < HD / 32; ++k) out_row[lane + 32 * k] = __float2bfloat16_rn(num[k] * inv);
+}
+
+// grid (n_runs, n_kv * chunks, n_seqs), chunks = ceil(G / 16); WARPS warps per block.
+template <int HD, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, (HD == 64 && WARPS <= 4) ? 12 / WARPS : 1)
+decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                  const __nv_bfloat16* __restrict__ v_cache, float* __restrict__ part_m, float* __restrict__ part_l,
+                  float* __restrict__ part_acc, const int* __restrict__ seq_slot, const int* __restrict__ seq_kvlen,
+                  const int* __restrict__ block_table, int max_pages, int n_q, int n_kv, float scale, int window,
+                  int pages_per_run, int n_runs, int* __restrict__ counters, __nv_bfloat16* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int PITCH = HD + 8;                         // elements; rows 16 bytes apart in the banks
+  constexpr int KS = HD / 16;                           // k-steps of Q K^T
+  constexpr int NT = HD / 8;                            // n-tiles of P V
+  constexpr int kTile = kMdPage * PITCH;                // elements of one staged page of K (or V)
+  constexpr int kPieces = HD / 8;                       // 16-byte pieces per row
+  extern __shared__ __align__(16) unsigned char md_smem[];
+  __shared__ int is_last;
+
+  const int run = blockIdx.x, seq = blockIdx.z;
+  const int G = n_q / n_kv;
+  const int chunks = (G + 15) / 16;
+  const int hk = blockIdx.y / chunks;
+  const int g0 = (blockIdx.y % chunks) * 16;
+  const int ng = min(16, G - g0);
+
+  const int len = seq_kvlen[seq];
+  const int lo = md_first_visible(len, window);
+  const int p_first = max(run * pages_per_run, lo / kMdPage);
+  const int p_last = min((run + 1) * pages_per_run - 1, (len - 1) / kMdPage);
+  if (len <= 0 || p_first > p_last) return;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  __nv_bfloat16* k_tile = reinterpret_cast<__nv_bfloat16*>(md_smem) + (size_t)warp * 2 * kTile;
+  __nv_bfloat16* v_tile = k_tile + kTile;
+  const unsigned k_addr = (unsigned)__cvta_generic_to_shared(k_tile);
+  const unsigned v_addr = (unsigned)__cvta_generic_to_shared(v_tile);
+  const int* pages = block_table + (size_t)seq_slot[seq] * max_pages;
+  const size_t head_off = (size_t)hk * kMdPage * HD;
+  const size_t page_stride = (size_t)n_kv * kMdPage * HD;
+
+  // a warp copies a whole page tile: 64 rows of HD elements into rows of PITCH elements
+  auto issue = [&](const __nv_bfloat16* cache, unsigned dst, int p) {
+    const __nv_bfloat16* src = cache + (size_t)pages[p] * page_stride + head_off;
+#pragma unroll
+    for (int i = 0; i < kMdPage * kPieces / 32; ++i) {
+      const int idx = i * 32 + lane;
+      const int row = idx / kPieces, piece = idx % kPieces;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (unsigned)(row * PITCH + piece * 8) * 2u),
+                   "l"(src + (size_t)row * HD + piece * 8) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  int p = p_first + warp;
+  const bool has_pages = p <= p_last;
+  if (has_pages) {
+    issue(k_cache, k_addr, p);
+    issue(v_cache, v_addr, p);
+  }
+  // the queries of this head group as A fragments: rows g and g + 8, all of head_dim
+  unsigned qa[KS][4];
+  {
+    const __nv_bfloat16* q_lo = q + ((size_t)seq * n_q + (size_t)hk * G + g0 + g) * HD;
+    const __nv_bfloat16* q_hi = q_lo + (size_t)8 * HD;
+    const bool lo_ok = g < ng, hi_ok = g + 8 < ng;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const int c = ks * 16 + 2 * t;
+      qa[ks][0] = lo_ok ? *reinterpret_cast<const unsigned*>(q_lo + c) : 0u;
+      qa[ks][1] = hi_ok ? *reinterpret_cast<const unsigned*>(q_hi + c) : 0u;
+      qa[ks][2] = lo_ok ? *reinterpret_cast<const unsigned*>(q_lo + c + 8) : 0u;
+      qa[ks][3] = hi_ok ? *reinterpret_cast<const unsigned*>(q_hi + c + 8) : 0u;
+    }
+  }
+  float o[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+  float m_lo = -INFINITY, m_hi = -INFINITY;            // running maxima of rows g and g + 8
+  float l_lo = 0.f, l_hi = 0.f;                        // this lane's share of the running sums
+
+  // ldmatrix row addresses: lane i gives row (i & 7) of matrix (i >> 3)
+  const int lm_r = lane & 7, lm_m = lane >> 3;
+  for (; p <= p_last; p += WARPS) {
+    const bool more = p + WARPS <= p_last;
+    asm volatile("cp.async.wait_group 1;" ::: "memory");   // K of this page has arrived (V may be on its way)
+    __syncwarp();
+    // ---- S = Q K^T: 8 tiles of 8 keys
+    float s[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {                   // pairs of key tiles
+        unsigned b[4];
+        const int key = (2 * np + (lm_m >> 1)) * 8 + lm_r, col = ks * 16 + (lm_m & 1) * 8;
+        md_ldmatrix(b, k_addr + (unsigned)(key * PITCH + col) * 2u);
+        md_mma(s[2 * np], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b[0], b[1]);
+        md_mma(s[2 * np + 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b[2], b[3]);
+      }
+    }
+    __syncwarp();                                        // every lane has read K: its tile is free
+    if (more) issue(k_cache, k_addr, p + WARPS);
+    // ---- scale, mask, running maximum and sum; probabilities relative to the new maximum
+    const int first = max(lo - p * kMdPage, 0);
+    const int last = min(len - p * kMdPage, kMdPage);    // visible keys of the page: [first, last)
+    float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int key = nt * 8 + 2 * t + c;
+        const bool vis = key >= first && key < last;
+        s[nt][c] = vis ? s[nt][c] * scale : -INFINITY;
+        s[nt][2 + c] = vis ? s[nt][2 + c] * scale : -INFINITY;
+        mx_lo = fmaxf(mx_lo, s[nt][c]);
+        mx_hi = fmaxf(mx_hi, s[nt][2 + c]);
+      }
+    }
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+    const float n_lo = fmaxf(m_lo, mx_lo), n_hi = fmaxf(m_hi, mx_hi);     // finite: the page holds a visible key
+    const float f_lo = (m_lo == -INFINITY) ? 0.f : expf(m_lo - n_lo);
+    const float f_hi = (m_hi == -INFINITY) ? 0.f : expf(m_hi - n_hi);
+    m_lo = n_lo;
+    m_hi = n_hi;
+    float sum_lo = 0.f, sum_hi = 0.f;
+    unsigned pa[4][4];                                   // P as A fragments: 4 steps of 16 keys
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const float p0 = expf(s[nt][0] - n_lo), p1 = expf(s[nt][1] - n_lo);
+      const float p2 = expf(s[nt][2] - n_hi), p3 = expf(s[nt][3] - n_hi);
+      sum_lo += p0 + p1;
+      sum_hi += p2 + p3;
+      pa[nt >> 1][(nt & 1) * 2] = md_pack(p0, p1);
+      pa[nt >> 1][(nt & 1) * 2 + 1] = md_pack(p2, p3);
+    }
+    l_lo = l_lo * f_lo + sum_lo;
+    l_hi = l_hi * f_hi + sum_hi;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      o[nt][0] *= f_lo;
+      o[nt][1] *= f_lo;
+      o[nt][2] *= f_hi;
+      o[nt][3] *= f_hi;
+    }
+    // ---- O += P V
+    if (more) asm volatile("cp.async.wait_group 1;" ::: "memory");      // V of this page (the next K may be on its way)
+    else asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+      for (int np = 0; np < NT / 2; ++np) {
+        unsigned b[4];
+        const int key = kk * 16 + (lm_m & 1) * 8 + lm_r, col = (2 * np + (lm_m >> 1)) * 8;
+        md_ldmatrix_trans(b, v_addr + (unsigned)(key * PITCH + col) * 2u);
+        md_mma(o[2 * np], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b[0], b[1]);
+        md_mma(o[2 * np + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b[2], b[3]);
+      }
+    }
+    __syncwarp();                                        // every lane has read V
+    if (more) issue(v_cache, v_addr, p + WARPS);
+  }
+  if (!has_pages) asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+  // ---- the warps' results meet: each leaves (m, l, O) for its 16 rows in its own K tile
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  constexpr int kRowFloats = HD + 2;                    // O row, then m and l
+  float* mine = reinterpret_cast<float*>(k_tile);      // 16 rows of kRowFloats floats: fits a tile
+  __syncwarp();
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    mine[g * kRowFloats + nt * 8 + 2 * t] = o[nt][0];
+    mine[g * kRowFloats + nt * 8 + 2 * t + 1] = o[nt][1];
+    mine[(g + 8) * kRowFloats + nt * 8 + 2 * t] = o[nt][2];
+    mine[(g + 8) * kRowFloats + nt * 8 + 2 * t + 1] = o[nt][3];
+  }
+  if (t == 0) {
+    mine[g * kRowFloats + HD] = m_lo;
+    mine[g * kRowFloats + HD + 1] = l_lo;
+    mine[(g + 8) * kRowFloats + HD] = m_hi;
+    mine[(g + 8) * kRowFloats + HD + 1] = l_hi;
+  }
+  __syncthreads();
+  const float* all = reinterpret_cast<const float*>(md_smem);
+  constexpr int kWarpFloats = 2 * kTile / 2;            // floats between two warps' tiles (2 tiles of bf16)
+  for (int i = threadIdx.x; i < ng * HD; i += WARPS * 32) {
+    const int row = i / HD, d = i % HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) M = fmaxf(M, all[w * kWarpFloats + row * kRowFloats + HD]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      const float* r = all + w * kWarpFloats + row * kRowFloats;
+      const float mw = r[HD];
+      const float f = (mw == -INFINITY) ? 0.f : expf(mw - M);
+      num = fmaf(f, r[d], num);
+      den = fmaf(f, r[HD + 1], den);
+    }
+    const size_t head = (size_t)seq * n_q + (size_t)hk * G + g0 + row;
+    if (n_runs == 1) {
+      out[head * HD + d] = __float2bfloat16_rn(num / den);
+    } else {
+      part_acc[(head * n_runs + run) * HD + d] = num;
+      if (d == 0) {
+        part_m[head * n_runs + run] = M;
+        part_l[head * n_runs + run] = den;
+      }
+    }
+  }
+  if (n_runs == 1) return;
+  // ---- the block that finishes last for this (sequence, head group) merges the runs
+  const int r0 = (lo / kMdPage) / pages_per_run, r1 = ((len - 1) / kMdPage) / pages_per_run;
+  __threadfence();                     // this block's partial results are visible before it is counted
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* c = counters + (size_t)seq * gridDim.y + blockIdx.y;
+    const int done = atomicAdd(c, 1) + 1;
+    is_last = (done == r1 - r0 + 1);
+    if (is_last) *c = 0;               // left clean for the next launch
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int row = warp; row < ng; row += WARPS) {
+    const size_t head = (size_t)seq * n_q + (size_t)hk * G + g0 + row;
+    md_merge_head<HD>(part_m, part_l, part_acc, out + head * HD, head * n_runs, r0, r1);
+  }
+}
+
+template <int HD, int WARPS>
+static int launch_mma(const void* q, const void* k_cache, const void* v_cache, float* part_m, float* part_l,
+                      float* part_acc, const int* seq_slot, const int* seq_kvlen, const int* block_table, int max_pages,
+                      int n_seqs, int n_q, int n_kv, float scale, int window, int pages_per_run, int n_runs,
+                      int* counters, void* out, cudaStream_t stream) {
+  const int G = n_q / n_kv;
+  const int chunks = (G + 15) / 16;
+  const size_t smem = (size_t)WARPS * 2 * kMdPage * (HD + 8) * sizeof(__nv_bfloat16);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<HD, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  launch_k(decode_mma_kernel<HD, WARPS>, dim3(n_runs, n_kv * chunks, n_seqs), dim3(WARPS * 32), smem, stream,
+           (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, part_m, part_l,
+           part_acc, seq_slot, seq_kvlen, block_table, max_pages, n_q, n_kv, scale, window, pages_per_run, n_runs,
+           counters, (__nv_bfloat16*)out);
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
+
+}  // namespace llmie
+
+using namespace llmie;
+
+extern "C" int llmie_attention_decode_mma_supported(int head_dim, int dtype, int page_size) {
+  return (dtype == LLMIE_BF16 && page_size == 64 && (head_dim == 64 || head_dim == 128)) ? 1 : 0;
+}
+
+// Pages per block for a step of n_seqs sequences none longer than max_kv_len. A whole sequence per
+// block wherever its warps then take at most four pages each in turn: merging runs through global
+// memory costs more than a few pages (measured on B200, 8 sequences of 520 keys: one run 0.858 ms per
+// step, two runs 0.900 ms). Longer sequences are halved while the grid stays within max_blocks.
+// n_groups = KV heads x chunks of 16 query heads.
+extern "C" int llmie_attention_decode_mma_pages(int n_seqs, int n_groups, int max_kv_len, int max_blocks) {
+  const int total = max_kv_len > 0 ? (max_kv_len + kMdPage - 1) / kMdPage : 1;
+  int pp = total;
+  while (pp > 8 && (pp + 7) / 8 > 4) {
+    const int half = (pp + 1) / 2;
+    if ((long long)n_seqs * n_groups * ((total + half - 1) / half) > max_blocks) break;
+    pp = half;
+  }
+  return pp;
+}
+
+// q, out bfloat16 [n_seqs, n_q hd]; caches [pages, n_kv, 64, hd]; seq_kvlen: keys each sequence holds
+// including this step's. n_runs * pages_per_run * 64 must cover the longest sequence. part_*: float32
+// scratch as in llmie_attention_decode (untouched when n_runs == 1); counters: int32 zeros, one per
+// (sequence, KV head, chunk of 16 query heads), left zero.
+extern "C" int llmie_attention_decode_mma(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                          float* part_m, float* part_l, float* part_acc, int* counters,
+                                          const int* seq_slot, const int* seq_kvlen, const int* block_table,
+                                          int max_pages, int page_size, int n_seqs, int n_q, int n_kv, int hd,
+                                          float scale, int window, int pages_per_run, int n_runs,
+                                          cudaStream_t stream) {
+  if (n_seqs < 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv || max_pages <= 0 || pages_per_run <= 0 || n_runs <= 0)
+    return LLMIE_ERR_BAD_ARG;
+  if (!llmie_attention_decode_mma_supported(hd, LLMIE_BF16, page_size)) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (n_runs > 1 && (!part_m || !part_l || !part_acc || !counters)) return LLMIE_ERR_BAD_ARG;
+  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache)) return LLMIE_ERR_ALIGNMENT;
+  if (n_seqs == 0) return LLMIE_OK;
+  const int chunks = (n_q / n_kv + 15) / 16;
+  // Warps per block. More warps finish a block's pages sooner; fewer let more blocks stay on an SM at once
+  // (a block holds two page tiles per warp in shared memory), and a grid that does not fit in one wave
+  // takes two. Estimate: waves x (pages a warp takes in turn + a fixed part), smallest wins.
+  const long long blocks = (long long)n_seqs * n_kv * chunks * n_runs;
+  const int tile_bytes = 2 * kMdPage * (hd + 8) * (int)sizeof(__nv_bfloat16);
+  const int options[4] = {8, 4, 3, 2};
+  int best_w = 4;
+  double best_cost = 1e30;
+  for (int i = 0; i < 4; ++i) {
+    const int w = options[i];
+    if (w * tile_bytes > 200 * 1024) continue;
+    int per_sm = (220 * 1024) / (w * tile_bytes);
+    if (hd == 64 && per_sm > 12 / w) per_sm = 12 / w > 0 ? 12 / w : 1;       // registers
+    if (per_sm < 1) continue;
+    const long long slots = 148LL * per_sm;
+    const double waves = (double)((blocks + slots - 1) / slots);
+    const double cost = waves * ((pages_per_run + w - 1) / w + 1.5);
+    if (cost < best_cost) {
+      best_cost = cost;
+      best_w = w;
+    }
+  }
+#define LLMIE_MMA(HD, W)                                                                                         \
+  return launch_mma<HD, W>(q, k_cache, v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen, block_table,      \
+                           max_pages, n_seqs, n_q, n_kv, scale, window, pages_per_run, n_runs, counters, out, stream)
+  if (hd == 64) {
+    if (best_w == 8) LLMIE_MMA(64, 8);
+    if (best_w == 4) LLMIE_MMA(64, 4);
+    if (best_w == 3) LLMIE_MMA(64, 3);
+    LLMIE_MMA(64, 2);
+  }
+  if (best_w >= 4) LLMIE_MMA(128, 4);
+  if (best_w == 3) LLMIE_MMA(128, 3);
+  LLMIE_MMA(128, 2);
+#undef LLMIE_MMA
+}

@@ -4,6 +4,8 @@ in which case the caller falls back to the plain kernel of the same math (never 
 library path)."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..kernels import ops
@@ -14,6 +16,8 @@ class KernelPlan:
         self.engine = engine
         self.bf16 = engine.dtype == torch.bfloat16
         self._counters = None          # zeroed once; the decode attention kernel leaves them zero
+        # LLMIE_DECODE_ATTN=split keeps the CUDA-core split-KV kernel for every one-token step (for comparisons)
+        self.decode_attention = os.environ.get("LLMIE_DECODE_ATTN", "auto")
 
     def _decode_counters(self, need: int, device) -> torch.Tensor:
         if self._counters is None or self._counters.numel() < need:
@@ -29,6 +33,15 @@ class KernelPlan:
 
     def attention(self, ctx, q, kv, out, n_q, n_kv, head_dim, scale, window) -> bool:
         """Returns True when a specialised kernel ran."""
+        if ctx.decode and self.decode_attention != "split" \
+                and ops.attention_decode_mma_supported(head_dim, q.dtype, kv.page_size):
+            # bfloat16, head size 64 or 128: a warp per page on the tensor cores
+            pages = ops.attention_decode_mma_pages(ctx.n_seqs, n_q, n_kv, ctx.max_kv_len)
+            n_runs = ((ctx.max_kv_len + 63) // 64 + pages - 1) // pages
+            counters = self._decode_counters(ops.decode_counter_ints(ctx.n_seqs, n_q, n_kv), q.device)
+            ops.attention_decode_mma(q, kv.k, kv.v, out, ctx.seq_slot, ctx.seq_kvlen, kv.block_table, kv.page_size,
+                                     n_q, n_kv, head_dim, scale, window, pages, n_runs, counters=counters)
+            return True
         if ctx.decode and kv.page_size == 64 and ops.attention_decode_supported(head_dim, q.dtype):
             run = self.decode_run_length(ctx.n_seqs, head_dim, q.dtype)
             n_runs = (ctx.max_kv_len + run - 1) // run

@@ -31,6 +31,7 @@ FAMILIES: Dict[str, tuple] = {
     "elementwise": ("elementwise.cu", [], []),
     "attention_simt": ("attention_simt.cu", [], []),
     "attention_decode": ("attention_decode.cu", [], []),
+    "attention_decode_mma": ("attention_decode_mma.cu", [], []),
     "attention_prefill_tc": ("attention_prefill_tc.cu", [], []),
     "gemm_simt": ("gemm_simt.cu", [], []),
     "gemm_skinny": ("gemm_skinny.cu", [], []),

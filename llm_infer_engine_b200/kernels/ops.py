@@ -9,6 +9,7 @@ raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -262,6 +263,61 @@ def attention_decode(q, k_cache, v_cache, out, seq_slot, seq_kvlen, block_table,
              base + 8 * n_ml, seq_slot.data_ptr(), seq_kvlen.data_ptr(), block_table.data_ptr(),
              block_table.shape[1], page_size, n, n_q, n_kv, head_dim, float(scale), int(window), int(run_len),
              int(n_runs), _dt(q, "q"), _stream()), "attention_decode")
+    return out
+
+
+MMA_MAX_BLOCKS = int(os.environ.get("LLMIE_MMA_MAX_BLOCKS", 148 * 2))
+
+
+def attention_decode_mma_supported(head_dim: int, dtype: torch.dtype, page_size: int) -> bool:
+    if dtype != torch.bfloat16:
+        return False
+    f = _fn("attention_decode_mma", "llmie_attention_decode_mma_supported", [_c_int] * 3)
+    return bool(f(head_dim, _DT[dtype], page_size))
+
+
+def attention_decode_mma_pages(n_seqs: int, n_q: int, n_kv: int, max_kv_len: int,
+                               max_blocks: Optional[int] = None) -> int:
+    """Cache pages per block that attention_decode_mma wants for this step's shape."""
+    groups = n_kv * ((n_q // n_kv + 15) // 16)
+    f = _fn("attention_decode_mma", "llmie_attention_decode_mma_pages", [_c_int] * 4)
+    return int(f(n_seqs, groups, max_kv_len, MMA_MAX_BLOCKS if max_blocks is None else max_blocks))
+
+
+def attention_decode_mma(q, k_cache, v_cache, out, seq_slot, seq_kvlen, block_table, page_size: int, n_q: int,
+                         n_kv: int, head_dim: int, scale: float, window: int, pages_per_run: int, n_runs: int,
+                         counters: Optional[torch.Tensor] = None, scratch: Optional[torch.Tensor] = None):
+    """Attention for a one-token step on the tensor cores (bfloat16): a warp per cache page, the warps of a
+    block merged in shared memory. Arguments as attention_decode; n_runs * pages_per_run pages must cover
+    the longest sequence. With n_runs == 1 neither scratch nor counters are touched."""
+    n = q.shape[0]
+    _need(q, "q", torch.bfloat16, (n, n_q * head_dim))
+    _need(out, "out", torch.bfloat16, (n, n_q * head_dim))
+    _need(k_cache, "k_cache", torch.bfloat16, (None, n_kv, page_size, head_dim))
+    _need(v_cache, "v_cache", torch.bfloat16, tuple(k_cache.shape))
+    for name, t in (("seq_slot", seq_slot), ("seq_kvlen", seq_kvlen), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    if seq_slot.numel() < n or seq_kvlen.numel() < n:
+        raise KernelError("attention_decode_mma: seq_slot / seq_kvlen shorter than the number of sequences")
+    base = n_ml = 0
+    cptr = None
+    if n_runs > 1:
+        need = decode_scratch_floats(n, n_q, head_dim, n_runs)
+        if scratch is None:
+            scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+        _need(scratch, "scratch", torch.float32)
+        if scratch.numel() < need:
+            raise KernelError(f"attention_decode_mma: scratch holds {scratch.numel()} floats, {need} are needed")
+        if counters is None or counters.numel() < n * n_kv * ((n_q // n_kv + 15) // 16):
+            raise KernelError("attention_decode_mma: counters are needed when a sequence spans several runs")
+        _need(counters, "counters", torch.int32)
+        base, n_ml, cptr = scratch.data_ptr(), n * n_q * n_runs, counters.data_ptr()
+    f = _fn("attention_decode_mma", "llmie_attention_decode_mma",
+            [_c_void_p] * 11 + [_c_int] * 6 + [_c_float] + [_c_int] * 3 + [_c_void_p])
+    _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), base or None,
+             (base + 4 * n_ml) or None, (base + 8 * n_ml) or None, cptr, seq_slot.data_ptr(), seq_kvlen.data_ptr(),
+             block_table.data_ptr(), block_table.shape[1], page_size, n, n_q, n_kv, head_dim, float(scale),
+             int(window), int(pages_per_run), int(n_runs), _stream()), "attention_decode_mma")
     return out
 
 

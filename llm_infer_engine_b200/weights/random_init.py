@@ -63,3 +63,14 @@ def write_random_model(config_json: dict, out_dir: str, seed: int, std: float = 
     save_file(tensors, os.path.join(out_dir, "model.safetensors"),
               metadata={"format": "pt", "seed": str(seed), "std": str(std)})
     return out_dir
+
+
+def scratch_folder(prefix: str) -> str:
+    """A new temporary folder that is deleted when the process exits (model folders of random
+    weights are gigabytes; nothing else removes them)."""
+    import atexit
+    import shutil
+    import tempfile
+    folder = tempfile.mkdtemp(prefix=prefix)
+    atexit.register(shutil.rmtree, folder, True)
+    return folder

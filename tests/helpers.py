@@ -3,12 +3,12 @@ import json
 import os
 import subprocess
 import sys
-import tempfile
 
 import numpy as np
 import torch
 
 import plain_llama as plain
+from llm_infer_engine_b200.weights import scratch_folder  # noqa: F401  (temporary folders deleted at exit)
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -31,7 +31,7 @@ def model_folder(tag: str, dtype: str = "bfloat16", std: float = None) -> str:
     key = (tag, dtype, std)
     if key not in _folders:
         spec = TINY[tag]
-        d = tempfile.mkdtemp(prefix=f"llmie_tiny_{tag}_")
+        d = scratch_folder(f"llmie_tiny_{tag}_")
         write_random_model(spec["cfg"], d, seed=spec["seed"], std=std or spec["std"], norm_range=spec["norm_range"],
                            dtype=dtype)
         _folders[key] = d
@@ -123,7 +123,7 @@ def run_plan_engine(engine, steps):
 
 def run_plan_trace_run(folder: str, dtype: str, steps, max_tokens: int, vocab: int, env=None):
     """Runs bin/trace_run as a subprocess; returns {id: [T, V] logits}."""
-    out = tempfile.mkdtemp(prefix="llmie_trace_")
+    out = scratch_folder("llmie_trace_")
     text = "\n".join(json.dumps(s) for s in steps) + "\n"
     proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
                            "--out", out, "--max-tokens", str(max_tokens)], input=text, capture_output=True, text=True,

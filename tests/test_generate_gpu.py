@@ -150,14 +150,14 @@ def test_far_keys_and_page_edges_matter(dtype, tol):
     projections are scaled up so that each query looks hard at a few keys, many of them far away
     or across page edges; one token at a time over several pages, slots used again."""
     from safetensors.torch import load_file, save_file
-    import json, tempfile
+    import json
     from llm_infer_engine_b200 import Engine
     src = helpers.model_folder("b")
     t = load_file(os.path.join(src, "model.safetensors"))
     for name in t:
         if "q_proj" in name or "k_proj" in name:
             t[name] = (t[name].float() * 6.0).to(torch.bfloat16)
-    folder = tempfile.mkdtemp(prefix="llmie_sharp_")
+    folder = helpers.scratch_folder("llmie_sharp_")
     save_file(t, os.path.join(folder, "model.safetensors"))
     json.dump(helpers.read_config(src), open(os.path.join(folder, "config.json"), "w"))
     w, cfg = helpers.plain_weights(folder), helpers.read_config(folder)

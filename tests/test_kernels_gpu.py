@@ -511,3 +511,62 @@ def test_attention_decode_many_sequences(dtype, n_q, n_kv, hd):
                                     pg.dense_v[i].float(), [lens[i] - 1], hd ** -0.5, window)[0]
                 assert torch.allclose(got[i], ref, atol=tol(dtype, 2e-5, 3e-2)), (window, fused, i)
         assert int(counters.abs().sum()) == 0          # left clean
+
+
+def test_attention_decode_mma_page_choice():
+    o = ops()
+    # a whole sequence per block while a warp takes at most four pages in turn
+    assert o.attention_decode_mma_pages(8, 32, 8, 512) == 8
+    assert o.attention_decode_mma_pages(8, 32, 8, 1024) == 16
+    assert o.attention_decode_mma_pages(64, 32, 8, 1024) == 16
+    assert o.attention_decode_mma_pages(8, 32, 8, 4096) == 32          # two runs, 128 blocks
+    assert o.attention_decode_mma_pages(256, 32, 8, 4096) == 64        # enough blocks already
+    for n, kv in ((1, 64), (1, 131072), (48, 640), (64, 8192), (256, 131072)):
+        pp = o.attention_decode_mma_pages(n, 32, 8, kv)
+        assert 1 <= pp <= (kv + 63) // 64
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd", [(32, 8, 64), (6, 2, 128), (40, 2, 64), (3, 3, 64)])
+@pytest.mark.parametrize("n_seqs,pages_per_run", [(36, 16), (36, 4), (5, 16), (5, 8), (2, 1)])
+def test_attention_decode_mma(n_q, n_kv, hd, n_seqs, pages_per_run):
+    check_attention_decode_mma(n_q, n_kv, hd, n_seqs, pages_per_run)
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd,n_seqs", [(32, 8, 64, 64), (32, 8, 64, 80), (6, 2, 128, 80), (6, 2, 128, 200)])
+def test_attention_decode_mma_block_forms(n_q, n_kv, hd, n_seqs):
+    """Grids that make the launcher take three and two warps per block."""
+    check_attention_decode_mma(n_q, n_kv, hd, n_seqs, 16)
+
+
+def check_attention_decode_mma(n_q, n_kv, hd, n_seqs, pages_per_run):
+    """A warp per page on the tensor cores: whole sequences in one block (written straight to the output)
+    and several runs (merged by the last block), few and many blocks (8 or 4 warps), groups of more than
+    16 query heads, with and without a window, lengths on, before and after a page boundary."""
+    o = ops()
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(11 + hd + pages_per_run + n_seqs)
+    lens = [int(x) for x in torch.randint(1, 1000, (n_seqs,), generator=g)]
+    special = [1, 1000, 64, 65, 128]
+    for i in range(min(n_seqs, len(special))):
+        lens[i] = special[i]
+    pg = Paged(lens, n_kv, hd, dtype, seed=hd)
+    pg.fill()
+    q = torch.randn(len(lens), n_q, hd, generator=g) * 2.0        # peaked scores: a skipped page would show
+    k_dev, v_dev, bt = pg.dev()
+    qd = q.to(dtype).reshape(len(lens), n_q * hd).to(DEV)
+    slots = torch.tensor(pg.slots, dtype=torch.int32, device=DEV)
+    kvlen = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    n_runs = (16 + pages_per_run - 1) // pages_per_run            # 16 pages hold 1024 keys
+    counters = torch.zeros(max(64, len(lens) * n_kv * 4), dtype=torch.int32, device=DEV)
+    assert o.attention_decode_mma_supported(hd, dtype, 64)
+    for window in (0, 90):
+        out = torch.full((len(lens), n_q * hd), float("nan"), dtype=dtype, device=DEV)
+        o.attention_decode_mma(qd, k_dev, v_dev, out, slots, kvlen, bt, 64, n_q, n_kv, hd, hd ** -0.5, window,
+                               pages_per_run, n_runs, counters=counters)
+        got = out.float().cpu().view(len(lens), n_q, hd)
+        assert not torch.isnan(got).any()
+        for i in sorted(set([0, 1, 2, 3, 4, 7, 23, 35, n_seqs - 1]) & set(range(n_seqs))):
+            ref = ref_attention(qd.float().cpu().view(len(lens), n_q, hd)[i:i + 1], pg.dense_k[i].float(),
+                                pg.dense_v[i].float(), [lens[i] - 1], hd ** -0.5, window)[0]
+            assert torch.allclose(got[i], ref, atol=3e-2), (window, i, float((got[i] - ref).abs().max()))
+    assert int(counters.abs().sum()) == 0          # left clean

@@ -3,7 +3,6 @@ the float32 engine must match the plain implementation closely however the work 
 bfloat16 engine (tensor-core attention, fused one-token kernels, head size 128, 128256-token
 vocabulary) must stay within bfloat16 rounding of it."""
 import copy
-import tempfile
 
 import pytest
 import torch
@@ -33,7 +32,7 @@ _cache = {}
 def setup(tag):
     if tag not in _cache:
         from llm_infer_engine_b200 import write_random_model
-        folder = tempfile.mkdtemp(prefix=f"llmie_{tag}_")
+        folder = helpers.scratch_folder(f"llmie_{tag}_")
         write_random_model(SHAPES[tag], folder, seed=2, std=0.02)
         w = helpers.plain_weights(folder)
         requests = {f"q{i}": helpers.random_tokens(128256, n, seed=900 + i) for i, n in enumerate([70, 9, 150])}
