@@ -69,51 +69,124 @@ __device__ __forceinline__ void tile_rows(int tile, int hd, int half_n, int& lo,
   }
 }
 
+// Fused epilogue of one tile for the lane that holds rows (g, g + 8) and batch columns 2t, 2t + 1.
+template <int VAR>
+__device__ __forceinline__ void tile_epilogue(const float (&acc)[4], int lo, int hi, int g, int t, float rs0, float rs1,
+                                              int batch, void* out, int ldo, const RopeStoreArgs& rope) {
+#pragma unroll
+  for (int cc = 0; cc < 2; ++cc) {
+    const int b = 2 * t + cc;
+    if (b >= batch) continue;
+    const float rs = cc ? rs1 : rs0;
+    float x1 = acc[cc] * rs, x2 = acc[2 + cc] * rs;
+    if (VAR == kVarF32) {
+      float* o = reinterpret_cast<float*>(out) + (size_t)b * ldo;
+      o[lo + g] = x1;
+      o[hi + g] = x2;
+    } else if (VAR == kVarGateSwiGLU) {
+      const float act = x1 / (1.f + expf(-x1)) * x2;
+      reinterpret_cast<__nv_bfloat16*>(out)[(size_t)b * ldo + lo + g] = __float2bfloat16_rn(act);
+    } else {
+      // rows lo + g and lo + g + hd/2 of one head: elements i and i + hd/2
+      const int hd = rope.hd;
+      const int head = lo / hd, i = lo - head * hd + g, half = hd >> 1;
+      const int pos = rope.tok_pos[b];
+      if (head < rope.n_q + rope.n_kv) {
+        const float2 cs = rope.table[(size_t)min(pos, rope.table_len - 1) * half + i];
+        const float y1 = x1 * cs.x - x2 * cs.y, y2 = x2 * cs.x + x1 * cs.y;
+        x1 = y1;
+        x2 = y2;
+      }
+      __nv_bfloat16* dst = nullptr;
+      if (head < rope.n_q) {
+        dst = rope.q_out + ((size_t)b * rope.n_q + head) * hd;
+      } else if (rope.write_kv) {
+        const int slot = rope.seq_slot[rope.tok_seq[b]];
+        const int page = rope.block_table[(size_t)slot * rope.max_pages + pos / rope.page_size];
+        const bool is_k = head < rope.n_q + rope.n_kv;
+        const int hk = head - rope.n_q - (is_k ? 0 : rope.n_kv);
+        dst = (is_k ? rope.k_cache : rope.v_cache) +
+              (((size_t)page * rope.n_kv + hk) * rope.page_size + (pos % rope.page_size)) * hd;
+      }
+      if (dst) {
+        dst[i] = __float2bfloat16_rn(x1);
+        dst[i + half] = __float2bfloat16_rn(x2);
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void fd_team_sync(int team, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(threads) : "memory");
+}
+
+// The block's warps form teams of S warps (S a power of two up to WARPS). A team takes a tile of 16
+// weight rows at a time (tile numbers go round the blocks first); each of its warps owns a
+// contiguous run of K and streams its share of the rows straight into mma.sync fragments. A warp's
+// work is a flat sequence of rounds (kFdUnroll chunks of 32 each) that runs on across tile
+// boundaries; two register buffers take turns, so the loads of the next round are always in flight
+// while the current one is used, and no buffer is ever copied. At the end of a tile the partial sums
+// meet in the team's first warp through shared memory (two buffers in turn, one team barrier per
+// tile; no block-wide barrier), whose lanes hold whole (row, row + 8) x (column pair) results: the
+// rotation pairs, the gate and up rows, or plain outputs. With S = 1 (many tiles: the LM head) a
+// warp streams whole rows and nothing is exchanged at all.
 template <int VAR, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 norm_gemm_kernel(const float* __restrict__ h, const float* __restrict__ norm_w, float eps,
                  const __nv_bfloat16* __restrict__ W, void* __restrict__ out, int batch, int K, int ldo, int tiles,
-                 int half_n, RopeStoreArgs rope) {
+                 int half_n, int S, RopeStoreArgs rope) {
   pdl_launch_dependents();
   extern __shared__ __align__(16) unsigned char fd_smem[];
   const int xs_stride = K + kFdPad;                                        // elements
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(fd_smem);           // [8][K + pad]
-  float* red = reinterpret_cast<float*>(fd_smem + (size_t)8 * xs_stride * 2);   // [WARPS][16][9]
-  float* ssw = red + WARPS * 16 * 9;                                       // [WARPS][8]
-  float* rstd = ssw + WARPS * 8;                                           // [8]
+  float4* red = reinterpret_cast<float4*>(fd_smem + (size_t)8 * xs_stride * 2);   // [2][WARPS][32]
+  float* ssw = reinterpret_cast<float*>(red + 2 * WARPS * 32);             // [WARPS][8]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
+  const int team = warp / S, j = warp - team * S;
   const int n_chunks = K >> 5;
-  // each warp takes a contiguous run of K, so that a row is read in long pieces
-  const int per_warp = (n_chunks + WARPS - 1) / WARPS;
-  const int c_begin = warp * per_warp, c_end = min(n_chunks, c_begin + per_warp);
+  const int per_warp = (n_chunks + S - 1) / S;
+  const int c_begin = j * per_warp, c_end = min(n_chunks, c_begin + per_warp);
+  const bool has_k = c_begin < c_end;          // a warp beyond the end of K only joins its team's barriers
+  const int n_rounds = has_k ? (c_end - c_begin + kFdUnroll - 1) / kFdUnroll : 1;
+  const int tile_stride = (WARPS / S) * gridDim.x;
   const int hd = rope.hd;
 
-  int tile = blockIdx.x;
-  int lo, hi;
-  // every weight row this block will stream, for all of its tiles, is asked into L2 right away
-  for (int i = threadIdx.x; ; i += WARPS * 32) {
-    const int tl = blockIdx.x + (i >> 4) * gridDim.x;
-    if (tl >= tiles) break;
-    int plo, phi;
-    tile_rows<VAR>(tl, hd, half_n, plo, phi);
-    const int r = i & 15;
-    l2_prefetch(W + (size_t)(r < 8 ? plo + r : phi + r - 8) * K, (unsigned)K * 2u);
-  }
-  tile_rows<VAR>(tile, hd, half_n, lo, hi);
-  const uint4* w_lo = reinterpret_cast<const uint4*>(W + (size_t)(lo + g) * K) + t;
-  const uint4* w_hi = reinterpret_cast<const uint4*>(W + (size_t)(hi + g) * K) + t;
-  uint4 wa[kFdUnroll], wb[kFdUnroll], na[kFdUnroll], nb2[kFdUnroll];
-#pragma unroll
-  for (int u = 0; u < kFdUnroll; ++u) {
-    const int c = c_begin + u;
-    if (c < c_end) {
-      wa[u] = fd_ldg16(w_lo + c * 4);
-      wb[u] = fd_ldg16(w_hi + c * 4);
-    }
-  }
-  pdl_wait();      // h is the previous kernels' result
+  int ltile = team * gridDim.x + blockIdx.x, lr = 0;   // where the next loads come from
+  const uint4* lw_lo = nullptr;
+  const uint4* lw_hi = nullptr;
+#define LLMIE_POINT_LOADS()                                                          \
+  do {                                                                               \
+    if (ltile < tiles) {                                                             \
+      int ra_, rb_;                                                                  \
+      tile_rows<VAR>(ltile, hd, half_n, ra_, rb_);                                   \
+      lw_lo = reinterpret_cast<const uint4*>(W + (size_t)(ra_ + g) * K) + t;         \
+      lw_hi = reinterpret_cast<const uint4*>(W + (size_t)(rb_ + g) * K) + t;         \
+    }                                                                                \
+  } while (0)
+#define LLMIE_ISSUE(wa, wb)                                                          \
+  do {                                                                               \
+    if (ltile < tiles && has_k) {                                                    \
+      const int lc0_ = c_begin + lr * kFdUnroll;                                     \
+      _Pragma("unroll") for (int u = 0; u < kFdUnroll; ++u) {                        \
+        const int c = lc0_ + u;                                                      \
+        if (c < c_end) {                                                             \
+          wa[u] = fd_ldg16(lw_lo + c * 4);                                           \
+          wb[u] = fd_ldg16(lw_hi + c * 4);                                           \
+        }                                                                            \
+      }                                                                              \
+      if (++lr >= n_rounds) {                                                        \
+        lr = 0;                                                                      \
+        ltile += tile_stride;                                                        \
+        LLMIE_POINT_LOADS();                                                         \
+      }                                                                              \
+    }                                                                                \
+  } while (0)
+  LLMIE_POINT_LOADS();
+  uint4 a0[kFdUnroll], b0[kFdUnroll], a1[kFdUnroll], b1[kFdUnroll];
+  LLMIE_ISSUE(a0, b0);     // weights are written by no kernel: on their way before the previous kernel has finished
+  pdl_wait();              // h is the previous kernels' result
 
   // ---- h * w as bfloat16 rows in shared memory, and the sum of squares of every row
   {
@@ -144,138 +217,79 @@ norm_gemm_kernel(const float* __restrict__ h, const float* __restrict__ norm_w, 
     }
 #pragma unroll
     for (int b = 0; b < 8; ++b) {
-      const float s = warp_sum(ssq[b]);
-      if (lane == 0) ssw[warp * 8 + b] = s;
+      const float sq = warp_sum(ssq[b]);
+      if (lane == 0) ssw[warp * 8 + b] = sq;
     }
     __syncthreads();
-    if (threadIdx.x < 8) {
-      float s = 0.f;
-      for (int w = 0; w < WARPS; ++w) s += ssw[w * 8 + threadIdx.x];
-      rstd[threadIdx.x] = rsqrtf(s / (float)K + eps);
+  }
+  float rs0, rs1;                     // rstd of the two batch columns this lane holds results of
+  {
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      s0 += ssw[w * 8 + 2 * t];
+      s1 += ssw[w * 8 + 2 * t + 1];
     }
-    __syncthreads();
+    rs0 = rsqrtf(s0 / (float)K + eps);
+    rs1 = rsqrtf(s1 / (float)K + eps);
   }
   const uint4* x_row = reinterpret_cast<const uint4*>(xs + (size_t)g * xs_stride) + t;   // this lane's batch row
 
-  // ---- tiles of 16 weight rows
+  int tile = team * gridDim.x + blockIdx.x, cr = 0, parity = 0;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};     // two chains of products, summed per tile
+#define LLMIE_CONSUME(wa, wb)                                                        \
+  do {                                                                               \
+    const int c0_ = c_begin + cr * kFdUnroll;                                        \
+    _Pragma("unroll") for (int u = 0; u < kFdUnroll; ++u) {                          \
+      const int c = c0_ + u;                                                         \
+      if (c < c_end) {                                                               \
+        const uint4 xv = x_row[c * 4];                                               \
+        fd_mma(acc, wa[u].x, wb[u].x, wa[u].y, wb[u].y, xv.x, xv.y);                 \
+        fd_mma(acc2, wa[u].z, wb[u].z, wa[u].w, wb[u].w, xv.z, xv.w);                \
+      }                                                                              \
+    }                                                                                \
+    if (++cr >= n_rounds) {                                                          \
+      _Pragma("unroll") for (int i = 0; i < 4; ++i) {                                \
+        acc[i] += acc2[i];                                                           \
+        acc2[i] = 0.f;                                                               \
+      }                                                                              \
+      if (S > 1) {                                                                   \
+        float4* mine = red + ((parity * WARPS + warp) * 32 + lane);                  \
+        if (j != 0) *mine = make_float4(acc[0], acc[1], acc[2], acc[3]);             \
+        fd_team_sync(team, S * 32);                                                  \
+        if (j == 0) {                                                                \
+          for (int o = 1; o < S; ++o) {                                              \
+            const float4 v = mine[o * 32];                                           \
+            acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;              \
+          }                                                                          \
+        }                                                                            \
+        parity ^= 1;                                                                 \
+      }                                                                              \
+      if (j == 0) {                                                                  \
+        int lo, hi;                                                                  \
+        tile_rows<VAR>(tile, hd, half_n, lo, hi);                                    \
+        tile_epilogue<VAR>(acc, lo, hi, g, t, rs0, rs1, batch, out, ldo, rope);      \
+      }                                                                              \
+      acc[0] = acc[1] = acc[2] = acc[3] = 0.f;                                       \
+      cr = 0;                                                                        \
+      tile += tile_stride;                                                           \
+    }                                                                                \
+  } while (0)
   while (tile < tiles) {
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    const int next_tile = tile + gridDim.x;
-    int nlo = 0, nhi = 0;
-    const uint4* nw_lo = w_lo;
-    const uint4* nw_hi = w_hi;
-    if (next_tile < tiles) {
-      tile_rows<VAR>(next_tile, hd, half_n, nlo, nhi);
-      nw_lo = reinterpret_cast<const uint4*>(W + (size_t)(nlo + g) * K) + t;
-      nw_hi = reinterpret_cast<const uint4*>(W + (size_t)(nhi + g) * K) + t;
-    }
-    for (int c0 = c_begin; c0 < c_end; c0 += kFdUnroll) {
-      // request what comes next: the next round of this tile, or the first round of the next tile
-      const bool last_round = c0 + kFdUnroll >= c_end;
-#pragma unroll
-      for (int u = 0; u < kFdUnroll; ++u) {
-        if (!last_round) {
-          const int c = c0 + kFdUnroll + u;
-          if (c < c_end) {
-            na[u] = fd_ldg16(w_lo + c * 4);
-            nb2[u] = fd_ldg16(w_hi + c * 4);
-          }
-        } else if (next_tile < tiles) {
-          const int c = c_begin + u;
-          if (c < c_end) {
-            na[u] = fd_ldg16(nw_lo + c * 4);
-            nb2[u] = fd_ldg16(nw_hi + c * 4);
-          }
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < kFdUnroll; ++u) {
-        const int c = c0 + u;
-        if (c < c_end) {
-          const uint4 xv = x_row[c * 4];
-          fd_mma(acc, wa[u].x, wb[u].x, wa[u].y, wb[u].y, xv.x, xv.y);
-          fd_mma(acc, wa[u].z, wb[u].z, wa[u].w, wb[u].w, xv.z, xv.w);
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < kFdUnroll; ++u) {
-        wa[u] = na[u];
-        wb[u] = nb2[u];
-      }
-    }
-    float* my = red + warp * 16 * 9;
-    my[g * 9 + 2 * t] = acc[0];
-    my[g * 9 + 2 * t + 1] = acc[1];
-    my[(g + 8) * 9 + 2 * t] = acc[2];
-    my[(g + 8) * 9 + 2 * t + 1] = acc[3];
-    __syncthreads();
-
-    if (VAR == kVarF32) {
-      for (int idx = threadIdx.x; idx < 128; idx += WARPS * 32) {
-        const int r = idx & 15, b = idx >> 4;
-        if (b >= batch) continue;
-        float v = 0.f;
-#pragma unroll
-        for (int w = 0; w < WARPS; ++w) v += red[(w * 16 + r) * 9 + b];
-        reinterpret_cast<float*>(out)[(size_t)b * ldo + (r < 8 ? lo + r : hi + r - 8)] = v * rstd[b];
-      }
-    } else {
-      for (int idx = threadIdx.x; idx < 64; idx += WARPS * 32) {
-        const int j = idx & 7, b = idx >> 3;
-        if (b >= batch) continue;
-        float x1 = 0.f, x2 = 0.f;
-#pragma unroll
-        for (int w = 0; w < WARPS; ++w) {
-          x1 += red[(w * 16 + j) * 9 + b];
-          x2 += red[(w * 16 + j + 8) * 9 + b];
-        }
-        x1 *= rstd[b];
-        x2 *= rstd[b];
-        if (VAR == kVarGateSwiGLU) {
-          const float act = x1 / (1.f + expf(-x1)) * x2;
-          reinterpret_cast<__nv_bfloat16*>(out)[(size_t)b * ldo + lo + j] = __float2bfloat16_rn(act);
-        } else {
-          // rows lo + j and lo + j + hd/2 of one head: elements i and i + hd/2
-          const int head = lo / hd, i = lo - head * hd + j, half = hd >> 1;
-          const int pos = rope.tok_pos[b];
-          if (head < rope.n_q + rope.n_kv) {
-            const float2 cs = rope.table[(size_t)min(pos, rope.table_len - 1) * half + i];
-            const float y1 = x1 * cs.x - x2 * cs.y, y2 = x2 * cs.x + x1 * cs.y;
-            x1 = y1;
-            x2 = y2;
-          }
-          __nv_bfloat16* dst;
-          if (head < rope.n_q) {
-            dst = rope.q_out + ((size_t)b * rope.n_q + head) * hd;
-          } else if (rope.write_kv) {
-            const int slot = rope.seq_slot[rope.tok_seq[b]];
-            const int page = rope.block_table[(size_t)slot * rope.max_pages + pos / rope.page_size];
-            const bool is_k = head < rope.n_q + rope.n_kv;
-            const int hk = head - rope.n_q - (is_k ? 0 : rope.n_kv);
-            dst = (is_k ? rope.k_cache : rope.v_cache) +
-                  (((size_t)page * rope.n_kv + hk) * rope.page_size + (pos % rope.page_size)) * hd;
-          } else {
-            dst = nullptr;
-          }
-          if (dst) {
-            dst[i] = __float2bfloat16_rn(x1);
-            dst[i + half] = __float2bfloat16_rn(x2);
-          }
-        }
-      }
-    }
-    __syncthreads();          // `red` is written again by the next tile
-    tile = next_tile;
-    lo = nlo;
-    hi = nhi;
-    w_lo = nw_lo;
-    w_hi = nw_hi;
+    LLMIE_ISSUE(a1, b1);
+    LLMIE_CONSUME(a0, b0);
+    if (tile >= tiles) break;
+    LLMIE_ISSUE(a0, b0);
+    LLMIE_CONSUME(a1, b1);
   }
+#undef LLMIE_POINT_LOADS
+#undef LLMIE_ISSUE
+#undef LLMIE_CONSUME
 }
 
 template <int VAR, int WARPS>
 static size_t fused_smem(int K) {
-  return (size_t)8 * (K + kFdPad) * 2 + (size_t)(WARPS * 16 * 9 + WARPS * 8 + 8) * sizeof(float);
+  return (size_t)8 * (K + kFdPad) * 2 + (size_t)2 * WARPS * 32 * sizeof(float4) + (size_t)WARPS * 8 * sizeof(float);
 }
 
 // Blocks of this instance that one SM holds at once (0 if it cannot run at all with this K).
@@ -297,34 +311,25 @@ static int fused_blocks_per_sm(int K) {
   return cached;
 }
 
-template <int VAR, int WARPS>
-static int launch_fused(const float* h, const float* norm_w, float eps, const void* W, void* out, int batch, int K,
-                        int ldo, int tiles, int half_n, const RopeStoreArgs& rope, cudaStream_t stream) {
-  const int per_sm = fused_blocks_per_sm<VAR, WARPS>(K);
-  if (per_sm < 1) return LLMIE_ERR_UNSUPPORTED_SIZE;
-  // as many blocks as stay resident together, evenly loaded: a block walks its tiles with the
-  // staged rows in place
-  const int resident = 148 * per_sm;
-  const int waves = (tiles + resident - 1) / resident;
-  const int blocks = (tiles + waves - 1) / waves;
-  launch_k(norm_gemm_kernel<VAR, WARPS>, dim3(blocks), dim3(WARPS * 32), fused_smem<VAR, WARPS>(K), stream, h, norm_w,
-           eps, (const __nv_bfloat16*)W, out, batch, K, ldo, tiles, half_n, rope);
-  LLMIE_LAUNCH_CHECK();
-  return LLMIE_OK;
-}
+constexpr int kFdWarps = 8;
 
-// Warps per block: the most (16, 8, 4) with which every tile still gets a block of its own in one
-// wave and every warp has work; matrices with more tiles than that take 8 warps and several tiles
-// per block.
+// Team size and grid: the largest teams with which every tile still gets a team of its own in one pass
+// over the warps the GPU holds at once; few tiles then make few blocks, spread over the SMs.
 template <int VAR>
 static int launch_fused_w(const float* h, const float* norm_w, float eps, const void* W, void* out, int batch, int K,
                           int ldo, int tiles, int half_n, const RopeStoreArgs& rope, cudaStream_t stream) {
-  const int chunks = K / 32;
-  if (chunks >= 16 * kFdUnroll && tiles <= 148 * fused_blocks_per_sm<VAR, 16>(K))
-    return launch_fused<VAR, 16>(h, norm_w, eps, W, out, batch, K, ldo, tiles, half_n, rope, stream);
-  if (chunks >= 8 * kFdUnroll && (tiles <= 148 * fused_blocks_per_sm<VAR, 8>(K) || chunks >= 16 * kFdUnroll))
-    return launch_fused<VAR, 8>(h, norm_w, eps, W, out, batch, K, ldo, tiles, half_n, rope, stream);
-  return launch_fused<VAR, 4>(h, norm_w, eps, W, out, batch, K, ldo, tiles, half_n, rope, stream);
+  const int per_sm = fused_blocks_per_sm<VAR, kFdWarps>(K);
+  if (per_sm < 1) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  const long long resident_warps = 148LL * per_sm * kFdWarps;
+  int S = kFdWarps;
+  while (S > 1 && (long long)tiles * S > resident_warps) S >>= 1;
+  const int teams_per_block = kFdWarps / S;
+  int blocks = (tiles + teams_per_block - 1) / teams_per_block;
+  if (blocks > 148 * per_sm) blocks = 148 * per_sm;
+  launch_k(norm_gemm_kernel<VAR, kFdWarps>, dim3(blocks), dim3(kFdWarps * 32), fused_smem<VAR, kFdWarps>(K), stream, h,
+           norm_w, eps, (const __nv_bfloat16*)W, out, batch, K, ldo, tiles, half_n, S, rope);
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
 }
 
 static int check_common(const float* h, const float* norm_w, const void* W, int batch, int N, int K) {

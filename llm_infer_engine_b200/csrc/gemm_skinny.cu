@@ -85,6 +85,21 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   // The weights are written by no kernel, so their first loads are already on their way while
   // the kernel before this one finishes; x (and out, for the add) are its results: wait for it here.
   pdl_wait();
+  // the activations of a round are requested a round ahead too, with the weights of that round, so
+  // that no round waits for an L2 round trip of its own (one batch block; more would not fit the registers)
+  constexpr bool kAhead = NB == 1;
+  uint4 xcur[kSkUnroll][NB], xnext[kSkUnroll][NB];
+  if (kAhead) {
+#pragma unroll
+    for (int u = 0; u < kSkUnroll; ++u) {
+      const int c = c_begin + u;
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+        xcur[u][nb] = make_uint4(0u, 0u, 0u, 0u);
+        if (c < c_end && xok[nb]) xcur[u][nb] = ldg16(xr[nb] + c * 4);
+      }
+    }
+  }
   for (int c0 = c_begin; c0 < c_end; c0 += kSkUnroll) {
 #pragma unroll
     for (int u = 0; u < kSkUnroll; ++u) {           // request the next round
@@ -93,15 +108,23 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         na[u] = ldg16(w_lo + c * 4);
         nbuf[u] = ldg16(w_hi + c * 4);
       }
+      if (kAhead) {
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          xnext[u][nb] = make_uint4(0u, 0u, 0u, 0u);
+          if (c < c_end && xok[nb]) xnext[u][nb] = ldg16(xr[nb] + c * 4);
+        }
+      }
     }
-    uint4 xv[kSkUnroll][NB];
+    if (!kAhead) {
 #pragma unroll
-    for (int u = 0; u < kSkUnroll; ++u) {
-      const int c = c0 + u;
+      for (int u = 0; u < kSkUnroll; ++u) {
+        const int c = c0 + u;
 #pragma unroll
-      for (int nb = 0; nb < NB; ++nb) {
-        xv[u][nb] = make_uint4(0u, 0u, 0u, 0u);
-        if (c < c_end && xok[nb]) xv[u][nb] = ldg16(xr[nb] + c * 4);
+        for (int nb = 0; nb < NB; ++nb) {
+          xcur[u][nb] = make_uint4(0u, 0u, 0u, 0u);
+          if (c < c_end && xok[nb]) xcur[u][nb] = ldg16(xr[nb] + c * 4);
+        }
       }
     }
 #pragma unroll
@@ -110,8 +133,8 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       if (c < c_end) {
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
-          mma_bf16_16x8x16(acc[nb], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xv[u][nb].x, xv[u][nb].y);
-          mma_bf16_16x8x16(acc[nb], wa[u].z, wb[u].z, wa[u].w, wb[u].w, xv[u][nb].z, xv[u][nb].w);
+          mma_bf16_16x8x16(acc[nb], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xcur[u][nb].x, xcur[u][nb].y);
+          mma_bf16_16x8x16(acc[nb], wa[u].z, wb[u].z, wa[u].w, wb[u].w, xcur[u][nb].z, xcur[u][nb].w);
         }
       }
     }
@@ -119,6 +142,10 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     for (int u = 0; u < kSkUnroll; ++u) {
       wa[u] = na[u];
       wb[u] = nbuf[u];
+      if (kAhead) {
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) xcur[u][nb] = xnext[u][nb];
+      }
     }
   }
   // this warp's share of K: rows g / g+8 of the tile, batch columns 2t, 2t+1 of each block
