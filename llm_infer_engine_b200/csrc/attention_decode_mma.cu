@@ -2,9 +2,9 @@
 //
 // One block serves one (sequence, KV head) - or one run of its pages - for up to 16 of the query
 // heads that share the KV head. The 16 x head_dim block of queries is the A operand of
-// mma.sync.m16n8k16; a WARP takes a whole page (64 keys) at a time: it copies the page's K and V
-// rows into its own shared-memory tiles (cp.async, the next page's K while this page's softmax
-// and P V run), computes S = Q K^T with 8 x head_dim/16 tensor-core products, keeps a running
+// mma.sync.m16n8k16; a WARP takes whole pages (64 keys), half a page at a time: it copies K and V
+// rows into its own two-stage shared-memory tiles (cp.async, the next half page while it works on
+// this one), computes S = Q K^T with 4 x head_dim/16 tensor-core products, keeps a running
 // maximum and sum per query head in registers (the online softmax of src/flash_attn.py:118-134
 // for one query row per head), converts P to bfloat16 in registers (the accumulator layout of two
 // neighbouring 8-key tiles is the A layout of one 16-key step) and adds P V. Warps of a block take
@@ -45,6 +45,13 @@ __device__ __forceinline__ void md_ldmatrix_trans(unsigned (&r)[4], unsigned add
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
+// 2^x by the special-function unit. Scores are kept in units of log2 (scaled by log2 e once), so every
+// exponential of the softmax and of the merges is this one instruction; -inf gives 0.
+__device__ __forceinline__ float md_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ unsigned md_pack(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<unsigned*>(&v);
@@ -66,7 +73,7 @@ __device__ __forceinline__ void md_merge_head(const float* part_m, const float* 
     const int r = c0 + lane;
     float w = 0.f;
     if (r <= r1) {
-      w = expf(__ldcg(part_m + base + r) - M);
+      w = md_exp2(__ldcg(part_m + base + r) - M);
       denom = fmaf(w, __ldcg(part_l + base + r), denom);
     }
     const int n_here = min(32, r1 - c0 + 1);
@@ -98,6 +105,7 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
   constexpr int NT = HD / 8;                            // n-tiles of P V
   constexpr int kTile = kMdPage * PITCH;                // elements of one staged page of K (or V)
   constexpr int kPieces = HD / 8;                       // 16-byte pieces per row
+  constexpr int kHalf = kMdPage / 2;                    // keys a warp works on at a time
   extern __shared__ __align__(16) unsigned char md_smem[];
   __shared__ int is_last;
 
@@ -116,32 +124,51 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
+  // this warp's shared memory: two stages, each a half page (32 keys) of K and of V
   __nv_bfloat16* k_tile = reinterpret_cast<__nv_bfloat16*>(md_smem) + (size_t)warp * 2 * kTile;
-  __nv_bfloat16* v_tile = k_tile + kTile;
-  const unsigned k_addr = (unsigned)__cvta_generic_to_shared(k_tile);
-  const unsigned v_addr = (unsigned)__cvta_generic_to_shared(v_tile);
+  const unsigned tile_addr = (unsigned)__cvta_generic_to_shared(k_tile);
+  constexpr unsigned kHalfBytes = (unsigned)(kHalf * PITCH * 2);          // one half page of K (or V)
   const int* pages = block_table + (size_t)seq_slot[seq] * max_pages;
   const size_t head_off = (size_t)hk * kMdPage * HD;
   const size_t page_stride = (size_t)n_kv * kMdPage * HD;
 
-  // a warp copies a whole page tile: 64 rows of HD elements into rows of PITCH elements
-  auto issue = [&](const __nv_bfloat16* cache, unsigned dst, int p) {
-    const __nv_bfloat16* src = cache + (size_t)pages[p] * page_stride + head_off;
+  // The warp's work is the sequence of half pages (p, h) of its pages that hold a visible key.
+  auto visible = [&](int p, int h) {
+    const int first = max(lo - p * kMdPage, 0), last = min(len - p * kMdPage, kMdPage);
+    return max(first, h * kHalf) < min(last, h * kHalf + kHalf);
+  };
+  auto advance = [&](int& p, int& h) {
+    do {
+      if (++h == 2) {
+        h = 0;
+        p += WARPS;
+      }
+    } while (p <= p_last && !visible(p, h));
+  };
+  // K and V rows of half page (p, h) into stage s: one group of asynchronous copies
+  auto issue = [&](int p, int h, int s) {
+    const size_t src = (size_t)pages[p] * page_stride + head_off + (size_t)h * kHalf * HD;
+    const unsigned dst = tile_addr + (unsigned)s * 2u * kHalfBytes;
 #pragma unroll
-    for (int i = 0; i < kMdPage * kPieces / 32; ++i) {
+    for (int i = 0; i < kHalf * kPieces / 32; ++i) {
       const int idx = i * 32 + lane;
       const int row = idx / kPieces, piece = idx % kPieces;
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (unsigned)(row * PITCH + piece * 8) * 2u),
-                   "l"(src + (size_t)row * HD + piece * 8) : "memory");
+      const unsigned off = (unsigned)(row * PITCH + piece * 8) * 2u;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + off),
+                   "l"(k_cache + src + (size_t)row * HD + piece * 8) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + kHalfBytes + off),
+                   "l"(v_cache + src + (size_t)row * HD + piece * 8) : "memory");
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
 
-  int p = p_first + warp;
-  const bool has_pages = p <= p_last;
-  if (has_pages) {
-    issue(k_cache, k_addr, p);
-    issue(v_cache, v_addr, p);
+  int p = p_first + warp, h = 0;
+  if (p <= p_last && !visible(p, h)) advance(p, h);
+  int np = p, nh = h;                                    // the unit after (p, h)
+  if (p <= p_last) {
+    issue(p, h, 0);
+    advance(np, nh);
+    if (np <= p_last) issue(np, nh, 1);
   }
   // the queries of this head group as A fragments: rows g and g + 8, all of head_dim
   unsigned qa[KS][4];
@@ -161,44 +188,45 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
   float o[NT][4];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
-  float m_lo = -INFINITY, m_hi = -INFINITY;            // running maxima of rows g and g + 8
+  float m_lo = -INFINITY, m_hi = -INFINITY;            // running maxima of rows g and g + 8 (units of log2)
   float l_lo = 0.f, l_hi = 0.f;                        // this lane's share of the running sums
 
+  const float scale2 = scale * 1.4426950408889634f;    // scores in units of log2
   // ldmatrix row addresses: lane i gives row (i & 7) of matrix (i >> 3)
   const int lm_r = lane & 7, lm_m = lane >> 3;
-  for (; p <= p_last; p += WARPS) {
-    const bool more = p + WARPS <= p_last;
-    asm volatile("cp.async.wait_group 1;" ::: "memory");   // K of this page has arrived (V may be on its way)
+  for (int idx = 0; p <= p_last; ++idx) {
+    const int s_ = idx & 1;
+    const unsigned k_addr = tile_addr + (unsigned)s_ * 2u * kHalfBytes, v_addr = k_addr + kHalfBytes;
+    if (np <= p_last) asm volatile("cp.async.wait_group 1;" ::: "memory");   // this unit has arrived, the next is on its way
+    else asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncwarp();
-    // ---- S = Q K^T: 8 tiles of 8 keys
-    float s[8][4];
+    // ---- S = Q K^T: 4 tiles of 8 keys
+    float s[4][4];
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+    for (int nt = 0; nt < 4; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {
 #pragma unroll
-      for (int np = 0; np < 4; ++np) {                   // pairs of key tiles
+      for (int pr = 0; pr < 2; ++pr) {                   // pairs of key tiles
         unsigned b[4];
-        const int key = (2 * np + (lm_m >> 1)) * 8 + lm_r, col = ks * 16 + (lm_m & 1) * 8;
+        const int key = (2 * pr + (lm_m >> 1)) * 8 + lm_r, col = ks * 16 + (lm_m & 1) * 8;
         md_ldmatrix(b, k_addr + (unsigned)(key * PITCH + col) * 2u);
-        md_mma(s[2 * np], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b[0], b[1]);
-        md_mma(s[2 * np + 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b[2], b[3]);
+        md_mma(s[2 * pr], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b[0], b[1]);
+        md_mma(s[2 * pr + 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b[2], b[3]);
       }
     }
-    __syncwarp();                                        // every lane has read K: its tile is free
-    if (more) issue(k_cache, k_addr, p + WARPS);
     // ---- scale, mask, running maximum and sum; probabilities relative to the new maximum
-    const int first = max(lo - p * kMdPage, 0);
-    const int last = min(len - p * kMdPage, kMdPage);    // visible keys of the page: [first, last)
+    const int first = max(lo - p * kMdPage, 0) - h * kHalf;
+    const int last = min(len - p * kMdPage, kMdPage) - h * kHalf;       // visible keys of the half page: [first, last)
     float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
+    for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         const int key = nt * 8 + 2 * t + c;
         const bool vis = key >= first && key < last;
-        s[nt][c] = vis ? s[nt][c] * scale : -INFINITY;
-        s[nt][2 + c] = vis ? s[nt][2 + c] * scale : -INFINITY;
+        s[nt][c] = vis ? s[nt][c] * scale2 : -INFINITY;
+        s[nt][2 + c] = vis ? s[nt][2 + c] * scale2 : -INFINITY;
         mx_lo = fmaxf(mx_lo, s[nt][c]);
         mx_hi = fmaxf(mx_hi, s[nt][2 + c]);
       }
@@ -207,17 +235,17 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
     mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
     mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
     mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-    const float n_lo = fmaxf(m_lo, mx_lo), n_hi = fmaxf(m_hi, mx_hi);     // finite: the page holds a visible key
-    const float f_lo = (m_lo == -INFINITY) ? 0.f : expf(m_lo - n_lo);
-    const float f_hi = (m_hi == -INFINITY) ? 0.f : expf(m_hi - n_hi);
+    const float n_lo = fmaxf(m_lo, mx_lo), n_hi = fmaxf(m_hi, mx_hi);     // finite: the unit holds a visible key
+    const float f_lo = md_exp2(m_lo - n_lo);             // 0 for the first unit (m = -inf)
+    const float f_hi = md_exp2(m_hi - n_hi);
     m_lo = n_lo;
     m_hi = n_hi;
     float sum_lo = 0.f, sum_hi = 0.f;
-    unsigned pa[4][4];                                   // P as A fragments: 4 steps of 16 keys
+    unsigned pa[2][4];                                   // P as A fragments: 2 steps of 16 keys
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-      const float p0 = expf(s[nt][0] - n_lo), p1 = expf(s[nt][1] - n_lo);
-      const float p2 = expf(s[nt][2] - n_hi), p3 = expf(s[nt][3] - n_hi);
+    for (int nt = 0; nt < 4; ++nt) {
+      const float p0 = md_exp2(s[nt][0] - n_lo), p1 = md_exp2(s[nt][1] - n_lo);
+      const float p2 = md_exp2(s[nt][2] - n_hi), p3 = md_exp2(s[nt][3] - n_hi);
       sum_lo += p0 + p1;
       sum_hi += p2 + p3;
       pa[nt >> 1][(nt & 1) * 2] = md_pack(p0, p1);
@@ -233,24 +261,25 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
       o[nt][3] *= f_hi;
     }
     // ---- O += P V
-    if (more) asm volatile("cp.async.wait_group 1;" ::: "memory");      // V of this page (the next K may be on its way)
-    else asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncwarp();
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {
+    for (int kk = 0; kk < 2; ++kk) {
 #pragma unroll
-      for (int np = 0; np < NT / 2; ++np) {
+      for (int pr = 0; pr < NT / 2; ++pr) {
         unsigned b[4];
-        const int key = kk * 16 + (lm_m & 1) * 8 + lm_r, col = (2 * np + (lm_m >> 1)) * 8;
+        const int key = kk * 16 + (lm_m & 1) * 8 + lm_r, col = (2 * pr + (lm_m >> 1)) * 8;
         md_ldmatrix_trans(b, v_addr + (unsigned)(key * PITCH + col) * 2u);
-        md_mma(o[2 * np], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b[0], b[1]);
-        md_mma(o[2 * np + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b[2], b[3]);
+        md_mma(o[2 * pr], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b[0], b[1]);
+        md_mma(o[2 * pr + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b[2], b[3]);
       }
     }
-    __syncwarp();                                        // every lane has read V
-    if (more) issue(v_cache, v_addr, p + WARPS);
+    __syncwarp();                                        // every lane has read this stage: it is free
+    p = np;
+    h = nh;
+    if (np <= p_last) {
+      advance(np, nh);
+      if (np <= p_last) issue(np, nh, s_);
+    }
   }
-  if (!has_pages) asm volatile("cp.async.wait_group 0;" ::: "memory");
 
   // ---- the warps' results meet: each leaves (m, l, O) for its 16 rows in its own K tile
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
@@ -286,7 +315,7 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
     for (int w = 0; w < WARPS; ++w) {
       const float* r = all + w * kWarpFloats + row * kRowFloats;
       const float mw = r[HD];
-      const float f = (mw == -INFINITY) ? 0.f : expf(mw - M);
+      const float f = (mw == -INFINITY) ? 0.f : md_exp2(mw - M);
       num = fmaf(f, r[d], num);
       den = fmaf(f, r[HD + 1], den);
     }

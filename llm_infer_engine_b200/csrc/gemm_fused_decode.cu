@@ -185,7 +185,8 @@ norm_gemm_kernel(const float* __restrict__ h, const float* __restrict__ norm_w, 
   } while (0)
   LLMIE_POINT_LOADS();
   uint4 a0[kFdUnroll], b0[kFdUnroll], a1[kFdUnroll], b1[kFdUnroll];
-  LLMIE_ISSUE(a0, b0);     // weights are written by no kernel: on their way before the previous kernel has finished
+  LLMIE_ISSUE(a0, b0);     // weights are written by no kernel: two rounds are on their way before the
+  LLMIE_ISSUE(a1, b1);     // previous kernel has finished
   pdl_wait();              // h is the previous kernels' result
 
   // ---- h * w as bfloat16 rows in shared memory, and the sum of squares of every row
@@ -276,11 +277,11 @@ norm_gemm_kernel(const float* __restrict__ h, const float* __restrict__ norm_w, 
     }                                                                                \
   } while (0)
   while (tile < tiles) {
-    LLMIE_ISSUE(a1, b1);
     LLMIE_CONSUME(a0, b0);
-    if (tile >= tiles) break;
     LLMIE_ISSUE(a0, b0);
+    if (tile >= tiles) break;
     LLMIE_CONSUME(a1, b1);
+    LLMIE_ISSUE(a1, b1);
   }
 #undef LLMIE_POINT_LOADS
 #undef LLMIE_ISSUE
