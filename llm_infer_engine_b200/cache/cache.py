@@ -97,6 +97,7 @@ class Cache:
         self.device = torch.device(device)
         self.slots = FreeList(n_slots, "slot")
         self.lengths: List[int] = [0] * (n_slots + 1)          # host mirror of seq_lens
+        self._mapped_upto: List[int] = [0] * (n_slots + 1)     # positions below this are writable without a new page
         self.seq_lens = torch.zeros(n_slots + 1, dtype=torch.int32, device=device)
 
         self._groups: Dict[KVRequest, _KVGroup] = {}
@@ -164,6 +165,7 @@ class Cache:
             store[:, slot].zero_()
         if self.lengths[slot] != 0:
             self.lengths[slot] = 0
+        self._mapped_upto[slot] = 0
         self.seq_lens[slot:slot + 1].zero_()
         return slot
 
@@ -174,6 +176,7 @@ class Cache:
             g.table.close_slot(slot)
         self.slots.give_back(slot)
         self.lengths[slot] = 0
+        self._mapped_upto[slot] = 0
 
     # ---------------------------------------------------------------- growth
     def pages_needed(self, slot: int, n_new: int) -> int:
@@ -188,6 +191,8 @@ class Cache:
     def reserve(self, slot: int, new_len: int) -> None:
         """Maps pages so that positions < new_len of `slot` can be written; updates the device
         block tables. Does not change the length."""
+        if new_len <= self._mapped_upto[slot]:
+            return                       # the common case of a one-token step inside a mapped page
         if not self.slots.is_held(slot):
             raise CacheError(f"slot {slot} is not held")
         if new_len > self.max_seq_len:
@@ -209,6 +214,8 @@ class Cache:
                 else:
                     for lp, pp in mapped:
                         g.block_table[slot, lp:lp + 1].copy_(torch.tensor([pp], dtype=torch.int32))
+        if new_len > 0:
+            self._mapped_upto[slot] = ((new_len - 1) // PAGE_SIZE + 1) * PAGE_SIZE
 
     def note_appended(self, slot: int, new_len: int, device_updated: bool) -> None:
         """Records that `slot` now holds new_len tokens. `device_updated` says whether a kernel

@@ -123,6 +123,8 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
         d1 = torch.cuda.Event(enable_timing=True)
         d0.record()
         graph = None
+        host_view = host_tokens.numpy()              # the same pinned memory, without tensor overheads
+        stream = torch.cuda.current_stream()
         while True:
             # --- decide on the host
             if on_tokens is not None:
@@ -148,7 +150,7 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
             live_slots = [slots[i] for i in live]
             # the tokens go back in from pinned host memory, as the reference writes each sampled id
             # into its device input buffer (main.py:282): the host may have the last word on them
-            host_tokens[:n] = torch.tensor(still_tokens, dtype=torch.int32)
+            host_view[:n] = still_tokens
             if engine.use_cuda_graph:
                 lanes = bucket_for(n)
                 longest = max(cache.lengths[s] for s in live_slots) + 1
@@ -177,8 +179,8 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
                 ops.sample(logits, sampled, sampling.temperature, sampling.top_p, sampling.seed, seq_ids, counters)
             # same stream: the upload above has read the pinned buffer before this download writes it
             host_tokens[:n].copy_(sampled[:n], non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-            new = host_tokens[:n].tolist()
+            stream.synchronize()
+            new = host_view[:n].tolist()
             stats.decode_steps += 1
             stats.decode_tokens += n
         d1.record()

@@ -54,7 +54,13 @@ def _check(status: int, name: str) -> None:
     raise KernelError(f"{name}: CUDA error {status} at launch")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current CUDA stream of the current device as a raw handle."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -552,6 +558,9 @@ def decode_stack(layers: torch.Tensor, n_layers: int, embedding, final_norm, fin
              counters.data_ptr(), tc_status_word(logits.device).data_ptr(), _ptr(phase_ns), _stream()), "decode_stack")
 
 
+_argmax_parts = {}
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """Greedy token per row of float32 logits [R, V] (lowest index wins a tie), many blocks per row."""
     R, V = logits.shape
@@ -560,8 +569,13 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     if out.shape[0] < R:
         raise KernelError("argmax: out is shorter than the number of rows")
     slices = max(1, min(128, V // 1024))
-    part_val = torch.empty(R * slices, dtype=torch.float32, device=logits.device)
-    part_idx = torch.empty(R * slices, dtype=torch.int32, device=logits.device)
+    key = (logits.device, R * slices)
+    parts = _argmax_parts.get(key)
+    if parts is None:        # kept: a generation loop calls this once per step (calls on one stream are ordered)
+        parts = (torch.empty(R * slices, dtype=torch.float32, device=logits.device),
+                 torch.empty(R * slices, dtype=torch.int32, device=logits.device))
+        _argmax_parts[key] = parts
+    part_val, part_idx = parts
     f = _fn("sampling", "llmie_argmax", [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p,
                                          _c_void_p])
     _check(f(logits.data_ptr(), R, V, logits.stride(0), slices, part_val.data_ptr(), part_idx.data_ptr(),
