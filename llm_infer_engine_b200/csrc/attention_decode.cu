@@ -21,7 +21,6 @@ namespace llmie {
 
 constexpr int kDecWarps = 4;
 constexpr int kDecThreads = kDecWarps * 32;
-constexpr int kStagedFromSeqs = 32;   // from this many sequences on, pages are staged in shared memory
 
 template <typename T> struct Vec16;
 template <> struct Vec16<__nv_bfloat16> { static constexpr int E = 8; };
@@ -42,22 +41,11 @@ __device__ __forceinline__ int first_visible(int len, int window) {
   return (window > 0 && len - window > 0) ? len - window : 0;
 }
 
-// Pages a staged block handles. Measured on B200 (64 sequences, context 640, head size 64): one
-// page per block gives 40.2 k tokens/s for the whole decode step, four pages 36.0 k: more, smaller
-// blocks keep more pages in flight. The kernel itself takes 1, 2 or 4.
-constexpr int kStagedPages = 1;
-template <typename T, int HD>
-constexpr int staged_pages() {
-  constexpr int fit = 65536 / (2 * 64 * HD * (int)sizeof(T));
-  constexpr int want = kStagedPages;
-  return fit >= want ? want : (fit >= 2 && want >= 2 ? 2 : 1);
-}
-
-// One block = one run of PAGES cache pages (64 keys each) of one KV head of one sequence, for all
-// its query heads. A page's K and V rows are contiguous in the cache, so the block asks for all of
-// them at once (every 16-byte load is issued before anything is computed): one memory latency per
-// block instead of one per key. run_len must equal 64 * PAGES; registers (not STAGED) hold one page.
-template <typename T, int HD, int GMAX, bool STAGED, int PAGES>
+// One block = one cache page (64 keys) of one KV head of one sequence, for all its query heads. A
+// page's K and V rows are contiguous in the cache, so the block asks for all of them at once (every
+// 16-byte load is issued, straight into registers, before anything is computed): one memory latency
+// per block instead of one per key. run_len must be 64.
+template <typename T, int HD, int GMAX>
 __global__ void __launch_bounds__(kDecThreads)
 decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                     float* __restrict__ part_m, float* __restrict__ part_l, float* __restrict__ part_acc,
@@ -70,8 +58,7 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, cons
   constexpr int E = Vec16<T>::E;
   constexpr int LPK = HD / E;          // lanes per key
   constexpr int KPW = 32 / LPK;        // keys per warp per iteration
-  constexpr int kRun = 64 * PAGES;     // keys per block
-  static_assert(STAGED || PAGES == 1, "registers hold one page");
+  constexpr int kRun = 64;             // keys per block
   __shared__ int is_last;
   constexpr int kIter = kRun / (kDecWarps * KPW);
   static_assert(LPK >= 1 && LPK <= 32 && 32 % LPK == 0 && kIter >= 1, "head size not supported by this kernel");
@@ -98,46 +85,23 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, cons
   const int* pages = block_table + (size_t)seq_slot[seq] * max_pages;
   const size_t head_off = (size_t)hk * page_size * HD;
   const size_t page_stride = (size_t)n_kv * page_size * HD;
-  const size_t page_base = (size_t)pages[begin / 64] * page_stride + head_off;     // first visible page (PAGES == 1: the page)
+  const size_t page_base = (size_t)pages[begin / 64] * page_stride + head_off;     // the page
   const T* kp = k_cache + page_base;
   const T* vp = v_cache + page_base;
 
-  // Every byte of this block's K and V pages is requested here, before anything is computed. Rows
-  // outside [first, first + n_keys) hold other positions of a page (never another sequence's), or
-  // were not loaded at all; they are never used.
-  //   STAGED (many sequences): asynchronous 16-byte copies into shared memory; no registers are
-  //   tied up, so many blocks per SM keep their pages in flight at once.
-  //   otherwise (few sequences, latency matters most): straight into registers.
-  extern __shared__ __align__(16) unsigned char page_smem[];
-  T* ks = reinterpret_cast<T*>(page_smem);                  // [kRun][HD]
-  T* vs = ks + kRun * HD;
-  float kreg[STAGED ? 1 : kIter][E], vreg[STAGED ? 1 : kIter][E];
-  if constexpr (STAGED) {
-    constexpr int kVecs = 64 * HD / E;                      // 16-byte pieces per page
-    const unsigned ks_addr = (unsigned)__cvta_generic_to_shared(ks), vs_addr = (unsigned)__cvta_generic_to_shared(vs);
+  // Every byte of this block's K and V page is requested here, before anything is computed. Rows
+  // outside [first, first + n_keys) hold other positions of the page (never another sequence's);
+  // they get probability zero.
+  float kreg[kIter][E], vreg[kIter][E];
 #pragma unroll
-    for (int pg = 0; pg < PAGES; ++pg) {
-      const int lp = run * PAGES + pg;                      // logical page
-      if (lp * 64 >= end || (lp + 1) * 64 <= begin) continue;     // holds no visible key
-      const size_t src = (size_t)pages[lp] * page_stride + head_off;
-      const unsigned dst = (unsigned)(pg * 64 * HD * sizeof(T));
-      for (int i = threadIdx.x; i < kVecs; i += kDecThreads) {
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ks_addr + dst + i * 16), "l"(k_cache + src + (size_t)i * E) : "memory");
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vs_addr + dst + i * 16), "l"(v_cache + src + (size_t)i * E) : "memory");
-      }
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-  } else {
+  for (int it = 0; it < kIter; ++it) {
+    const int row = (it * kDecWarps + warp) * KPW + sub;
+    load_vec<T, E>(kp + (size_t)row * HD + e0, kreg[it]);
+  }
 #pragma unroll
-    for (int it = 0; it < kIter; ++it) {
-      const int row = (it * kDecWarps + warp) * KPW + sub;
-      load_vec<T, E>(kp + (size_t)row * HD + e0, kreg[it]);
-    }
-#pragma unroll
-    for (int it = 0; it < kIter; ++it) {
-      const int row = (it * kDecWarps + warp) * KPW + sub;
-      load_vec<T, E>(vp + (size_t)row * HD + e0, vreg[it]);
-    }
+  for (int it = 0; it < kIter; ++it) {
+    const int row = (it * kDecWarps + warp) * KPW + sub;
+    load_vec<T, E>(vp + (size_t)row * HD + e0, vreg[it]);
   }
   // this lane's slice of each query head, pre-scaled
   float qv[GMAX][E];
@@ -155,22 +119,13 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, cons
     }
   }
 
-  if constexpr (STAGED) {
-    asm volatile("cp.async.wait_all;" ::: "memory");
-    __syncthreads();
-  }
-
   // ---- phase 1: scores of the page's rows
 #pragma unroll
   for (int it = 0; it < kIter; ++it) {
     const int row = (it * kDecWarps + warp) * KPW + sub;
     float kv[E];
-    if constexpr (STAGED) {
-      load_vec<T, E>(ks + (size_t)row * HD + e0, kv);
-    } else {
 #pragma unroll
-      for (int e = 0; e < E; ++e) kv[e] = kreg[it][e];
-    }
+    for (int e = 0; e < E; ++e) kv[e] = kreg[it][e];
 #pragma unroll
     for (int g = 0; g < GMAX; ++g) {
       float dot = 0.f;
@@ -218,16 +173,8 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, cons
   for (int it = 0; it < kIter; ++it) {
     const int row = (it * kDecWarps + warp) * KPW + sub;
     float vv[E];
-    if constexpr (STAGED) {
-      load_vec<T, E>(vs + (size_t)row * HD + e0, vv);
-      if (row < first || row >= first + n_keys) {           // never loaded, or not this token's to see
 #pragma unroll
-        for (int e = 0; e < E; ++e) vv[e] = 0.f;
-      }
-    } else {
-#pragma unroll
-      for (int e = 0; e < E; ++e) vv[e] = vreg[it][e];
-    }
+    for (int e = 0; e < E; ++e) vv[e] = vreg[it][e];
 #pragma unroll
     for (int g = 0; g < GMAX; ++g) {
       const float p = (g < ng) ? scores[g][row] : 0.f;
@@ -359,24 +306,10 @@ static int launch_split(const void* q, const void* k_cache, const void* v_cache,
   const int G = n_q / n_kv;
   const int chunks = (G + GMAX - 1) / GMAX;
   dim3 grid(n_runs, n_kv * chunks, n_seqs);
-  if (n_seqs >= kStagedFromSeqs) {
-    constexpr int P = staged_pages<T, HD>();
-    if (run_len != 64 * P) return LLMIE_ERR_BAD_ARG;
-    const size_t smem = (size_t)2 * 64 * P * HD * sizeof(T);  // the K and the V pages
-    if (smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(decode_split_kernel<T, HD, GMAX, true, P>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return (int)e;
-    }
-    launch_k(decode_split_kernel<T, HD, GMAX, true, P>, dim3(grid), dim3(kDecThreads), smem, stream, (const T*)q,
-             (const T*)k_cache, (const T*)v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen, block_table,
-             max_pages, page_size, n_q, n_kv, scale, window, run_len, n_runs, counters, (T*)out);
-  } else {
-    if (run_len != 64) return LLMIE_ERR_BAD_ARG;
-    launch_k(decode_split_kernel<T, HD, GMAX, false, 1>, dim3(grid), dim3(kDecThreads), 0, stream, (const T*)q,
-             (const T*)k_cache, (const T*)v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen, block_table,
-             max_pages, page_size, n_q, n_kv, scale, window, run_len, n_runs, counters, (T*)out);
-  }
+  if (run_len != 64) return LLMIE_ERR_BAD_ARG;
+  launch_k(decode_split_kernel<T, HD, GMAX>, dim3(grid), dim3(kDecThreads), 0, stream, (const T*)q, (const T*)k_cache,
+           (const T*)v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen, block_table, max_pages, page_size, n_q,
+           n_kv, scale, window, run_len, n_runs, counters, (T*)out);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }
@@ -428,13 +361,10 @@ extern "C" int llmie_attention_decode_supported(int hd, int dtype) {
   return (hd == 16 || hd == 32 || hd == 64 || hd == 128) ? 1 : 0;
 }
 
-// Keys per block (`run_len`) that the kernels use for this many sequences, head size and dtype.
+// Keys per block (`run_len`) that the kernels use: one cache page.
 extern "C" int llmie_attention_decode_run_len(int n_seqs, int hd, int dtype) {
-  if (n_seqs < kStagedFromSeqs) return 64;
-  const int bytes = dtype == LLMIE_F32 ? 4 : 2;
-  const int fit = 65536 / (2 * 64 * hd * bytes);
-  const int want = kStagedPages;
-  return 64 * (fit >= want ? want : (fit >= 2 && want >= 2 ? 2 : 1));
+  (void)n_seqs; (void)hd; (void)dtype;
+  return 64;
 }
 
 // q, out: [n_seqs, n_q * hd] (one token per sequence); caches [n_pages, n_kv, page_size, hd].

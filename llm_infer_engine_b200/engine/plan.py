@@ -26,8 +26,7 @@ class KernelPlan:
 
     @staticmethod
     def decode_run_length(n_seqs: int, head_dim: int, dtype) -> int:
-        """Keys per block of the split-KV kernel: one cache page for few sequences (latency), up to
-        four pages staged in shared memory for many (bandwidth); the reference uses runs of 256
+        """Keys per block of the split-KV kernel: one cache page; the reference uses runs of 256
         (src/flash_decode.py:271-272). Depends only on the step's shape, never on its data."""
         return ops.attention_decode_run_len(n_seqs, head_dim, dtype)
 

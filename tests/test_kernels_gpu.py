@@ -483,7 +483,7 @@ def test_norm_qkv_rope(batch, n_q, n_kv, hd, K):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("n_q,n_kv,hd", [(32, 8, 64), (6, 2, 128), (4, 4, 16)])
 def test_attention_decode_many_sequences(dtype, n_q, n_kv, hd):
-    """From 32 sequences on the kernel stages several pages per block in shared memory."""
+    """Many sequences of unequal lengths in one launch, merged in the same launch or by the second kernel."""
     o = ops()
     g = torch.Generator().manual_seed(3 + hd)
     lens = [int(x) for x in torch.randint(1, 700, (40,), generator=g)]
