@@ -7,41 +7,60 @@
 // same chain as ~17 launches per layer (src/model.py:39-127), or one CUDA graph of them for
 // batch 1 (src/cuda_graph.py).
 //
-// Measured on B200 at the Llama 3.2 1B shape, batch 8, 512 cached tokens: 1.27 ms per step, against
-// 0.93 ms for the same step as a CUDA graph of the stand-alone kernels. Per layer (us, block 0):
-// QKV 8.6, attention 7.4 (+6.5 waiting for the slowest block), output projection 5.0, gate/up 19.6,
-// down 15.5, barriers 1.7-3.4 each. With one block of 8 warps per SM a phase streams its weights at
-// about 30 GB/s per SM, staging of the activations (two to five microseconds) is not overlapped with
-// it, and 5 barriers a layer cost what the launch gaps did. The engine therefore uses this kernel
-// only when LLMIE_STACKED_DECODE=1 is set; it is kept, tested, as the base for a version that
-// overlaps phases.
+// Weights never depend on data, so their stream is decoupled from the phases: four producer warps
+// per block request every 16-row tile segment of every phase, in order, into a ring of
+// shared-memory slots with bulk asynchronous copies (cp.async.bulk, completion counted by an
+// mbarrier per slot), as far ahead as the ring has room - through barriers, staging and attention.
+// Eight consumer warps stage the activations of a phase in shared memory, multiply slot by slot
+// with mma.sync (16-byte fragment reads from the slot), and release slots through a second
+// mbarrier. Every wait (slot barriers, grid barriers) is bounded and ends the launch with a status.
 //
-// The math of every phase is that of the stand-alone kernels, whose code it follows:
-//   gemm_fused_decode.cu  h * w staged as bfloat16 rows in shared memory, weights streamed
-//                         straight into mma.sync fragments, rstd applied to the sums
+// Measured on B200 at the Llama 3.2 1B shape, batch 8, 512 cached tokens: 1.21 ms per step, against
+// 0.77 ms for the same step as a CUDA graph of the stand-alone kernels. Per layer (us, block 0):
+// QKV 8.5, attention 8.9 (+6.7 waiting for the slowest block), output projection 5.2, gate/up 16.2,
+// down 15.7, other barriers about 2 each. The ring is full most of the time (the producers wait
+// 75 % of the launch): the consumer warps are the limit. They spend per layer about 12 us staging
+// activations, 11 us in the products, 10 us in reductions and epilogues, 16 us in attention and
+// 10 us at barriers, and only the ring's 128 KB per SM (3 us of streaming) can run ahead of that;
+// a bound of about 43 us a layer follows, no better than the stand-alone kernels. The engine
+// therefore uses this kernel only when LLMIE_STACKED_DECODE=1 is set; it is kept, tested.
+//
+// The math of every phase is that of the stand-alone kernels:
+//   gemm_fused_decode.cu  h * w staged as bfloat16 rows in shared memory, rstd applied to the sums
 //   attention_decode.cu   one cache page per work item, all query heads of a KV head; the group
 //                         that finishes a (sequence, KV head) last merges its pages
 // Data that another block wrote earlier in the same launch (h, q, attention partials, activations,
 // this step's K/V rows) is read with loads that bypass L1, which is not coherent between SMs.
-// All phases share one copy of the product code (a loop over phase descriptors): five inlined
-// copies made the compiler keep the weight buffers in local memory.
 //
 // Limits (the caller checks them and otherwise runs the per-kernel path): bfloat16 weights and
 // cache, at most 8 sequences, pages of 64, head size 64 or 128 with the whole head rotated, at
-// most 8 query heads per KV head, no window, widths that are multiples of 32, and eight rows of
-// the widest activation must fit one SM's shared memory.
+// most 8 query heads per KV head, no window, widths that are multiples of 32, a model width of at
+// most 4096 (wider feed-forward inputs are taken in passes of 4096 columns).
 #include "common.cuh"
-#include <cooperative_groups.h>
+#include "tcgen05.cuh"
 #include <math.h>
 
 namespace llmie {
 
-constexpr int kStWarps = 8;
-constexpr int kStThreads = kStWarps * 32;
-constexpr int kStUnroll = 4;
-constexpr int kStPad = 32;                 // bfloat16 elements of padding per staged row
+using namespace tc;      // mbarriers with bounded waits
+
+constexpr int kStWarps = 8;                  // warps that compute (the "consumers")
+constexpr int kStCThreads = kStWarps * 32;
+constexpr int kStPWarps = 4;                  // warps that only request weights (the "producers"), a segment each in turn
+constexpr int kStThreads = kStCThreads + kStPWarps * 32;
+constexpr int kStPad = 32;                   // bfloat16 elements of padding per staged row
 constexpr int kStMaxGroups = 4;               // attention work groups per block, at most
 constexpr int kStatusBarrierTimeout = 4;
+constexpr int kStatusRingTimeout = 5;
+// The ring of weight slots in shared memory: a slot holds kSegChunks chunks of 32 k (1 KB) of each of a
+// tile's 16 rows; rows are 64 bytes further apart than their data, so that the 16-byte fragment reads of a
+// quarter warp (two rows) fall into different banks.
+constexpr int kSegChunks = 16;
+constexpr int kSegK = kSegChunks * 32;
+constexpr int kSlotPitch = kSegK * 2 + 64;    // bytes between rows of a slot
+constexpr int kSlotBytes = 16 * kSlotPitch;
+constexpr int kMaxSlots = 24;
+constexpr int kXsK = 4096;                    // columns of the staged activations at most; wider inputs go in passes
 
 struct StackLayer {                        // one entry of the run order
   const __nv_bfloat16* wqkv;               // [(n_q + 2 n_kv) hd, d]
@@ -75,7 +94,7 @@ struct StackParams {
   const int* block_table;
   int max_pages, n_runs;                   // n_runs * 64 covers the longest sequence of this launch
   int red_offset;                          // bytes of shared memory before the reduction scratch
-  int s_qkv, s_o, s_gate, s_down, s_head;  // warps per team in each product phase
+  int ring_offset, n_slots;                // the ring of weight slots
   int* counters;                           // [8 n_kv], zero between launches
   float* h;                                // [8, d]
   __nv_bfloat16* q;                        // [8, n_q hd]
@@ -118,23 +137,27 @@ __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long
   asm volatile("ld.acquire.gpu.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
+// named barriers: 1 = the consumer warps, 2.. = attention work groups
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kStCThreads) : "memory"); }
 __device__ __forceinline__ void group_sync(int group, int threads) {      // the threads of one attention work group
-  asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(threads) : "memory");
+  asm volatile("bar.sync %0, %1;" ::"r"(group + 2), "r"(threads) : "memory");
 }
 
-// All blocks of the launch meet here. The counter only ever grows: barrier number k of launch
-// number e completes when it reaches (e * barriers_per_launch + k + 1) * blocks, so nothing has
-// to be reset while some block may still be polling. The wait is bounded; a block that gives up
-// sets the status word and the whole launch winds down (every other block gives up at the same
-// barrier). Returns false when the launch is to be abandoned.
-__device__ __forceinline__ bool grid_barrier(unsigned long long* counter, unsigned long long target, int* status, int* s_abort) {
+// All blocks of the launch meet here (their consumer warps; the producer warp runs ahead: weights
+// depend on nothing). The counter only ever grows: barrier number k of launch number e completes
+// when it reaches (e * barriers_per_launch + k + 1) * blocks, so nothing has to be reset while
+// some block may still be polling. The wait is bounded; a block that gives up sets the status word
+// and the whole launch winds down (every other block gives up at the same barrier). Returns false
+// when the launch is to be abandoned.
+__device__ __forceinline__ bool grid_barrier(unsigned long long* counter, unsigned long long target, int* status,
+                                             volatile int* s_abort) {
   __threadfence();
-  __syncthreads();
+  consumer_sync();
   if (threadIdx.x == 0) {
     atomicAdd(counter, 1ull);
     unsigned spins = 0;
     while (ld_acquire_u64(counter) < target) {
-      if (++spins > (1u << 22)) {
+      if (++spins > (1u << 22) || *s_abort) {
         atomicExch(status, kStatusBarrierTimeout);
         *s_abort = 1;
         break;
@@ -142,7 +165,7 @@ __device__ __forceinline__ bool grid_barrier(unsigned long long* counter, unsign
     }
     __threadfence();
   }
-  __syncthreads();
+  consumer_sync();
   return *s_abort == 0;
 }
 
@@ -170,16 +193,15 @@ struct StackShared {
   float ssw[kStWarps * 8];     // sums of squares of the staged rows, per warp
   int last[kStMaxGroups];
   int abort;
+  uint64_t full[kMaxSlots];    // a slot's weights have arrived
+  uint64_t empty[kMaxSlots];   // every consumer warp is done with the slot
 };
-
-__device__ __forceinline__ void team_sync(int team, int threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(threads) : "memory");
-}
 
 // Rows of h * w (or of the embedding row * w at the first layer) as bfloat16 in shared memory, and
 // per warp the sums of squares of the rows. A thread takes eight consecutive elements of four rows
 // at a time, so those loads are in flight together while few registers are held. With FROM_EMB,
-// block b also writes row b of the float32 residual stream. Ends with a block barrier.
+// block b also writes row b of the float32 residual stream. Consumer threads only; ends with
+// their barrier.
 __device__ __forceinline__ void stage_normed(bool FROM_EMB, const StackParams& p, const float* norm_w, int K,
                                              __nv_bfloat16* xs, StackShared& sh) {
   const int xs_stride = K + kStPad;
@@ -187,7 +209,7 @@ __device__ __forceinline__ void stage_normed(bool FROM_EMB, const StackParams& p
 #pragma unroll 1
   for (int b0 = 0; b0 < 8; b0 += 4) {
     float ssq[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int k = threadIdx.x * 8; k < K; k += kStThreads * 8) {
+    for (int k = threadIdx.x * 8; k < K; k += kStCThreads * 8) {
       float wv[8];
       load8(norm_w + k, wv);
       float hv[4][8];
@@ -228,21 +250,23 @@ __device__ __forceinline__ void stage_normed(bool FROM_EMB, const StackParams& p
       if (lane == 0) sh.ssw[warp * 8 + b0 + r] = v;
     }
   }
-  __syncthreads();
+  consumer_sync();
 }
 
-// rows of a bfloat16 activation [batch, K] into shared memory. Ends with a block barrier.
-__device__ __forceinline__ void stage_plain(const StackParams& p, const __nv_bfloat16* src, int K, __nv_bfloat16* xs) {
+// Columns [k0, k0 + K) of a bfloat16 activation [batch, ld] into shared memory. Consumer threads
+// only; ends with their barrier.
+__device__ __forceinline__ void stage_plain(const StackParams& p, const __nv_bfloat16* src, int ld, int k0, int K,
+                                            __nv_bfloat16* xs) {
   const int xs_stride = K + kStPad;
   const int per_row = K >> 3;
 #pragma unroll 4
-  for (int i = threadIdx.x; i < 8 * per_row; i += kStThreads) {
+  for (int i = threadIdx.x; i < 8 * per_row; i += kStCThreads) {
     const int b = i / per_row, k = (i - b * per_row) << 3;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (b < p.batch) v = st_ldcg16(src + (size_t)b * K + k);
+    if (b < p.batch) v = st_ldcg16(src + (size_t)b * ld + k0 + k);
     *reinterpret_cast<uint4*>(xs + (size_t)b * xs_stride + k) = v;
   }
-  __syncthreads();
+  consumer_sync();
 }
 
 // Fused epilogue of one tile for the lane that holds rows (g, g + 8) and batch columns 2t, 2t + 1.
@@ -293,155 +317,206 @@ __device__ __forceinline__ void tile_epilogue(int VAR, const StackParams& p, con
   }
 }
 
-// End of a tile: the team's partial sums meet in its first warp (two buffers of shared memory in
-// turn, one team barrier per tile), whose lanes then run the epilogue; the sums start again at zero.
-__device__ __forceinline__ void finish_tile(int VAR, const StackParams& p, const StackLayer* L, float (&acc)[4], int S,
-                                            int team, int j, int warp, int lane, int g, int t, int& parity,
-                                            float4* red, int tile, int hd, int half_n, float rs0, float rs1,
-                                            void* out, int ldo, const StackShared& sh) {
-  if (S > 1) {
-    float4* mine = red + ((parity * kStWarps + warp) * 32 + lane);
-    if (j != 0) *mine = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    team_sync(team, S * 32);
-    if (j == 0) {
-      for (int o = 1; o < S; ++o) {
-        const float4 v = mine[o * 32];
-        acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
-      }
-    }
-    parity ^= 1;
-  }
-  if (j == 0) {
-    int lo, hi;
-    st_tile_rows(VAR, tile, hd, half_n, lo, hi);
-    tile_epilogue(VAR, p, L, acc, lo, hi, g, t, rs0, rs1, out, ldo, sh);
-  }
-  acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+// ------------------------------------------------------------------------------------------ schedule
+// The step as a list of passes that the producer warp and the consumer warps walk in the same
+// order. Per layer: A (norm, QKV, rotation, cache write), B (attention), C (output projection,
+// h += y; in passes of kXsK input columns), D (norm, gate / up, SwiGLU), E (down projection, h += y;
+// in passes); at the end the final norm and the head. A pass of a product streams, for every tile
+// of 16 weight rows that the block owns (tile numbers go round the blocks), the columns
+// [k0, k0 + klen) of those rows in segments of kSegK.
+struct Pass {
+  int kind;                    // 0 product, 1 attention
+  int var;
+  bool normed, from_emb, barrier_after;
+  const StackLayer* L;
+  const __nv_bfloat16* W;      // [rows, ldw]
+  int ldw, k0, klen, tiles, half_n;
+  void* out;
+  int ldo;
+  const float* norm_w;
+  float eps;
+  const __nv_bfloat16* x_src;  // for the passes that are not normed: [batch, ldw]
+};
+
+template <int HD>
+__device__ __forceinline__ int passes_per_layer(const StackParams& p, int& n_c, int& n_e) {
+  n_c = (p.n_q * HD + kXsK - 1) / kXsK;
+  n_e = (p.ff + kXsK - 1) / kXsK;
+  return 3 + n_c + n_e;
 }
 
-// One product phase: out = x W^T over tiles of 16 weight rows, x being the staged rows.
-//
-// The block's warps form teams of S warps. A team takes a tile at a time (tile numbers
-// go round the SMs first, so few tiles still spread over all of them); each of its warps owns a
-// contiguous run of K and streams its share of the 16 rows straight into mma.sync fragments.
-// A warp's work is a flat sequence of rounds (kStUnroll chunks of 32 each) that runs on across
-// tile boundaries; two register buffers take turns, so that the loads of the next round are
-// always issued before the current round is waited for, and a buffer is never copied (a copy
-// would wait for its loads). Partial sums meet in the team's first warp through shared memory
-// (two buffers in turn, one team barrier per tile), and that warp's lanes hold whole
-// (row, row + 8) x (column pair) results, which is what every epilogue needs: rotation pairs,
-// gate and up rows, or plain stores. S is chosen by the launcher so that the teams of the grid
-// cover the tiles in one pass where that is possible. The first loads are issued before x is staged.
-__device__ __forceinline__ void gemm_phase(int VAR, bool NORMED, bool FROM_EMB, const StackParams& p, const StackLayer* L, const __nv_bfloat16* W, int K,
-                                        int tiles, int half_n, void* out, int ldo, int S, const float* norm_w,
-                                        float eps, const __nv_bfloat16* x_src, __nv_bfloat16* xs, float4* red,
-                                        StackShared& sh) {
+template <int HD>
+__device__ __forceinline__ void get_pass(const StackParams& p, int idx, int per_layer, int n_c, int n_e, Pass& q) {
+  const int l = idx / per_layer;
+  q.kind = 0;
+  q.normed = false;
+  q.from_emb = false;
+  q.barrier_after = true;
+  q.half_n = 0;
+  q.k0 = 0;
+  q.norm_w = nullptr;
+  q.eps = 0.f;
+  q.x_src = nullptr;
+  if (l >= p.n_layers) {        // the head
+    q.L = p.layers + (p.n_layers - 1);
+    q.var = kGemmF32; q.normed = true; q.W = p.head; q.ldw = p.d; q.klen = p.d; q.tiles = p.vocab >> 4;
+    q.out = p.logits; q.ldo = p.vocab; q.norm_w = p.final_norm; q.eps = p.final_eps; q.barrier_after = false;
+    return;
+  }
+  const StackLayer* L = p.layers + l;
+  q.L = L;
+  int r = idx - l * per_layer;
+  if (r == 0) {
+    q.var = kGemmQkvRope; q.normed = true; q.from_emb = l == 0; q.W = L->wqkv; q.ldw = p.d; q.klen = p.d;
+    q.tiles = (p.n_q + 2 * p.n_kv) * (HD >> 4); q.out = nullptr; q.ldo = 0; q.norm_w = L->norm1; q.eps = L->eps1;
+    return;
+  }
+  if (r == 1) {
+    q.kind = 1;
+    q.tiles = 0;
+    return;
+  }
+  r -= 2;
+  if (r < n_c) {
+    const int K = p.n_q * HD;
+    q.var = kGemmAddH; q.W = L->wo; q.ldw = K; q.k0 = r * kXsK; q.klen = min(kXsK, K - q.k0); q.tiles = p.d >> 4;
+    q.out = p.h; q.ldo = p.d; q.x_src = p.attn; q.barrier_after = r == n_c - 1;
+    return;
+  }
+  r -= n_c;
+  if (r == 0) {
+    q.var = kGemmGateSwiGLU; q.normed = true; q.W = L->wgu; q.ldw = p.d; q.klen = p.d; q.tiles = p.ff >> 3;
+    q.half_n = p.ff; q.out = p.act; q.ldo = p.ff; q.norm_w = L->norm2; q.eps = L->eps2;
+    return;
+  }
+  r -= 1;
+  q.var = kGemmAddH; q.W = L->wdown; q.ldw = p.ff; q.k0 = r * kXsK; q.klen = min(kXsK, p.ff - q.k0);
+  q.tiles = p.d >> 4; q.out = p.h; q.ldo = p.d; q.x_src = p.act; q.barrier_after = r == n_e - 1;
+}
+
+__device__ __forceinline__ void bulk_g2s(unsigned dst, const void* src, unsigned bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// The producer warp: requests every segment of every tile of every pass into the ring, as far
+// ahead as the ring has room - across passes and grid barriers, since weights depend on nothing.
+// So the memory system stays busy while the consumers wait for one another, stage activations
+// or do attention. Lane r copies row r of the tile (a bulk asynchronous copy that reports its
+// bytes to the slot's barrier).
+template <int HD>
+__device__ __forceinline__ void produce(const StackParams& p, StackShared& sh, unsigned ring_addr) {
+  const int lane = threadIdx.x & 31;
+  const int pw = (threadIdx.x - kStCThreads) >> 5;     // which producer warp: it takes every kStPWarps-th segment
+  int n_c, n_e;
+  const int per_layer = passes_per_layer<HD>(p, n_c, n_e);
+  const int n_passes = p.n_layers * per_layer + 1;
+  unsigned count = 0;                                  // segments of the block so far
+  for (int idx = 0; idx < n_passes; ++idx) {
+    Pass q;
+    get_pass<HD>(p, idx, per_layer, n_c, n_e, q);
+    if (q.kind != 0) continue;
+    const int n_seg = (q.klen + kSegK - 1) / kSegK;
+    for (int tile = blockIdx.x; tile < q.tiles; tile += gridDim.x) {
+      int lo, hi;
+      st_tile_rows(q.var, tile, HD, q.half_n, lo, hi);
+      const int row = lane < 8 ? lo + lane : hi + lane - 8;
+      const __nv_bfloat16* src_row = q.W + (size_t)row * q.ldw + q.k0;
+      for (int seg = 0; seg < n_seg; ++seg, ++count) {
+        if ((int)(count % kStPWarps) != pw) continue;
+        const int slot = count % p.n_slots;
+        const unsigned use = count / p.n_slots;
+        if (!mbar_wait(&sh.empty[slot], (use & 1u) ^ 1u, &sh.abort)) {     // the slot's previous use is over
+          if (lane == 0 && !sh.abort) {
+            atomicExch(p.status, kStatusRingTimeout);
+            sh.abort = 1;
+          }
+          return;
+        }
+        const int cols = min(kSegK, q.klen - seg * kSegK);
+        if (lane == 0) mbar_arrive_expect_tx(&sh.full[slot], 16u * (unsigned)cols * 2u);
+        __syncwarp();
+        if (lane < 16)
+          bulk_g2s(ring_addr + (unsigned)slot * kSlotBytes + (unsigned)lane * kSlotPitch, src_row + seg * kSegK,
+                   (unsigned)cols * 2u, &sh.full[slot]);
+      }
+    }
+  }
+}
+
+// One product pass on the consumer side: stage the activations, then for every tile of the block
+// take its segments from the ring. Warp w multiplies chunk w of a segment (16-byte fragment reads
+// from the slot, the matching activations from the staged rows), then lets the slot go. At the end
+// of a tile the eight partial sums meet in warp 0 through shared memory (two buffers in turn, one
+// consumer barrier per tile), whose lanes hold whole (row, row + 8) x (column pair) results and
+// run the epilogue while the others go on with the next tile.
+template <int HD>
+__device__ __forceinline__ bool consume_pass(const StackParams& p, const Pass& q, StackShared& sh, __nv_bfloat16* xs,
+                                             float4* red, const unsigned char* ring, unsigned& count, int& parity) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int team = warp / S, j = warp - team * S;
-  const int n_chunks = K >> 5;
-  const int per_warp = (n_chunks + S - 1) / S;
-  const int c_begin = j * per_warp, c_end = min(n_chunks, c_begin + per_warp);
-  const int hd = p.hd;
-  const int xs_stride = K + kStPad;
-  const int tile_stride = (kStWarps / S) * gridDim.x;
-  const bool has_k = c_begin < c_end;          // a warp beyond the end of K only joins the team's barriers
-  // where the next loads come from
-  // rounds of a tile are taken in a rotated order that differs from SM to SM, so that the SMs do not
-  // all ask for the same offset within their rows at the same time
-  const int n_rounds = has_k ? (c_end - c_begin + kStUnroll - 1) / kStUnroll : 1;
-  const int rot = (blockIdx.x * 5 + team * 3) % n_rounds;
-  int ltile = team * gridDim.x + blockIdx.x, lr = 0;
-  const uint4* lw_lo = nullptr;
-  const uint4* lw_hi = nullptr;
-#define LLMIE_POINT_LOADS()                                                          \
-  do {                                                                               \
-    if (ltile < tiles) {                                                             \
-      int ra_, rb_;                                                                  \
-      st_tile_rows(VAR, ltile, hd, half_n, ra_, rb_);                                \
-      lw_lo = reinterpret_cast<const uint4*>(W + (size_t)(ra_ + g) * K) + t;         \
-      lw_hi = reinterpret_cast<const uint4*>(W + (size_t)(rb_ + g) * K) + t;         \
-    }                                                                                \
-  } while (0)
-  // the loads of the next round into one of the two register buffers
-#define LLMIE_ISSUE(wa, wb)                                                          \
-  do {                                                                               \
-    if (ltile < tiles && has_k) {                                                    \
-      int rr_ = lr + rot;                                                            \
-      if (rr_ >= n_rounds) rr_ -= n_rounds;                                          \
-      const int lc0_ = c_begin + rr_ * kStUnroll;                                    \
-      _Pragma("unroll") for (int u = 0; u < kStUnroll; ++u) {                        \
-        const int c = lc0_ + u;                                                      \
-        if (c < c_end) {                                                             \
-          wa[u] = st_ldg16(lw_lo + c * 4);                                           \
-          wb[u] = st_ldg16(lw_hi + c * 4);                                           \
-        }                                                                            \
-      }                                                                              \
-      if (++lr >= n_rounds) {                                                        \
-        lr = 0;                                                                      \
-        ltile += tile_stride;                                                        \
-        LLMIE_POINT_LOADS();                                                         \
-      }                                                                              \
-    }                                                                                \
-  } while (0)
-  // one round of math from a buffer; at the end of a tile, the team's sums and the epilogue
-#define LLMIE_CONSUME(wa, wb)                                                        \
-  do {                                                                               \
-    int rr_ = cr + rot;                                                              \
-    if (rr_ >= n_rounds) rr_ -= n_rounds;                                            \
-    const int c0_ = c_begin + rr_ * kStUnroll;                                       \
-    _Pragma("unroll") for (int u = 0; u < kStUnroll; ++u) {                          \
-      const int c = c0_ + u;                                                         \
-      if (c < c_end) {                                                               \
-        const uint4 xv = x_row[c * 4];                                               \
-        st_mma(acc, wa[u].x, wb[u].x, wa[u].y, wb[u].y, xv.x, xv.y);                 \
-        st_mma(acc2, wa[u].z, wb[u].z, wa[u].w, wb[u].w, xv.z, xv.w);                \
-      }                                                                              \
-    }                                                                                \
-    if (++cr >= n_rounds) {                                                          \
-      _Pragma("unroll") for (int i = 0; i < 4; ++i) {                                \
-        acc[i] += acc2[i];                                                           \
-        acc2[i] = 0.f;                                                               \
-      }                                                                              \
-      finish_tile(VAR, p, L, acc, S, team, j, warp, lane, g, t, parity, red, tile, hd, half_n, rs0, rs1, out, ldo, \
-                  sh);                                                               \
-      cr = 0;                                                                        \
-      tile += tile_stride;                                                           \
-    }                                                                                \
-  } while (0)
-
-  LLMIE_POINT_LOADS();
-  uint4 a0[kStUnroll], b0[kStUnroll], a1[kStUnroll], b1[kStUnroll];
-  LLMIE_ISSUE(a0, b0);
-
   float rs0 = 1.f, rs1 = 1.f;        // rstd of the two batch columns this lane holds
-  if (NORMED) {
-    stage_normed(FROM_EMB, p, norm_w, K, xs, sh);
+  if (q.normed) {
+    stage_normed(q.from_emb, p, q.norm_w, q.klen, xs, sh);
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
     for (int w = 0; w < kStWarps; ++w) {
       s0 += sh.ssw[w * 8 + 2 * t];
       s1 += sh.ssw[w * 8 + 2 * t + 1];
     }
-    rs0 = rsqrtf(s0 / (float)K + eps);
-    rs1 = rsqrtf(s1 / (float)K + eps);
+    rs0 = rsqrtf(s0 / (float)q.klen + q.eps);
+    rs1 = rsqrtf(s1 / (float)q.klen + q.eps);
   } else {
-    stage_plain(p, x_src, K, xs);
+    stage_plain(p, q.x_src, q.ldw, q.k0, q.klen, xs);
   }
+  const int xs_stride = q.klen + kStPad;
   const uint4* x_row = reinterpret_cast<const uint4*>(xs + (size_t)g * xs_stride) + t;
-
-  int tile = team * gridDim.x + blockIdx.x, cr = 0, parity = 0;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};   // two chains of products, summed per tile
-  while (tile < tiles) {
-    LLMIE_ISSUE(a1, b1);
-    LLMIE_CONSUME(a0, b0);
-    if (tile >= tiles) break;
-    LLMIE_ISSUE(a0, b0);
-    LLMIE_CONSUME(a1, b1);
+  const int n_seg = (q.klen + kSegK - 1) / kSegK;
+  const int n_chunks = q.klen >> 5;
+  for (int tile = blockIdx.x; tile < q.tiles; tile += gridDim.x) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int seg = 0; seg < n_seg; ++seg, ++count) {
+      const int slot = count % p.n_slots;
+      const unsigned use = count / p.n_slots;
+      if (!mbar_wait(&sh.full[slot], use & 1u, &sh.abort)) {
+        if (lane == 0 && !sh.abort) {
+          atomicExch(p.status, kStatusRingTimeout);
+          sh.abort = 1;
+        }
+        return false;
+      }
+#pragma unroll
+      for (int i = 0; i < kSegChunks / kStWarps; ++i) {
+        const int cs = warp * (kSegChunks / kStWarps) + i;     // this warp's chunks of 32 k within the segment
+        const int c = seg * kSegChunks + cs;
+        if (c < n_chunks) {
+          const unsigned char* base = ring + (size_t)slot * kSlotBytes + cs * 64 + t * 16;
+          const uint4 wa = *reinterpret_cast<const uint4*>(base + g * kSlotPitch);
+          const uint4 wb = *reinterpret_cast<const uint4*>(base + (g + 8) * kSlotPitch);
+          const uint4 xv = x_row[c * 4];
+          st_mma(acc, wa.x, wb.x, wa.y, wb.y, xv.x, xv.y);
+          st_mma(acc, wa.z, wb.z, wa.w, wb.w, xv.z, xv.w);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh.empty[slot]);
+    }
+    float4* mine = red + ((parity * kStWarps + warp) * 32 + lane);
+    if (warp != 0) *mine = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    consumer_sync();
+    if (warp == 0) {
+#pragma unroll
+      for (int o = 1; o < kStWarps; ++o) {
+        const float4 v = mine[o * 32];
+        acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+      }
+      int lo, hi;
+      st_tile_rows(q.var, tile, HD, q.half_n, lo, hi);
+      tile_epilogue(q.var, p, q.L, acc, lo, hi, g, t, rs0, rs1, q.out, q.ldo, sh);
+    }
+    parity ^= 1;
   }
-#undef LLMIE_POINT_LOADS
-#undef LLMIE_ISSUE
-#undef LLMIE_CONSUME
+  return true;
 }
 
 // Merge of the pages of one (sequence, query head) by one warp (src/flash_decode.py:182-205):
@@ -617,11 +692,12 @@ __device__ __forceinline__ void attention_item(const StackParams& p, const Stack
 
 template <int HD>
 __global__ void __launch_bounds__(kStThreads, 1) decode_stack_kernel(const __grid_constant__ StackParams p) {
-  extern __shared__ __align__(16) unsigned char st_smem[];
+  extern __shared__ __align__(128) unsigned char st_smem[];
   __shared__ StackShared sh;
-  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(st_smem);          // [8][K + pad], K the phase's inner size
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(st_smem);          // [8][K + pad], K the pass's inner size
   float4* red = reinterpret_cast<float4*>(st_smem + p.red_offset);        // [2][warps][32 lanes]
   float* att_smem = reinterpret_cast<float*>(st_smem);                    // aliases xs during attention
+  const unsigned char* ring = st_smem + p.ring_offset;
   constexpr int GW = HD == 64 ? 2 : 4;             // warps per attention work group
   constexpr int kGroups = kStWarps / GW;
   constexpr int kAttFloats = 8 * 64 + GW * 4 * HD;
@@ -633,13 +709,31 @@ __global__ void __launch_bounds__(kStThreads, 1) decode_stack_kernel(const __gri
     sh.pos[b] = p.seq_lens[slot];
     sh.tok[b] = b < p.batch ? p.tokens[b] : 0;
   }
-  if (threadIdx.x == 0) sh.abort = 0;
+  if (threadIdx.x == 0) {
+    sh.abort = 0;
+    for (int i = 0; i < p.n_slots; ++i) {
+      mbar_init(&sh.full[i], 1);                   // the producer's expect_tx arrival; the copies report bytes
+      mbar_init(&sh.empty[i], kStWarps);           // one arrival per consumer warp
+    }
+    fence_mbar_init();
+  }
   __syncthreads();
-  const unsigned long long per_launch = (unsigned long long)p.n_layers * 5ull;
-  unsigned long long target = (*p.epoch) * per_launch * gridDim.x;
-  const int group = threadIdx.x / (GW * 32);
-  const int n_groups = gridDim.x * kGroups;
-  int n_phase = 0;
+
+  if (threadIdx.x >= kStCThreads) {
+    // ---- the producer warps
+    produce<HD>(p, sh, smem_u32(ring));
+  } else {
+    // ---- the consumer warps
+    int n_c, n_e;
+    const int per_layer = passes_per_layer<HD>(p, n_c, n_e);
+    const int n_passes = p.n_layers * per_layer + 1;
+    const unsigned long long per_launch = (unsigned long long)p.n_layers * 5ull;
+    unsigned long long target = (*p.epoch) * per_launch * gridDim.x;
+    const int group = threadIdx.x / (GW * 32);
+    const int n_groups = gridDim.x * kGroups;
+    int n_phase = 0;
+    unsigned count = 0;                            // segments taken from the ring so far
+    int parity = 0;
 #define LLMIE_STAMP()                                                                 \
   do {                                                                                 \
     if (p.phase_ns && blockIdx.x == 0 && threadIdx.x == 0) {                           \
@@ -649,86 +743,79 @@ __global__ void __launch_bounds__(kStThreads, 1) decode_stack_kernel(const __gri
     }                                                                                  \
     ++n_phase;                                                                         \
   } while (0)
-#define LLMIE_BARRIER()                                                        \
-  do {                                                                          \
-    LLMIE_STAMP();                                                              \
-    target += gridDim.x;                                                        \
-    if (!grid_barrier(p.bar_counter, target, p.status, &sh.abort)) return;      \
-    LLMIE_STAMP();                                                              \
-  } while (0)
-  LLMIE_STAMP();
-
-  // The phases of the step in order: per layer A (norm, QKV, rotation, cache write), B (attention),
-  // C (output projection, h += y), D (norm, gate / up, SwiGLU), E (down projection, h += y); at the
-  // end the final norm and the head. One copy of the product code serves all of them.
-  const int n_phases = p.n_layers * 5 + 1;
-  for (int ph = 0; ph < n_phases; ++ph) {
-    const int l = ph / 5;
-    const int kind = (ph == n_phases - 1) ? 5 : ph - l * 5;
-    const StackLayer* L = p.layers + (l < p.n_layers ? l : p.n_layers - 1);
-    if (kind == 1) {
-      // one cache page per work item; pages in the outer order, so that the pages that hold keys
-      // come first and spread over all groups
-      const int per_run = p.batch * p.n_kv;
-      const int n_items = per_run * p.n_runs;
-      for (int item = blockIdx.x * kGroups + group; item < n_items; item += n_groups) {
-        const int run = item / per_run, rest = item - run * per_run;
-        attention_item<HD, GW>(p, L, rest / p.n_kv, rest % p.n_kv, run, group, att_smem + group * kAttFloats, sh);
-      }
-    } else {
-      int var, K, tiles, half_n = 0, ldo, S;
-      bool normed = false;
-      const __nv_bfloat16* W;
-      const __nv_bfloat16* x_src = nullptr;
-      const float* norm_w = nullptr;
-      float eps = 0.f;
-      void* out;
-      if (kind == 0) {
-        var = kGemmQkvRope; normed = true; W = L->wqkv; K = p.d; tiles = (p.n_q + 2 * p.n_kv) * (HD >> 4);
-        out = nullptr; ldo = 0; S = p.s_qkv; norm_w = L->norm1; eps = L->eps1;
-      } else if (kind == 2) {
-        var = kGemmAddH; W = L->wo; K = p.n_q * HD; tiles = p.d >> 4; out = p.h; ldo = p.d; S = p.s_o; x_src = p.attn;
-      } else if (kind == 3) {
-        var = kGemmGateSwiGLU; normed = true; W = L->wgu; K = p.d; tiles = p.ff >> 3; half_n = p.ff;
-        out = p.act; ldo = p.ff; S = p.s_gate; norm_w = L->norm2; eps = L->eps2;
-      } else if (kind == 4) {
-        var = kGemmAddH; W = L->wdown; K = p.ff; tiles = p.d >> 4; out = p.h; ldo = p.d; S = p.s_down; x_src = p.act;
+    LLMIE_STAMP();
+    bool ok = true;
+    for (int idx = 0; idx < n_passes && ok; ++idx) {
+      Pass q;
+      get_pass<HD>(p, idx, per_layer, n_c, n_e, q);
+      if (q.kind == 1) {
+        // one cache page per work item; pages in the outer order, so that the pages that hold keys
+        // come first and spread over all groups
+        const int per_run = p.batch * p.n_kv;
+        const int n_items = per_run * p.n_runs;
+        for (int item = blockIdx.x * kGroups + group; item < n_items; item += n_groups) {
+          const int run = item / per_run, rest = item - run * per_run;
+          attention_item<HD, GW>(p, q.L, rest / p.n_kv, rest % p.n_kv, run, group, att_smem + group * kAttFloats, sh);
+        }
       } else {
-        var = kGemmF32; normed = true; W = p.head; K = p.d; tiles = p.vocab >> 4; out = p.logits; ldo = p.vocab;
-        S = p.s_head; norm_w = p.final_norm; eps = p.final_eps;
+        ok = consume_pass<HD>(p, q, sh, xs, red, ring, count, parity);
       }
-      gemm_phase(var, normed, ph == 0, p, L, W, K, tiles, half_n, out, ldo, S, norm_w, eps, x_src, xs, red, sh);
+      if (ok && q.barrier_after) {
+        LLMIE_STAMP();
+        target += gridDim.x;
+        ok = grid_barrier(p.bar_counter, target, p.status, &sh.abort);
+        LLMIE_STAMP();
+      }
     }
-    if (ph + 1 < n_phases) LLMIE_BARRIER();
-  }
-#undef LLMIE_BARRIER
-  LLMIE_STAMP();
+    LLMIE_STAMP();
 #undef LLMIE_STAMP
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
-    for (int b = 0; b < p.batch; ++b)
-      if (sh.slot[b] != p.scratch_slot) p.seq_lens[sh.slot[b]] = sh.pos[b] + 1;
-    *p.epoch += 1ull;
+    if (ok && blockIdx.x == 0 && threadIdx.x == 0) {
+      for (int b = 0; b < p.batch; ++b)
+        if (sh.slot[b] != p.scratch_slot) p.seq_lens[sh.slot[b]] = sh.pos[b] + 1;
+      *p.epoch += 1ull;
+    }
+  }
+  // Both roles meet before the block leaves. After a failure, copies may still be on their way into
+  // this block's shared memory: give each slot's barrier a bounded time to report them.
+  __syncthreads();
+  if (sh.abort && threadIdx.x == kStCThreads) {
+    for (int i = 0; i < p.n_slots; ++i) {
+      for (unsigned spin = 0; spin < (1u << 16); ++spin) {
+        if (mbar_test(&sh.full[i], 0) || mbar_test(&sh.full[i], 1)) break;
+        __nanosleep(64);
+      }
+    }
   }
 }
 
-// Shared memory: the staged rows (or the attention scratch of the four work groups, whichever is
-// larger), then the reduction scratch.
+// Shared memory: the staged rows (at most kXsK columns; or the attention scratch of the work groups,
+// whichever is larger), the reduction scratch, then the ring of weight slots with what is left.
 static size_t stack_staging_bytes(int d, int ff, int n_q, int hd) {
-  int kmax = d > ff ? d : ff;
-  if (n_q * hd > kmax) kmax = n_q * hd;
+  int kmax = d;
+  const int wide = ff > n_q * hd ? ff : n_q * hd;
+  const int pass = wide > kXsK ? kXsK : wide;
+  if (pass > kmax) kmax = pass;
   const size_t rows = (size_t)8 * (kmax + kStPad) * 2;
   const size_t att = (size_t)kStMaxGroups * (8 * 64 + 4 * 4 * hd) * sizeof(float);
-  return rows > att ? rows : att;
+  const size_t bytes = rows > att ? rows : att;
+  return (bytes + 127) / 128 * 128;
 }
-static size_t stack_smem_bytes(int d, int ff, int n_q, int hd) {
-  return stack_staging_bytes(d, ff, n_q, hd) + (size_t)2 * kStWarps * 32 * sizeof(float4);
+static size_t stack_red_bytes() { return (size_t)2 * kStWarps * 32 * sizeof(float4); }
+static int stack_slots(int d, int ff, int n_q, int hd) {
+  const long long left = 226LL * 1024 - (long long)stack_staging_bytes(d, ff, n_q, hd) - (long long)stack_red_bytes();
+  long long n = left / kSlotBytes;
+  if (n > kMaxSlots) n = kMaxSlots;
+  return (int)n;
 }
 
 template <int HD>
 static int launch_stack(StackParams& p, cudaStream_t stream) {
+  if (p.d > kXsK) return LLMIE_ERR_UNSUPPORTED_SIZE;
   p.red_offset = (int)stack_staging_bytes(p.d, p.ff, p.n_q, HD);
-  const size_t smem = stack_smem_bytes(p.d, p.ff, p.n_q, HD);
-  if (smem > 220 * 1024) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  p.ring_offset = p.red_offset + (int)stack_red_bytes();
+  p.n_slots = stack_slots(p.d, p.ff, p.n_q, HD);
+  if (p.n_slots < 4) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  const size_t smem = (size_t)p.ring_offset + (size_t)p.n_slots * kSlotBytes;
   cudaError_t e = cudaFuncSetAttribute(decode_stack_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem);
   if (e != cudaSuccess) return (int)e;
@@ -739,17 +826,6 @@ static int launch_stack(StackParams& p, cudaStream_t stream) {
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  // warps per team: as many as leave every tile of the phase a team of its own in one pass
-  auto team_size = [sms](int tiles) {
-    int s = kStWarps;
-    while (s > 1 && (long long)tiles * s > (long long)sms * kStWarps) s >>= 1;
-    return s;
-  };
-  p.s_qkv = team_size((p.n_q + 2 * p.n_kv) * (HD >> 4));
-  p.s_o = team_size(p.d >> 4);
-  p.s_gate = team_size(p.ff >> 3);
-  p.s_down = team_size(p.d >> 4);
-  p.s_head = team_size(p.vocab >> 4);
   // every block must be resident at once (they wait for one another): a cooperative launch of one block per SM
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(sms);
@@ -779,7 +855,7 @@ extern "C" int llmie_decode_stack_supported(int batch, int d, int ff, int n_q, i
   if (hd != 64 && hd != 128) return 0;
   if (n_q % n_kv || n_q / n_kv > 8) return 0;
   if (d % 32 || ff % 32 || (n_q * hd) % 32 || vocab % 16) return 0;
-  if (stack_smem_bytes(d, ff, n_q, hd) > 220 * 1024) return 0;
+  if (d > kXsK || stack_slots(d, ff, n_q, hd) < 4) return 0;
   return 1;
 }
 

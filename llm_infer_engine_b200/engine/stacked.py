@@ -7,7 +7,7 @@ pre-norm blocks of RMSNorm, grouped-query attention with a fully rotated head ov
 without a window, and a SwiGLU feed-forward, all in bfloat16 with the same sizes in every layer.
 Whether a model is such a stack is asked of its parts (`stack_view()`), not of its architecture
 name; a model with any other part, or a batch beyond the kernel's limit, runs part by part.
-Measured slower than the CUDA graph of stand-alone kernels so far (1.27 ms against 0.93 ms per step
+Measured slower than the CUDA graph of stand-alone kernels so far (1.21 ms against 0.77 ms per step
 at the Llama 3.2 1B shape, batch 8), so it is used only when LLMIE_STACKED_DECODE=1 is set.
 The reference captures the same step for batch 1 as a graph of its ~17 launches per layer
 (src/cuda_graph.py:23-70).

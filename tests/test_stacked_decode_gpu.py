@@ -51,10 +51,6 @@ def test_only_known_stacks_are_taken():
     assert Engine(helpers.model_folder("c"), dtype="float32", max_batch=2).stacked_decode() is None
     # head sizes 16 and 32 are not the kernel's
     assert Engine(helpers.model_folder("a"), dtype="bfloat16", max_batch=2).stacked_decode() is None
-    # nor is a feed-forward so wide that eight rows of it do not fit one SM's shared memory
-    import test_real_shapes_gpu as real
-    folder, _, _ = real.setup("8b")
-    assert Engine(folder, dtype="bfloat16", max_batch=2, max_seq_len=512, max_tokens=64 * 12).stacked_decode() is None
 
 
 @pytest.mark.parametrize("lanes", [1, 4, 8])
@@ -99,7 +95,7 @@ def test_stacked_step_over_many_pages():
     assert float((got[0] - want).abs().max()) <= max(3e-2, 0.015 * float(want.abs().max()))
 
 
-@pytest.mark.parametrize("tag", ["1b", "3b"])
+@pytest.mark.parametrize("tag", ["1b", "3b", "8b"])
 def test_stacked_step_real_shapes(tag):
     import test_real_shapes_gpu as real
     from llm_infer_engine_b200 import Engine
