@@ -65,3 +65,44 @@ def test_real_shapes(tag, dtype, tol):
         ops.check_tc_status("cuda")
     del engine
     torch.cuda.empty_cache()
+
+
+def test_long_context_1b_shape():
+    """A 2,400-token sequence at the 1B layer shape in bfloat16: the prompt in one step (tensor-core
+    attention over 19 key tiles), then 24 tokens one by one (decode attention over 38 pages, cut into
+    runs that are merged), eagerly and through the captured step, against the plain implementation at
+    the last positions."""
+    from llm_infer_engine_b200 import Engine
+    from llm_infer_engine_b200.kernels import ops
+    folder, _, _ = setup("1b")
+    cfg = SHAPES["1b"]
+    w = helpers.plain_weights(folder)
+    tokens = helpers.random_tokens(128256, 2400, seed=77)
+    tail = 24
+    hidden = plain.hidden_states(w, cfg, tokens)[-(tail + 1):]      # logits at the last tail + 1 positions only
+    want = plain.rms_norm(hidden, w["model.norm.weight"], cfg["rms_norm_eps"]) @ plain.head_weight(w, cfg).T
+    bound = 0.015 * float(want.abs().max())
+    engine = Engine(folder, dtype="bfloat16", max_batch=2, max_seq_len=4096, max_tokens=2 * 4096)
+    # eager steps
+    slot = engine.open()
+    got = [engine.step([slot], [tokens[:-tail]], "last").float().cpu()]
+    for t in tokens[-tail:]:
+        got.append(engine.step([slot], [[t]], "last").float().cpu())
+    engine.close(slot)
+    err = float((torch.cat(got) - want).abs().max())
+    assert err <= bound, ("eager", err, bound)
+    # the captured step
+    slot = engine.open()
+    engine.step([slot], [tokens[:-tail]], "last")
+    g = engine.decode_graph(1, len(tokens))
+    g.set_lanes([slot])
+    rows = []
+    for t in tokens[-tail:]:
+        g.tokens[:1].copy_(torch.tensor([t], dtype=torch.int32))
+        engine.cache.reserve(slot, engine.cache.lengths[slot] + 1)
+        rows.append(g.replay()[:1].float().cpu().clone())
+        engine.cache.note_appended(slot, engine.cache.lengths[slot] + 1, device_updated=True)
+    engine.close(slot)
+    err = float((torch.cat(rows) - want[1:]).abs().max())
+    assert err <= bound, ("graph", err, bound)
+    ops.check_tc_status("cuda")
