@@ -8,14 +8,15 @@
 // h simply reads key/value head h / (Hq / Hkv) from the cache, and a sequence may start at any
 // position (the reference's mask is only right at position 0).
 //
-// One block = 128 consecutive query tokens of one sequence and one query head, 192 threads:
+// One block = 128 consecutive query tokens of one sequence and one query head, 320 threads:
 //   warp 0      TMA producer: the Q tile once, then for every tile of 128 keys the two cache pages
 //               of K and of V ([64 keys, hd] each) into their stages
 //   warp 1      owns TMEM (score buffer(s) of 128 columns, one P.V buffer of hd); one lane issues
 //               S = Q K^T for the NEXT key tile as soon as its buffer is free, then O_j = P_j V_j
-//   warps 2..5  softmax, one query row per thread: read S from TMEM (tcgen05.ld), mask, running
-//               max and sum, write P as bfloat16 into shared memory in the tensor core's swizzled
-//               operand layout, then add the P.V tile to the output kept in registers
+//   warps 2..9  softmax, two threads per query row (each half of a key tile's columns and half of
+//               the output's): read S from TMEM (tcgen05.ld), mask, running max and sum, write P
+//               as bfloat16 into shared memory in the tensor core's swizzled operand layout, then
+//               add the P.V tile to the output kept in registers
 // V is used as an MN-major B operand (rows of the cache are keys, i.e. the K dimension of P.V),
 // so nothing is transposed. Every barrier wait is bounded (tcgen05.cuh).
 #include "tcgen05.cuh"
@@ -26,7 +27,8 @@ using namespace tc;
 
 constexpr int kQTile = 128;       // query rows per block
 constexpr int kKTile = 128;       // keys per step (two cache pages of 64)
-constexpr int kAttnThreads = 192;
+constexpr int kSoftmaxThreads = 256;   // two per query row: each takes half of a key tile's columns
+constexpr int kAttnThreads = 64 + kSoftmaxThreads;
 constexpr int kSubTileBytes = 128 * 128;   // [128 rows x 64 bf16], 16 KB
 
 template <int HD> struct AttnCfg {
@@ -53,6 +55,10 @@ struct AttnShared {
   uint64_t p_ready, pv_full;
   uint32_t tmem_base;
   int abort;
+  // the two threads of a query row tell each other their maxima (and, at the end, their sums): a
+  // value and the number of the key tile it belongs to, which the partner polls for (bounded)
+  float row_val[2][128];
+  int row_tag[2][128];
 };
 
 // 2^x by the special-function unit (about 2 units in the last place; the probabilities are then
@@ -85,10 +91,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   uint8_t* p_smem = v_smem + Cfg::kVStages * Cfg::kKvBytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int seq = blockIdx.z, head = blockIdx.y;
+  const int seq = blockIdx.z, head = blockIdx.x;
   const int q_begin = cu_q[seq], q_len = cu_q[seq + 1] - q_begin;
-  // late query tiles see the most keys: they are handed out first so that the long blocks start early
-  const int t0 = (gridDim.x - 1 - blockIdx.x) * kQTile;
+  // Late query tiles see the most keys. Blocks are handed out in the order of blockIdx.x, then y: with
+  // the head as x and the query tile (latest first) as y, every head's longest block starts first and
+  // the short ones fill the end (longest-processing-time-first), instead of one head after another.
+  const int t0 = (gridDim.y - 1 - blockIdx.y) * kQTile;
   if (t0 >= q_len) return;                         // uniform for the block: nothing was set up yet
   const int start = seq_start[seq];                // tokens the sequence held before this step
   const int hk = head / (n_q / n_kv);
@@ -109,13 +117,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sh.s_full[b], 1);
-      mbar_init(&sh.s_free[b], 128);
+      mbar_init(&sh.s_free[b], kSoftmaxThreads);
     }
-    mbar_init(&sh.p_ready, 128);
+    mbar_init(&sh.p_ready, kSoftmaxThreads);
     mbar_init(&sh.pv_full, 1);
     sh.abort = 0;
     fence_mbar_init();
   }
+  for (int i = threadIdx.x; i < 256; i += kAttnThreads) (&sh.row_tag[0][0])[i] = 0;     // no exchange has happened
   if (warp == 1) {
     tmem_alloc(&sh.tmem_base, Cfg::kTmemCols);
     tmem_relinquish();
@@ -220,30 +229,53 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax, one query row per thread
+    // ------------------------------------------------------------------ softmax, two threads per query row
+    // Warps 2..5 take the first 64 key columns of a tile (and the first half of the head dimension of
+    // the output), warps 6..9 the second; a warp reads the TMEM lanes of its quarter (warp % 4).
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;                   // row of the tile = TMEM lane
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
     const int qpos = start + t0 + r;                     // absolute position of this query
     const int lo = (window > 0 && qpos - window + 1 > 0) ? qpos - window + 1 : 0;
     const float sl2 = scale * 1.4426950408889634f;       // exp(x * scale) = exp2(x * scale * log2 e)
-    float o[HD];
+    constexpr int kCols = kKTile / 2;                    // key columns of a tile this thread handles
+    constexpr int kOut = HD / 2;                         // output columns this thread keeps
+    float o[kOut];
 #pragma unroll
-    for (int d = 0; d < HD; ++d) o[d] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    for (int d = 0; d < kOut; ++d) o[d] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;                // l_run: the sum over this thread's columns only
     bool ok = true;
+    // hands `mine` to the row's other thread and takes its value; `tag` (> 0, growing) names the exchange
+    auto exchange = [&](float mine, int tag, float& theirs) -> bool {
+      volatile float* val = &sh.row_val[0][0];
+      volatile int* tg = &sh.row_tag[0][0];
+      val[half * 128 + r] = mine;
+      __threadfence_block();
+      tg[half * 128 + r] = tag;
+      for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
+        if (tg[(half ^ 1) * 128 + r] == tag) {
+          __threadfence_block();
+          theirs = val[(half ^ 1) * 128 + r];
+          return true;
+        }
+        if (spin > 1024 && *abort) return false;
+      }
+      return false;
+    };
     for (int jt = 0; jt < n_tiles; ++jt) {
       const int b = jt % Cfg::kSBufs;
       if (!mbar_wait(&sh.s_full[b], (jt / Cfg::kSBufs) & 1, abort)) { LLMIE_FAIL(kStatusTimeoutMma); ok = false; break; }
       tc_fence_after_sync();
-      const int kbase = (tile_lo + jt) * kKTile;
-      const bool edge = (kbase + kKTile - 1 > start + t0) || (window > 0 && kbase < start + t0 + kQTile - window);
+      const int kbase = (tile_lo + jt) * kKTile + half * kCols;
+      const bool edge = ((tile_lo + jt) * kKTile + kKTile - 1 > start + t0) ||
+                        (window > 0 && (tile_lo + jt) * kKTile < start + t0 + kQTile - window);
       // pass 1: the row's maximum over the keys it may see
       float m_tile = -INFINITY;
 #pragma unroll
-      for (int c0 = 0; c0 < kKTile; c0 += 32) {
+      for (int c0 = 0; c0 < kCols; c0 += 32) {
         uint32_t v[32];
-        tmem_ld_32x32(lane_addr + b * 128 + c0, v);
+        tmem_ld_32x32(lane_addr + b * 128 + half * kCols + c0, v);
         tmem_ld_wait();
         if (edge) {
 #pragma unroll
@@ -257,6 +289,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, __uint_as_float(v[i]));
         }
       }
+      float other;
+      if (!exchange(m_tile, jt + 1, other)) { LLMIE_FAIL(kStatusTimeoutMma); ok = false; break; }
+      m_tile = fmaxf(m_tile, other);
       const float m_new = fmaxf(m_run, m_tile);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;      // a row that has seen no key yet
       const float alpha = exp2_approx((m_run - m_use) * sl2);      // 0 while m_run is -inf
@@ -264,9 +299,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // pass 2: probabilities, their sum, and P in bfloat16 into the swizzled operand tile
       float l_tile = 0.f;
 #pragma unroll
-      for (int c0 = 0; c0 < kKTile; c0 += 32) {
+      for (int c0 = 0; c0 < kCols; c0 += 32) {
         uint32_t v[32];
-        tmem_ld_32x32(lane_addr + b * 128 + c0, v);
+        tmem_ld_32x32(lane_addr + b * 128 + half * kCols + c0, v);
         tmem_ld_wait();
         float p[32];
         if (edge) {
@@ -284,7 +319,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int i = 0; i < 32; ++i) l_tile += p[i];
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {                 // four 16-byte chunks of 8 keys
-          const int chunk = (c0 >> 3) + ch;              // 0..15 within the 128 keys
+          const int chunk = ((half * kCols + c0) >> 3) + ch;       // 0..15 within the 128 keys
           uint4 w;
           w.x = pack_bf16(p[ch * 8 + 0], p[ch * 8 + 1]);
           w.y = pack_bf16(p[ch * 8 + 2], p[ch * 8 + 3]);
@@ -297,13 +332,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_arrive(&sh.s_free[b]);
       fence_proxy_async_smem();                // P is visible to the tensor core's reads
       mbar_arrive(&sh.p_ready);
-      // the P.V tile for these keys
+      // the P.V tile for these keys: this thread's half of the head dimension
       if (!mbar_wait(&sh.pv_full, jt & 1, abort)) { LLMIE_FAIL(kStatusTimeoutMma); ok = false; break; }
       tc_fence_after_sync();
 #pragma unroll
-      for (int c0 = 0; c0 < HD; c0 += 32) {
+      for (int c0 = 0; c0 < kOut; c0 += 32) {
         uint32_t v[32];
-        tmem_ld_32x32(lane_addr + Cfg::kPvCol + c0, v);
+        tmem_ld_32x32(lane_addr + Cfg::kPvCol + half * kOut + c0, v);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha, __uint_as_float(v[i]));
@@ -312,11 +347,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       m_run = m_new;
       tc_fence_before_sync();                  // ordered before the next arrival on p_ready
     }
+    // the row's sum is the two halves' sums (both were kept relative to the same running maximum)
+    if (ok) {
+      float other;
+      if (exchange(l_run, n_tiles + 1, other)) l_run += other;
+      else { LLMIE_FAIL(kStatusTimeoutMma); ok = false; }
+    }
     if (ok && r < rows_here) {
       const float inv = 1.f / l_run;
-      __nv_bfloat16* dst = out + ((size_t)(q_begin + t0 + r) * n_q + head) * HD;
+      __nv_bfloat16* dst = out + ((size_t)(q_begin + t0 + r) * n_q + head) * HD + half * kOut;
 #pragma unroll
-      for (int d = 0; d < HD; d += 8) {
+      for (int d = 0; d < kOut; d += 8) {
         float v8[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) v8[e] = o[d + e] * inv;
@@ -350,7 +391,7 @@ static int launch_prefill(const void* q, const void* k_cache, const void* v_cach
   cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg::kSmem);
   if (e != cudaSuccess) return (int)e;
-  dim3 grid((max_q_len + kQTile - 1) / kQTile, n_q, n_seqs);
+  dim3 grid(n_q, (max_q_len + kQTile - 1) / kQTile, n_seqs);
   attention_prefill_tc_kernel<HD><<<grid, kAttnThreads, Cfg::kSmem, stream>>>(
       map_q, map_k, map_v, (__nv_bfloat16*)out, cu_q, seq_slot, seq_start, block_table, max_pages, n_pages_total - 1,
       n_q, n_kv, scale, window, status);
