@@ -49,7 +49,8 @@ class Linear:
         exists. Returns False (and does nothing) otherwise."""
         if self.weight.dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
             return False
-        if x.shape[0] > ops.SKINNY_BEST_BATCH or not ops.gemm_skinny_ok(x.shape[0], self.out_features, self.in_features):
+        if x.shape[0] > ops.SKINNY_ADD_BEST_BATCH or not ops.gemm_skinny_ok(x.shape[0], self.out_features,
+                                                                             self.in_features):
             return False
         ops.gemm_skinny(x, self.weight, h, ops.SKINNY_ADD_F32)
         return True
