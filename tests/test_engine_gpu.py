@@ -81,3 +81,28 @@ def test_trace_run_program(dtype):
     got = helpers.run_plan_trace_run(helpers.model_folder(tag), dtype, steps, helpers.max_tokens_for(steps),
                                      helpers.TINY[tag]["cfg"]["vocab_size"])
     check(got, want, TOL[dtype], f"trace_run/{dtype}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_requests", [13, 40])
+def test_wide_batches_match_plain(dtype, n_requests):
+    """Batches of 13 and of 40 sequences decoded together: above 8 rows the bfloat16 step takes other
+    kernels (the library product for most projections, the add-into product up to 16 rows, other block
+    forms of the decode attention) than the batches of the other tests."""
+    from llm_infer_engine_b200 import Engine
+    tag = "c"
+    folder = helpers.model_folder(tag)
+    w, cfg = helpers.plain_weights(folder), helpers.read_config(folder)
+    g = torch.Generator().manual_seed(n_requests)
+    lens = [int(x) for x in torch.randint(2, 150, (n_requests,), generator=g)]
+    lens[0], lens[1] = 129, 64
+    requests = {f"w{i}": helpers.random_tokens(cfg["vocab_size"], n, seed=300 + i) for i, n in enumerate(lens)}
+    want = {rid: plain.logits(w, cfg, toks) for rid, toks in requests.items()}
+    steps = helpers.plan_batched(requests, batch_size=n_requests, prompt_frac=0.8)
+    engine = Engine(folder, dtype=dtype, max_batch=n_requests, max_tokens=64 * 3 * n_requests, cuda_graph=False)
+    got = helpers.run_plan_engine(engine, steps)
+    check(got, want, TOL[dtype], f"{tag}/{dtype}/wide{n_requests}")
+    if dtype == "bfloat16":
+        from llm_infer_engine_b200.kernels import ops
+        ops.check_tc_status("cuda")
+    assert engine.cache.free_slots() == engine.cache.n_slots
