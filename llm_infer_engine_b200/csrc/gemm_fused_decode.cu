@@ -46,7 +46,14 @@ __device__ __forceinline__ void fd_mma(float (&c)[4], unsigned a0, unsigned a1, 
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ uint4 fd_ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+// 16 bytes of a weight row: read-only path, not kept in L1 (every byte is used once), and L2 is asked to
+// fetch 256 bytes around a miss (the rest of the run is about to be asked for)
+__device__ __forceinline__ uint4 fd_ldg16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::256B.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
 __device__ __forceinline__ unsigned fd_pack(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<unsigned*>(&v);

@@ -34,6 +34,14 @@ __device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], unsigned a0, uns
 }
 
 __device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+// 16 bytes of a weight row: read-only path, not kept in L1 (every byte is used once), and L2 is asked to
+// fetch 256 bytes around a miss (the rest of the run is about to be asked for)
+__device__ __forceinline__ uint4 ldg16_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::256B.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
 
 // The whole matrix has to be in flight within a memory latency or two, so a block uses many
 // warps on its 16 rows: warp w takes the chunks w, w + WARPS, ...; every round it first requests
@@ -78,8 +86,8 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   for (int u = 0; u < kSkUnroll; ++u) {
     const int c = c_begin + u;
     if (c < c_end) {
-      wa[u] = ldg16(w_lo + c * 4);
-      wb[u] = ldg16(w_hi + c * 4);
+      wa[u] = ldg16_stream(w_lo + c * 4);
+      wb[u] = ldg16_stream(w_hi + c * 4);
     }
   }
   // The weights are written by no kernel, so their first loads are already on their way while
@@ -105,8 +113,8 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     for (int u = 0; u < kSkUnroll; ++u) {           // request the next round
       const int c = c0 + kSkUnroll + u;
       if (c < c_end) {
-        na[u] = ldg16(w_lo + c * 4);
-        nbuf[u] = ldg16(w_hi + c * 4);
+        na[u] = ldg16_stream(w_lo + c * 4);
+        nbuf[u] = ldg16_stream(w_hi + c * 4);
       }
       if (kAhead) {
 #pragma unroll
