@@ -321,8 +321,10 @@ static int fused_blocks_per_sm(int K) {
 
 constexpr int kFdWarps = 8;
 
-// Team size and grid: the largest teams with which every tile still gets a team of its own in one pass
-// over the warps the GPU holds at once; few tiles then make few blocks, spread over the SMs.
+// Team size and grid: the largest teams that leave a team at most about two tiles (the second tile's first
+// loads are requested while the first is finished, which hides the tile's end; measured on the gate / up
+// product of the 1B shape: 4 warps a tile and 1.7 tiles a team beat 2 warps and one tile by 1.7 % of the
+// whole step); few tiles make few blocks, spread over the SMs.
 template <int VAR>
 static int launch_fused_w(const float* h, const float* norm_w, float eps, const void* W, void* out, int batch, int K,
                           int ldo, int tiles, int half_n, const RopeStoreArgs& rope, cudaStream_t stream) {
@@ -330,7 +332,7 @@ static int launch_fused_w(const float* h, const float* norm_w, float eps, const 
   if (per_sm < 1) return LLMIE_ERR_UNSUPPORTED_SIZE;
   const long long resident_warps = 148LL * per_sm * kFdWarps;
   int S = kFdWarps;
-  while (S > 1 && (long long)tiles * S > resident_warps) S >>= 1;
+  while (S > 1 && (long long)tiles * S > 2 * resident_warps) S >>= 1;
   const int teams_per_block = kFdWarps / S;
   int blocks = (tiles + teams_per_block - 1) / teams_per_block;
   if (blocks > 148 * per_sm) blocks = 148 * per_sm;
