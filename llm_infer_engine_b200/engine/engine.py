@@ -155,15 +155,18 @@ class Engine:
         return logits
 
     # ---------------------------------------------------------------- captured one-token step
-    def decode_graph(self, n_lanes: int, kv_len: Optional[int] = None) -> "DecodeGraph":
+    def decode_graph(self, n_lanes: int, kv_len: Optional[int] = None, sampling=None) -> "DecodeGraph":
         """The captured one-token step for `n_lanes` sequences none of which holds more than `kv_len`
         tokens after the step (default: the engine's limit). Kept per (lanes, length bucket): the
-        attention grid of a captured step is sized for the bucket, not for the longest possible sequence."""
+        attention grid of a captured step is sized for the bucket, not for the longest possible sequence.
+        With `sampling` (a SamplingParams) the draw of the next tokens is part of the captured step:
+        `sampled` then holds them after a replay."""
         limit = kv_bucket_for(self.max_seq_len if kv_len is None else kv_len, self.max_seq_len)
-        g = self._graphs.get((n_lanes, limit))
+        key = (n_lanes, limit, None if sampling is None else (sampling.temperature, sampling.top_p, sampling.seed))
+        g = self._graphs.get(key)
         if g is None:
-            g = DecodeGraph(self, n_lanes, limit)
-            self._graphs[(n_lanes, limit)] = g
+            g = DecodeGraph(self, n_lanes, limit, sampling)
+            self._graphs[key] = g
         return g
 
     def stacked_decode(self):
@@ -213,9 +216,10 @@ class DecodeGraph:
     the cache's `seq_lens`; the step derives positions from them, so replaying needs no host
     writes beyond the two buffers when the set of sequences changes. `logits` is [n_lanes, vocab]."""
 
-    def __init__(self, engine: Engine, n_lanes: int, kv_limit: Optional[int] = None):
+    def __init__(self, engine: Engine, n_lanes: int, kv_limit: Optional[int] = None, sampling=None):
         self.engine = engine
         self.n = n_lanes
+        self.sampling = sampling
         self.kv_limit = engine.max_seq_len if kv_limit is None else kv_limit     # lengths this capture serves
         dev = engine.device
         cache = engine.cache
@@ -228,6 +232,11 @@ class DecodeGraph:
         self.seq_start = torch.zeros(n_lanes, **i32)
         self.seq_kvlen = torch.zeros(n_lanes, **i32)
         self.rows = torch.arange(n_lanes, **i32)
+        # with sampling in the captured step: the drawn tokens, and per lane the request's number and how
+        # many tokens it has drawn so far (they name the uniform number of each draw)
+        self.sampled = torch.zeros(n_lanes, **i32)
+        self.seq_ids = torch.zeros(n_lanes, **i32)
+        self.counters = torch.zeros(n_lanes, **i32)
         self.logits: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._lane_slots: List[int] = [cache.scratch_slot] * n_lanes
@@ -237,6 +246,13 @@ class DecodeGraph:
         self._capture()
 
     def _run(self) -> torch.Tensor:
+        logits = self._forward()
+        if self.sampling is not None:
+            s = self.sampling
+            ops.sample(logits, self.sampled, s.temperature, s.top_p, s.seed, self.seq_ids, self.counters)
+        return logits
+
+    def _forward(self) -> torch.Tensor:
         e = self.engine
         if self.stacked is not None:
             return self.stacked.run(self.tokens, self.slots, self.n, self._stacked_buffers)

@@ -155,21 +155,19 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
                 lanes = bucket_for(n)
                 longest = max(cache.lengths[s] for s in live_slots) + 1
                 if graph is None or graph.n != lanes or longest > graph.kv_limit:
-                    graph = engine.decode_graph(lanes, longest)
+                    graph = engine.decode_graph(lanes, longest, sampling)       # the draw is part of the captured step
                     changed = True
                 for s in live_slots:
                     cache.reserve(s, cache.lengths[s] + 1)
                 if changed:
                     graph.set_lanes(live_slots)
-                    seq_ids = torch.tensor([batch[i] for i in live], dtype=torch.int32, device=dev)
-                    counters = torch.tensor([len(outputs[batch[i]]) for i in live], dtype=torch.int32, device=dev)
-                    sampled = torch.empty(n, dtype=torch.int32, device=dev)
+                    graph.seq_ids[:n].copy_(torch.tensor([batch[i] for i in live], dtype=torch.int32))
+                    graph.counters[:n].copy_(torch.tensor([len(outputs[batch[i]]) for i in live], dtype=torch.int32))
+                    sampled = graph.sampled
                 graph.tokens[:n].copy_(host_tokens[:n], non_blocking=True)
-                logits = graph.replay()
+                graph.replay()
                 for s in live_slots:
                     cache.note_appended(s, cache.lengths[s] + 1, device_updated=True)
-                ops.sample(logits[:n], sampled, sampling.temperature, sampling.top_p, sampling.seed, seq_ids,
-                           counters)
             else:
                 logits = engine.step(live_slots, [[t] for t in still_tokens], "last")
                 if changed:
