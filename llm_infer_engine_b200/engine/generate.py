@@ -164,7 +164,8 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
                     graph.seq_ids[:n].copy_(torch.tensor([batch[i] for i in live], dtype=torch.int32))
                     graph.counters[:n].copy_(torch.tensor([len(outputs[batch[i]]) for i in live], dtype=torch.int32))
                     sampled = graph.sampled
-                graph.tokens[:n].copy_(host_tokens[:n], non_blocking=True)
+                    tok_dst, tok_src, out_src = graph.tokens[:n], host_tokens[:n], sampled[:n]    # views, made once
+                tok_dst.copy_(tok_src, non_blocking=True)
                 graph.replay()
                 for s in live_slots:
                     cache.note_appended(s, cache.lengths[s] + 1, device_updated=True)
@@ -175,8 +176,9 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
                     counters = torch.tensor([len(outputs[batch[i]]) for i in live], dtype=torch.int32, device=dev)
                     sampled = torch.empty(n, dtype=torch.int32, device=dev)
                 ops.sample(logits, sampled, sampling.temperature, sampling.top_p, sampling.seed, seq_ids, counters)
+                tok_src, out_src = host_tokens[:n], sampled[:n]
             # same stream: the upload above has read the pinned buffer before this download writes it
-            host_tokens[:n].copy_(sampled[:n], non_blocking=True)
+            tok_src.copy_(out_src, non_blocking=True)
             stream.synchronize()
             new = host_view[:n].tolist()
             stats.decode_steps += 1
