@@ -3,7 +3,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
 
 A "step" is one decode step of the whole batch (captured forward + sampling). The default run
-is BASELINE's 1B configuration in bfloat16 with a batch of 8, 512-token prompts and a 4096-token
+is the Llama 3.2 1B benchmark configuration in bfloat16 with a batch of 8, 512-token prompts and a 4096-token
 context limit. It prints ONE JSON line: `value` is decoded tokens per second over K timed steps
 (CUDA events, after W warm-up steps); `e2e` is the same through `generate()` with host tokens
 in and out every step; `prefill` is one 2,048-token prompt; `roofline` compares the decode
@@ -24,7 +24,7 @@ sys.path.insert(0, ROOT)
 
 METRIC = "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (Llama 3.2 1B)"
 
-# BASELINE.json configs[2]: the Llama 3.2 1B shape
+# the benchmark configuration: the Llama 3.2 1B shape
 CONFIG_1B = {
     "architectures": ["LlamaForCausalLM"], "model_type": "llama",
     "num_hidden_layers": 16, "hidden_size": 2048, "num_attention_heads": 32, "num_key_value_heads": 8,

@@ -42,7 +42,7 @@ def setup(tag):
 
 
 @pytest.mark.parametrize("tag", ["1b", "3b", "8b"])
-# float32: BASELINE's bound (1e-3 absolute). bfloat16: rounding grows with the width of the sums and the
+# float32: 1e-3 absolute, the bound this benchmark shape is quoted with. bfloat16: rounding grows with the width of the sums and the
 # size of the logits, so the bound is relative to the largest logit of the request (1.5 %).
 @pytest.mark.parametrize("dtype,tol", [("float32", 1e-3), ("bfloat16", 0.015)])
 def test_real_shapes(tag, dtype, tol):
