@@ -55,10 +55,12 @@ struct AttnShared {
   uint64_t p_ready, pv_full;
   uint32_t tmem_base;
   int abort;
-  // the two threads of a query row tell each other their maxima (and, at the end, their sums): a
-  // value and the number of the key tile it belongs to, which the partner polls for (bounded)
-  float row_val[2][128];
-  int row_tag[2][128];
+  // the two threads of a query row tell each other their maxima (and, at the end, their sums) through
+  // shared memory; the two warps that share a quarter of the rows meet at an mbarrier of their own
+  // (a bounded wait that sleeps in hardware, so a waiting warp does not take issue slots from its partner
+  // on the same scheduler). Two value buffers in turn: a thread is never more than one exchange ahead.
+  float row_val[2][2][128];
+  uint64_t pair_bar[4];
 };
 
 // 2^x by the special-function unit (about 2 units in the last place; the probabilities are then
@@ -121,10 +123,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     mbar_init(&sh.p_ready, kSoftmaxThreads);
     mbar_init(&sh.pv_full, 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&sh.pair_bar[i], 64);
     sh.abort = 0;
     fence_mbar_init();
   }
-  for (int i = threadIdx.x; i < 256; i += kAttnThreads) (&sh.row_tag[0][0])[i] = 0;     // no exchange has happened
   if (warp == 1) {
     tmem_alloc(&sh.tmem_base, Cfg::kTmemCols);
     tmem_relinquish();
@@ -246,32 +248,30 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     for (int d = 0; d < kOut; ++d) o[d] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;                // l_run: the sum over this thread's columns only
     bool ok = true;
-    // hands `mine` to the row's other thread and takes its value; `tag` (> 0, growing) names the exchange
-    auto exchange = [&](float mine, int tag, float& theirs) -> bool {
-      volatile float* val = &sh.row_val[0][0];
-      volatile int* tg = &sh.row_tag[0][0];
-      val[half * 128 + r] = mine;
-      __threadfence_block();
-      tg[half * 128 + r] = tag;
-      for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
-        if (tg[(half ^ 1) * 128 + r] == tag) {
-          __threadfence_block();
-          theirs = val[(half ^ 1) * 128 + r];
-          return true;
-        }
-        if (spin > 1024 && *abort) return false;
-      }
-      return false;
+    // hands `mine` to the row's other thread and takes its value; n counts the exchanges of this block
+    int n_exchanges = 0;
+    auto exchange = [&](float mine, float& theirs) -> bool {
+      const int buf = n_exchanges & 1;
+      sh.row_val[buf][half][r] = mine;
+      mbar_arrive(&sh.pair_bar[quarter]);                // release: the value is written before the arrival counts
+      const bool ok_ = mbar_wait(&sh.pair_bar[quarter], n_exchanges & 1, abort);
+      theirs = sh.row_val[buf][half ^ 1][r];
+      ++n_exchanges;
+      return ok_;
     };
     for (int jt = 0; jt < n_tiles; ++jt) {
       const int b = jt % Cfg::kSBufs;
-      if (!mbar_wait(&sh.s_full[b], (jt / Cfg::kSBufs) & 1, abort)) { LLMIE_FAIL(kStatusTimeoutMma); ok = false; break; }
+      // every decision to give up is taken by the whole warp: the tensor-memory reads below are warp-wide
+      // instructions, a warp must never reach them with some of its lanes gone
+      if (!__all_sync(0xffffffffu, mbar_wait(&sh.s_full[b], (jt / Cfg::kSBufs) & 1, abort))) { LLMIE_FAIL(kStatusTimeoutMma); ok = false; break; }
       tc_fence_after_sync();
       const int kbase = (tile_lo + jt) * kKTile + half * kCols;
       const bool edge = ((tile_lo + jt) * kKTile + kKTile - 1 > start + t0) ||
                         (window > 0 && (tile_lo + jt) * kKTile < start + t0 + kQTile - window);
       // pass 1: the row's maximum over the keys it may see
-      float m_tile = -INFINITY;
+      // (four running maxima and, below, four running sums: one chain of 64 dependent operations would be
+      // what a row's time consists of)
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int c0 = 0; c0 < kCols; c0 += 32) {
         uint32_t v[32];
@@ -282,22 +282,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           for (int i = 0; i < 32; ++i) {
             const int key = kbase + c0 + i;
             const float s = (key > qpos || key < lo) ? -INFINITY : __uint_as_float(v[i]);
-            m_tile = fmaxf(m_tile, s);
+            mx[i & 3] = fmaxf(mx[i & 3], s);
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, __uint_as_float(v[i]));
+          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(v[i]));
         }
       }
+      float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       float other;
-      if (!exchange(m_tile, jt + 1, other)) { LLMIE_FAIL(kStatusTimeoutMma); ok = false; break; }
+      if (!__all_sync(0xffffffffu, exchange(m_tile, other))) { LLMIE_FAIL(kStatusTimeoutMma); ok = false; break; }
       m_tile = fmaxf(m_tile, other);
       const float m_new = fmaxf(m_run, m_tile);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;      // a row that has seen no key yet
       const float alpha = exp2_approx((m_run - m_use) * sl2);      // 0 while m_run is -inf
       const float m_scaled = m_use * sl2;
       // pass 2: probabilities, their sum, and P in bfloat16 into the swizzled operand tile
-      float l_tile = 0.f;
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c0 = 0; c0 < kCols; c0 += 32) {
         uint32_t v[32];
@@ -316,7 +317,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           for (int i = 0; i < 32; ++i) p[i] = exp2_approx(fmaf(__uint_as_float(v[i]), sl2, -m_scaled));
         }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) l_tile += p[i];
+        for (int i = 0; i < 32; ++i) ls[i & 3] += p[i];
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {                 // four 16-byte chunks of 8 keys
           const int chunk = ((half * kCols + c0) >> 3) + ch;       // 0..15 within the 128 keys
@@ -333,7 +334,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       fence_proxy_async_smem();                // P is visible to the tensor core's reads
       mbar_arrive(&sh.p_ready);
       // the P.V tile for these keys: this thread's half of the head dimension
-      if (!mbar_wait(&sh.pv_full, jt & 1, abort)) { LLMIE_FAIL(kStatusTimeoutMma); ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(&sh.pv_full, jt & 1, abort))) { LLMIE_FAIL(kStatusTimeoutMma); ok = false; break; }
       tc_fence_after_sync();
 #pragma unroll
       for (int c0 = 0; c0 < kOut; c0 += 32) {
@@ -343,14 +344,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha, __uint_as_float(v[i]));
       }
-      l_run = fmaf(l_run, alpha, l_tile);
+      l_run = fmaf(l_run, alpha, (ls[0] + ls[1]) + (ls[2] + ls[3]));
       m_run = m_new;
       tc_fence_before_sync();                  // ordered before the next arrival on p_ready
     }
     // the row's sum is the two halves' sums (both were kept relative to the same running maximum)
     if (ok) {
       float other;
-      if (exchange(l_run, n_tiles + 1, other)) l_run += other;
+      if (exchange(l_run, other)) l_run += other;
       else { LLMIE_FAIL(kStatusTimeoutMma); ok = false; }
     }
     if (ok && r < rows_here) {

@@ -111,7 +111,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   } else {
     const int quarter = warp & 3;               // TMEM lanes this warp may read
-    bool ok = mbar_wait(&sh.accum_full, 0, abort);
+    // the whole warp decides together: tcgen05.ld is a warp-wide instruction
+    const bool ok = __all_sync(0xffffffffu, mbar_wait(&sh.accum_full, 0, abort));
     if (!ok && !*abort) { *abort = 1; atomicExch(status, kStatusTimeoutMma); }
     tc_fence_after_sync();
     const int row = m0 + quarter * 32 + lane;
