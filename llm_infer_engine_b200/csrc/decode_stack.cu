@@ -139,6 +139,17 @@ __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long
 }
 // named barriers: 1 = the consumer warps, 2.. = attention work groups
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kStCThreads) : "memory"); }
+// the consumers' barrier with a vote: true for everyone when any thread brings true
+__device__ __forceinline__ bool consumer_sync_any(bool mine) {
+  unsigned any;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.or.pred p, 1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(any) : "r"((unsigned)mine), "n"(kStCThreads) : "memory");
+  return any != 0;
+}
 __device__ __forceinline__ void group_sync(int group, int threads) {      // the threads of one attention work group
   asm volatile("bar.sync %0, %1;" ::"r"(group + 2), "r"(threads) : "memory");
 }
@@ -426,7 +437,8 @@ __device__ __forceinline__ void produce(const StackParams& p, StackShared& sh, u
         if ((int)(count % kStPWarps) != pw) continue;
         const int slot = count % p.n_slots;
         const unsigned use = count / p.n_slots;
-        if (!mbar_wait(&sh.empty[slot], (use & 1u) ^ 1u, &sh.abort)) {     // the slot's previous use is over
+        // (the whole warp decides together: the lanes meet again at the warp barrier below)
+        if (!__all_sync(0xffffffffu, mbar_wait(&sh.empty[slot], (use & 1u) ^ 1u, &sh.abort))) {     // the slot's previous use is over
           if (lane == 0 && !sh.abort) {
             atomicExch(p.status, kStatusRingTimeout);
             sh.abort = 1;
@@ -475,15 +487,18 @@ __device__ __forceinline__ bool consume_pass(const StackParams& p, const Pass& q
   const int n_chunks = q.klen >> 5;
   for (int tile = blockIdx.x; tile < q.tiles; tile += gridDim.x) {
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int seg = 0; seg < n_seg; ++seg, ++count) {
+    bool failed = false;             // a warp whose wait ran out skips to the tile's barrier and says so there
+    for (int seg = 0; seg < n_seg && !failed; ++seg, ++count) {
       const int slot = count % p.n_slots;
       const unsigned use = count / p.n_slots;
-      if (!mbar_wait(&sh.full[slot], use & 1u, &sh.abort)) {
+      // (the whole warp decides together: mma.sync and the warp barrier below are warp-wide)
+      if (!__all_sync(0xffffffffu, mbar_wait(&sh.full[slot], use & 1u, &sh.abort))) {
         if (lane == 0 && !sh.abort) {
           atomicExch(p.status, kStatusRingTimeout);
           sh.abort = 1;
         }
-        return false;
+        failed = true;
+        break;
       }
 #pragma unroll
       for (int i = 0; i < kSegChunks / kStWarps; ++i) {
@@ -503,7 +518,8 @@ __device__ __forceinline__ bool consume_pass(const StackParams& p, const Pass& q
     }
     float4* mine = red + ((parity * kStWarps + warp) * 32 + lane);
     if (warp != 0) *mine = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    consumer_sync();
+    // every consumer warp reaches this barrier, whatever happened to its waits: nobody is left behind at it
+    if (consumer_sync_any(failed)) return false;
     if (warp == 0) {
 #pragma unroll
       for (int o = 1; o < kStWarps; ++o) {
