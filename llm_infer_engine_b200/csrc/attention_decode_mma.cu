@@ -99,7 +99,6 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
                   const int* __restrict__ block_table, int max_pages, int n_q, int n_kv, float scale, int window,
                   int pages_per_run, int n_runs, int* __restrict__ counters, __nv_bfloat16* __restrict__ out) {
   pdl_launch_dependents();
-  pdl_wait();
   constexpr int PITCH = HD + 8;                         // elements; rows 16 bytes apart in the banks
   constexpr int KS = HD / 16;                           // k-steps of Q K^T
   constexpr int NT = HD / 8;                            // n-tiles of P V
@@ -165,11 +164,18 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
   int p = p_first + warp, h = 0;
   if (p <= p_last && !visible(p, h)) advance(p, h);
   int np = p, nh = h;                                    // the unit after (p, h)
-  if (p <= p_last) {
-    issue(p, h, 0);
-    advance(np, nh);
-    if (np <= p_last) issue(np, nh, 1);
-  }
+  if (p <= p_last) advance(np, nh);
+  // The kernel before this one wrote the queries and the newest key and value, which lie in the
+  // sequence's last page. Lengths, slots and the page table were written before that kernel was even
+  // launched, and every other page long ago: those are read, and their copies requested, while the
+  // previous kernel is still running.
+  const int p_new = (len - 1) / kMdPage;
+  const bool early0 = p <= p_last && p != p_new, early1 = early0 && np <= p_last && np != p_new;
+  if (early0) issue(p, h, 0);
+  if (early1) issue(np, nh, 1);
+  pdl_wait();
+  if (p <= p_last && !early0) issue(p, h, 0);
+  if (np <= p_last && !early1) issue(np, nh, 1);
   // the queries of this head group as A fragments: rows g and g + 8, all of head_dim
   unsigned qa[KS][4];
   {

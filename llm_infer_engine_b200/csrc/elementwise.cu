@@ -11,8 +11,11 @@ namespace llmie {
 template <typename W>
 __global__ void embedding_kernel(const int* __restrict__ tokens, const W* __restrict__ table,
                                  float* __restrict__ h, int d, int vocab) {
-  pdl_launch_dependents();
+  // The step's index arrays (positions, lengths, slots) come from the kernel before this one. Later
+  // kernels read them ahead of their own waits, so nothing after this kernel may be scheduled before
+  // those arrays are complete: the dependents are released after the wait, not at the top.
   pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   int id = tokens[t];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // the host refuses such ids; never read outside

@@ -77,9 +77,49 @@ __device__ __forceinline__ void tile_rows(int tile, int hd, int half_n, int& lo,
 }
 
 // Fused epilogue of one tile for the lane that holds rows (g, g + 8) and batch columns 2t, 2t + 1.
+// What the rotation epilogue looks up by token, fetched ahead by the lanes that will need it: the token's
+// position, the cache page it is written to, and (for the lane's first tile) its angle's cosine and sine.
+// The chain token -> sequence -> slot -> page is three dependent loads. All of it was written before the
+// previous kernel was launched, so it is fetched while that kernel is still running.
+struct RopeAhead {
+  float2 cs[2];
+  int pos[2];
+  int page[2];
+  int tile;          // the tile that cs belongs to
+};
+
 template <int VAR>
-__device__ __forceinline__ void tile_epilogue(const float (&acc)[4], int lo, int hi, int g, int t, float rs0, float rs1,
-                                              int batch, void* out, int ldo, const RopeStoreArgs& rope) {
+__device__ __forceinline__ void rope_ahead(RopeAhead& ra, int tile, int tiles, int t, int g, int batch, int half_n,
+                                           const RopeStoreArgs& rope) {
+  ra.tile = -1;
+  if (VAR != kVarQkvRope) return;
+  const int hd = rope.hd;
+  int lo = 0, hi = 0;
+  if (tile < tiles) tile_rows<VAR>(tile, hd, half_n, lo, hi);
+  const int head = lo / hd, i = lo - head * hd + g;
+#pragma unroll
+  for (int cc = 0; cc < 2; ++cc) {
+    const int b = 2 * t + cc;
+    ra.pos[cc] = 0;
+    ra.page[cc] = 0;
+    ra.cs[cc] = make_float2(1.f, 0.f);
+    if (b >= batch) continue;
+    const int pos = rope.tok_pos[b];
+    ra.pos[cc] = pos;
+    if (rope.write_kv) {
+      const int slot = rope.seq_slot[rope.tok_seq[b]];
+      ra.page[cc] = rope.block_table[(size_t)slot * rope.max_pages + pos / rope.page_size];
+    }
+    if (tile < tiles && head < rope.n_q + rope.n_kv)
+      ra.cs[cc] = rope.table[(size_t)min(pos, rope.table_len - 1) * (hd >> 1) + i];
+  }
+  if (tile < tiles) ra.tile = tile;
+}
+
+template <int VAR>
+__device__ __forceinline__ void tile_epilogue(const float (&acc)[4], int tile, int lo, int hi, int g, int t, float rs0,
+                                              float rs1, int batch, void* out, int ldo, const RopeStoreArgs& rope,
+                                              const RopeAhead& ra) {
 #pragma unroll
   for (int cc = 0; cc < 2; ++cc) {
     const int b = 2 * t + cc;
@@ -97,9 +137,9 @@ __device__ __forceinline__ void tile_epilogue(const float (&acc)[4], int lo, int
       // rows lo + g and lo + g + hd/2 of one head: elements i and i + hd/2
       const int hd = rope.hd;
       const int head = lo / hd, i = lo - head * hd + g, half = hd >> 1;
-      const int pos = rope.tok_pos[b];
+      const int pos = ra.pos[cc];
       if (head < rope.n_q + rope.n_kv) {
-        const float2 cs = rope.table[(size_t)min(pos, rope.table_len - 1) * half + i];
+        const float2 cs = tile == ra.tile ? ra.cs[cc] : rope.table[(size_t)min(pos, rope.table_len - 1) * half + i];
         const float y1 = x1 * cs.x - x2 * cs.y, y2 = x2 * cs.x + x1 * cs.y;
         x1 = y1;
         x2 = y2;
@@ -108,8 +148,7 @@ __device__ __forceinline__ void tile_epilogue(const float (&acc)[4], int lo, int
       if (head < rope.n_q) {
         dst = rope.q_out + ((size_t)b * rope.n_q + head) * hd;
       } else if (rope.write_kv) {
-        const int slot = rope.seq_slot[rope.tok_seq[b]];
-        const int page = rope.block_table[(size_t)slot * rope.max_pages + pos / rope.page_size];
+        const int page = ra.page[cc];
         const bool is_k = head < rope.n_q + rope.n_kv;
         const int hk = head - rope.n_q - (is_k ? 0 : rope.n_kv);
         dst = (is_k ? rope.k_cache : rope.v_cache) +
@@ -194,6 +233,8 @@ norm_gemm_kernel(const float* __restrict__ h, const float* __restrict__ norm_w, 
   uint4 a0[kFdUnroll], b0[kFdUnroll], a1[kFdUnroll], b1[kFdUnroll];
   LLMIE_ISSUE(a0, b0);     // weights are written by no kernel: two rounds are on their way before the
   LLMIE_ISSUE(a1, b1);     // previous kernel has finished
+  RopeAhead ra;
+  if (j == 0) rope_ahead<VAR>(ra, team * gridDim.x + blockIdx.x, tiles, t, g, batch, half_n, rope);
   pdl_wait();              // h is the previous kernels' result
 
   // ---- h * w as bfloat16 rows in shared memory, and the sum of squares of every row
@@ -276,7 +317,7 @@ norm_gemm_kernel(const float* __restrict__ h, const float* __restrict__ norm_w, 
       if (j == 0) {                                                                  \
         int lo, hi;                                                                  \
         tile_rows<VAR>(tile, hd, half_n, lo, hi);                                    \
-        tile_epilogue<VAR>(acc, lo, hi, g, t, rs0, rs1, batch, out, ldo, rope);      \
+        tile_epilogue<VAR>(acc, tile, lo, hi, g, t, rs0, rs1, batch, out, ldo, rope, ra); \
       }                                                                              \
       acc[0] = acc[1] = acc[2] = acc[3] = 0.f;                                       \
       cr = 0;                                                                        \
