@@ -12,6 +12,8 @@ captured once with all per-step inputs (tokens, slots, lengths) in device memory
 """
 from __future__ import annotations
 
+import array
+import itertools
 from typing import Dict, List, Optional, Sequence, Union
 
 import numpy as np
@@ -43,6 +45,28 @@ def _round_up(x: int, m: int) -> int:
     return (x + m - 1) // m * m
 
 
+def _flatten_tokens(tokens, lens) -> np.ndarray:
+    """All sequences' token ids as one int64 array. Lists of Python ints, numpy arrays and CPU
+    tensors are taken; anything that is not an integer is refused."""
+    parts = []
+    try:
+        if max(lens) < 128 and not isinstance(tokens[0], (np.ndarray, torch.Tensor)):
+            # many short sequences (one-token steps): one pass over all of them
+            return np.frombuffer(array.array("q", itertools.chain.from_iterable(tokens)), dtype=np.int64)
+        for seq in tokens:
+            if isinstance(seq, torch.Tensor):
+                seq = seq.detach().cpu().numpy()
+            if isinstance(seq, np.ndarray):
+                if seq.dtype.kind not in "iu":
+                    raise TypeError(f"token ids of dtype {seq.dtype}")
+                parts.append(seq.reshape(-1).astype(np.int64, copy=False))
+            else:
+                parts.append(np.frombuffer(array.array("q", seq), dtype=np.int64))
+    except (TypeError, ValueError, OverflowError) as exc:
+        raise EngineError(f"step: token ids must be integers ({exc})") from None
+    return parts[0] if len(parts) == 1 else np.concatenate(parts)
+
+
 class Engine:
     def __init__(self, model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16", device: Union[str, int] = 0,
                  max_batch: int = 8, max_seq_len: Optional[int] = None, max_tokens: Optional[int] = None,
@@ -72,6 +96,9 @@ class Engine:
         self._graphs: Dict[tuple, "DecodeGraph"] = {}
         self._stacked = None          # StackedDecode, False (the model is no such stack) or None (not asked yet)
         self.launches = 0
+        # a step's index arrays are written into pinned host memory and uploaded in one asynchronous copy
+        self._staging_tensor = torch.empty(0, dtype=torch.int32)
+        self._staging_done = torch.cuda.Event()
 
     # ---------------------------------------------------------------- sequences
     def open(self) -> int:
@@ -84,6 +111,14 @@ class Engine:
 
     def length(self, slot: int) -> int:
         return self.cache.lengths[slot]
+
+    def _staging(self, n_ints: int) -> np.ndarray:
+        """A pinned int32 buffer of at least n_ints, free to be written: the upload of the step before
+        has finished."""
+        self._staging_done.synchronize()
+        if self._staging_tensor.numel() < n_ints:
+            self._staging_tensor = torch.empty(max(4096, 2 * n_ints), dtype=torch.int32).pin_memory()
+        return self._staging_tensor.numpy()
 
     # ---------------------------------------------------------------- the step
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
@@ -99,11 +134,14 @@ class Engine:
         lens = [len(t) for t in tokens]
         if min(lens) < 1:
             raise EngineError("step: every sequence must bring at least one token")
-        if want == "last":
-            want = [[l - 1] for l in lens]
-        elif want == "all":
-            want = [list(range(l)) for l in lens]
-        if len(want) != n:
+        want_last = isinstance(want, str) and want == "last"
+        if want_last:
+            pass
+        elif isinstance(want, str) and want == "all":
+            want = [range(l) for l in lens]
+        elif isinstance(want, str):
+            raise EngineError(f"step: want must be 'last', 'all' or lists of indices, got {want!r}")
+        if not want_last and len(want) != n:
             raise EngineError("step: want must have one list per sequence")
         cache = self.cache
         starts = []
@@ -119,39 +157,55 @@ class Engine:
             cache.reserve(s, st + l)
 
         T = sum(lens)
-        flat = np.fromiter((t for seq in tokens for t in seq), dtype=np.int64, count=T)
+        flat = _flatten_tokens(tokens, lens)
         if flat.min() < 0 or flat.max() >= self.vocab_size:
             raise EngineError(f"step: token id outside the vocabulary (0..{self.vocab_size - 1})")
-        cu = np.zeros(n + 1, dtype=np.int64)
-        np.cumsum(lens, out=cu[1:])
-        rows = []
-        for i, w in enumerate(want):
-            for j in w:
-                if not 0 <= j < lens[i]:
-                    raise EngineError(f"step: want index {j} is outside sequence {i}'s {lens[i]} tokens")
-                rows.append(int(cu[i]) + j)
+        cu = [0] * (n + 1)
+        for i, l in enumerate(lens):
+            cu[i + 1] = cu[i] + l
+        if want_last:
+            rows = cu[1:]
+            rows = [r - 1 for r in rows]
+        else:
+            rows = []
+            for i, w in enumerate(want):
+                for j in w:
+                    if not 0 <= j < lens[i]:
+                        raise EngineError(f"step: want index {j} is outside sequence {i}'s {lens[i]} tokens")
+                    rows.append(cu[i] + j)
         R = len(rows)
-        tok_seq = np.repeat(np.arange(n), lens)
-        tok_pos = np.arange(T) - cu[tok_seq] + np.asarray(starts)[tok_seq]
-        kvlen = np.asarray(starts) + np.asarray(lens)
+        kvlen = [st + l for st, l in zip(starts, lens)]
         # one packed upload: [tokens | tok_pos | tok_seq | cu_q | seq_slot | seq_start | seq_kvlen | rows]
         sizes = [T, T, T, n + 1, n, n, n, R]
-        offs = np.concatenate([[0], np.cumsum([_round_up(s, 4) for s in sizes])])
-        packed = np.zeros(int(offs[-1]), dtype=np.int32)
-        for k, arr in enumerate((flat, tok_pos, tok_seq, cu, np.asarray(slots), np.asarray(starts), kvlen,
-                                 np.asarray(rows, dtype=np.int64))):
-            packed[offs[k]:offs[k] + sizes[k]] = arr
-        dev = torch.from_numpy(packed).to(self.device)
-        view = [dev[int(offs[k]):int(offs[k]) + sizes[k]] for k in range(8)]
+        offs = [0]
+        for sz in sizes:
+            offs.append(offs[-1] + _round_up(sz, 4))
+        packed = self._staging(offs[-1])
+        packed[:T] = flat
+        if n == 1:
+            packed[offs[1]:offs[1] + T] = np.arange(starts[0], starts[0] + T, dtype=np.int32)
+            packed[offs[2]:offs[2] + T] = 0
+        else:
+            tok_seq = np.repeat(np.arange(n, dtype=np.int32), lens)
+            shift = np.asarray(starts, dtype=np.int32) - np.asarray(cu[:-1], dtype=np.int32)
+            packed[offs[1]:offs[1] + T] = np.arange(T, dtype=np.int32) + shift[tok_seq]
+            packed[offs[2]:offs[2] + T] = tok_seq
+        for k, vals in ((3, cu), (4, slots), (5, starts), (6, kvlen), (7, rows)):
+            packed[offs[k]:offs[k] + sizes[k]] = vals
+        dev = torch.empty(offs[-1], dtype=torch.int32, device=self.device)
+        dev.copy_(self._staging_tensor[:offs[-1]], non_blocking=True)
+        self._staging_done.record()
+        view = [dev[offs[k]:offs[k] + sizes[k]] for k in range(8)]
+        max_kv = max(kvlen)
         ctx = StepContext(
-            n_tokens=T, n_seqs=n, decode=max(lens) == 1, max_q_len=max(lens), max_kv_len=int(kvlen.max()),
+            n_tokens=T, n_seqs=n, decode=max(lens) == 1, max_q_len=max(lens), max_kv_len=max_kv,
             tokens=view[0], tok_pos=view[1], tok_seq=view[2], cu_q=view[3], seq_slot=view[4], seq_start=view[5],
             seq_kvlen=view[6], logit_rows=view[7], dtype=self.dtype, device=self.device, kernels=self.kernels,
-            all_rows=rows == list(range(T)))
+            all_rows=R == T and rows == list(range(T)))
         logits = self.model.forward(ctx, cache)
         ops.advance_lengths(ctx.seq_slot, ctx.seq_kvlen, cache.seq_lens, n, cache.scratch_slot)
         for s, new_len in zip(slots, kvlen):
-            cache.note_appended(s, int(new_len), device_updated=True)
+            cache.note_appended(s, new_len, device_updated=True)
         return logits
 
     # ---------------------------------------------------------------- captured one-token step
