@@ -209,17 +209,23 @@ class Engine:
         return logits
 
     # ---------------------------------------------------------------- captured one-token step
-    def decode_graph(self, n_lanes: int, kv_len: Optional[int] = None, sampling=None) -> "DecodeGraph":
+    def decode_graph(self, n_lanes: int, kv_len: Optional[int] = None, sampling=None,
+                     host_io: bool = False) -> "DecodeGraph":
         """The captured one-token step for `n_lanes` sequences none of which holds more than `kv_len`
         tokens after the step (default: the engine's limit). Kept per (lanes, length bucket): the
         attention grid of a captured step is sized for the bucket, not for the longest possible sequence.
         With `sampling` (a SamplingParams) the draw of the next tokens is part of the captured step:
-        `sampled` then holds them after a replay."""
+        `sampled` then holds them after a replay. With `host_io` as well, the captured step begins with the
+        upload of `host_in` (pinned) into `tokens` and ends with the download of `sampled` into `host_out`
+        (pinned): a generation loop then needs one launch per step and no copy calls of its own."""
         limit = kv_bucket_for(self.max_seq_len if kv_len is None else kv_len, self.max_seq_len)
-        key = (n_lanes, limit, None if sampling is None else (sampling.temperature, sampling.top_p, sampling.seed))
+        if host_io and sampling is None:
+            raise EngineError("decode_graph: host_io needs the draw inside the captured step (give sampling)")
+        key = (n_lanes, limit, None if sampling is None else (sampling.temperature, sampling.top_p, sampling.seed),
+               bool(host_io))
         g = self._graphs.get(key)
         if g is None:
-            g = DecodeGraph(self, n_lanes, limit, sampling)
+            g = DecodeGraph(self, n_lanes, limit, sampling, host_io)
             self._graphs[key] = g
         return g
 
@@ -270,10 +276,12 @@ class DecodeGraph:
     the cache's `seq_lens`; the step derives positions from them, so replaying needs no host
     writes beyond the two buffers when the set of sequences changes. `logits` is [n_lanes, vocab]."""
 
-    def __init__(self, engine: Engine, n_lanes: int, kv_limit: Optional[int] = None, sampling=None):
+    def __init__(self, engine: Engine, n_lanes: int, kv_limit: Optional[int] = None, sampling=None,
+                 host_io: bool = False):
         self.engine = engine
         self.n = n_lanes
         self.sampling = sampling
+        self.host_io = bool(host_io)
         self.kv_limit = engine.max_seq_len if kv_limit is None else kv_limit     # lengths this capture serves
         dev = engine.device
         cache = engine.cache
@@ -291,6 +299,9 @@ class DecodeGraph:
         self.sampled = torch.zeros(n_lanes, **i32)
         self.seq_ids = torch.zeros(n_lanes, **i32)
         self.counters = torch.zeros(n_lanes, **i32)
+        # pinned host memory that the captured step reads its tokens from and leaves the drawn ones in
+        self.host_in = torch.zeros(n_lanes, dtype=torch.int32).pin_memory() if self.host_io else None
+        self.host_out = torch.zeros(n_lanes, dtype=torch.int32).pin_memory() if self.host_io else None
         self.logits: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._lane_slots: List[int] = [cache.scratch_slot] * n_lanes
@@ -300,10 +311,14 @@ class DecodeGraph:
         self._capture()
 
     def _run(self) -> torch.Tensor:
+        if self.host_io:
+            self.tokens.copy_(self.host_in, non_blocking=True)
         logits = self._forward()
         if self.sampling is not None:
             s = self.sampling
             ops.sample(logits, self.sampled, s.temperature, s.top_p, s.seed, self.seq_ids, self.counters)
+        if self.host_io:
+            self.host_out.copy_(self.sampled, non_blocking=True)
         return logits
 
     def _forward(self) -> torch.Tensor:

@@ -148,14 +148,16 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
             # --- one token each
             n = len(live)
             live_slots = [slots[i] for i in live]
-            # the tokens go back in from pinned host memory, as the reference writes each sampled id
+            # the tokens go back in from (pinned) host memory, as the reference writes each sampled id
             # into its device input buffer (main.py:282): the host may have the last word on them
-            host_view[:n] = still_tokens
             if engine.use_cuda_graph:
                 lanes = bucket_for(n)
                 longest = max(cache.lengths[s] for s in live_slots) + 1
                 if graph is None or graph.n != lanes or longest > graph.kv_limit:
-                    graph = engine.decode_graph(lanes, longest, sampling)       # the draw is part of the captured step
+                    # the upload of the tokens, the draw and the download of the drawn tokens are part of
+                    # the captured step: one launch a step
+                    graph = engine.decode_graph(lanes, longest, sampling, host_io=True)
+                    in_view, out_view = graph.host_in.numpy(), graph.host_out.numpy()
                     changed = True
                 for s in live_slots:
                     cache.reserve(s, cache.lengths[s] + 1)
@@ -163,12 +165,12 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
                     graph.set_lanes(live_slots)
                     graph.seq_ids[:n].copy_(torch.tensor([batch[i] for i in live], dtype=torch.int32))
                     graph.counters[:n].copy_(torch.tensor([len(outputs[batch[i]]) for i in live], dtype=torch.int32))
-                    sampled = graph.sampled
-                    tok_dst, tok_src, out_src = graph.tokens[:n], host_tokens[:n], sampled[:n]    # views, made once
-                tok_dst.copy_(tok_src, non_blocking=True)
+                in_view[:n] = still_tokens
                 graph.replay()
                 for s in live_slots:
                     cache.note_appended(s, cache.lengths[s] + 1, device_updated=True)
+                stream.synchronize()
+                new = out_view[:n].tolist()
             else:
                 logits = engine.step(live_slots, [[t] for t in still_tokens], "last")
                 if changed:
@@ -176,11 +178,10 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
                     counters = torch.tensor([len(outputs[batch[i]]) for i in live], dtype=torch.int32, device=dev)
                     sampled = torch.empty(n, dtype=torch.int32, device=dev)
                 ops.sample(logits, sampled, sampling.temperature, sampling.top_p, sampling.seed, seq_ids, counters)
-                tok_src, out_src = host_tokens[:n], sampled[:n]
-            # same stream: the upload above has read the pinned buffer before this download writes it
-            tok_src.copy_(out_src, non_blocking=True)
-            stream.synchronize()
-            new = host_view[:n].tolist()
+                # same stream: the upload in step() has read its pinned buffer before this download writes one
+                host_tokens[:n].copy_(sampled[:n], non_blocking=True)
+                stream.synchronize()
+                new = host_view[:n].tolist()
             stats.decode_steps += 1
             stats.decode_tokens += n
         d1.record()
