@@ -521,6 +521,8 @@ def test_attention_decode_mma_page_choice():
     assert o.attention_decode_mma_pages(64, 32, 8, 1024) == 16
     assert o.attention_decode_mma_pages(8, 32, 8, 4096) == 32          # two runs, 128 blocks
     assert o.attention_decode_mma_pages(256, 32, 8, 4096) == 64        # enough blocks already
+    assert o.attention_decode_mma_pages(1, 32, 8, 3500) == 7           # one long sequence: cut on, 64 blocks
+    assert o.attention_decode_mma_pages(4, 32, 8, 3500) == 14          # 128 blocks; eight runs would be 256
     for n, kv in ((1, 64), (1, 131072), (48, 640), (64, 8192), (256, 131072)):
         pp = o.attention_decode_mma_pages(n, 32, 8, kv)
         assert 1 <= pp <= (kv + 63) // 64
