@@ -220,16 +220,18 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, cons
   __syncthreads();
   if (!is_last) return;
   __threadfence();
+  // The other blocks' partial results are read from L2 (__ldcg), never through this SM's L1: an earlier
+  // block on this SM may have read a neighbouring entry of the same 128-byte line before this one was written.
   // weights of the runs, 64 runs at a time (they sit where the scores were), then every thread
   // owns output elements and walks the runs with independent loads
   __shared__ float head_max[GMAX], head_inv[GMAX];
   for (int g = warp; g < ng; g += kDecWarps) {
     const size_t base = ((size_t)seq * n_q + (size_t)hk * G + g0 + g) * n_runs;
     float M = -INFINITY;
-    for (int r = r0 + lane; r <= r1; r += 32) M = fmaxf(M, part_m[base + r]);
+    for (int r = r0 + lane; r <= r1; r += 32) M = fmaxf(M, __ldcg(part_m + base + r));
     M = warp_max(M);
     float denom = 0.f;
-    for (int r = r0 + lane; r <= r1; r += 32) denom += expf(part_m[base + r] - M) * part_l[base + r];
+    for (int r = r0 + lane; r <= r1; r += 32) denom += expf(__ldcg(part_m + base + r) - M) * __ldcg(part_l + base + r);
     denom = warp_sum(denom);
     if (lane == 0) {
       head_max[g] = M;
@@ -246,7 +248,7 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, cons
     for (int i = threadIdx.x; i < ng * n_here; i += kDecThreads) {
       const int g = i / n_here, r = i - g * n_here;
       const size_t base = ((size_t)seq * n_q + (size_t)hk * G + g0 + g) * n_runs;
-      scores[g][r] = expf(part_m[base + c0 + r] - head_max[g]);
+      scores[g][r] = expf(__ldcg(part_m + base + c0 + r) - head_max[g]);
     }
     __syncthreads();
 #pragma unroll
@@ -257,7 +259,7 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, cons
         const float* pa = part_acc + (((size_t)seq * n_q + (size_t)hk * G + g0 + g) * n_runs + c0) * HD + d;
         float a = num[i];
 #pragma unroll 8
-        for (int r = 0; r < n_here; ++r) a = fmaf(scores[g][r], pa[(size_t)r * HD], a);
+        for (int r = 0; r < n_here; ++r) a = fmaf(scores[g][r], __ldcg(pa + (size_t)r * HD), a);
         num[i] = a;
       }
     }

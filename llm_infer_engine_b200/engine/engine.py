@@ -13,6 +13,7 @@ captured once with all per-step inputs (tokens, slots, lengths) in device memory
 from __future__ import annotations
 
 import array
+import gc
 import itertools
 from typing import Dict, List, Optional, Sequence, Union
 
@@ -346,8 +347,18 @@ class DecodeGraph:
         torch.cuda.synchronize(self.engine.device)
         self.graph = torch.cuda.CUDAGraph()
         before = ops.LAUNCHES
-        with torch.cuda.graph(self.graph):
-            self.logits = self._run()
+        # No garbage collection inside the capture: collecting an engine that is no longer used frees its
+        # pinned memory, for which the allocator records an event on the default stream, and work on the
+        # default stream while another stream is capturing invalidates the capture.
+        gc.collect()
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph):
+                self.logits = self._run()
+        finally:
+            if gc_was_on:
+                gc.enable()
         self.launches_per_replay = ops.LAUNCHES - before      # this library's kernels inside one replay
 
     def set_lanes(self, slots: Sequence[int]) -> None:

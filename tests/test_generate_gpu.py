@@ -113,7 +113,9 @@ def test_captured_step_equals_eager_step(dtype):
     for s in slots:
         graphed.cache.reserve(s, graphed.cache.lengths[s] + 1)
     got = g.replay()[:3].cpu()
-    assert torch.equal(got, want)
+    diff = (got - want).abs()
+    assert torch.equal(got, want), (diff.max(dim=1).values.tolist(), (diff > 0).sum(dim=1).tolist(),
+                                    bool(torch.isnan(got).any()), bool(torch.isnan(want).any()))
     assert graphed.cache.seq_lens.cpu().tolist()[:3] == [4, 65, 30]
     assert int(graphed.cache.seq_lens[graphed.cache.scratch_slot]) == 0
 

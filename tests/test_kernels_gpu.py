@@ -480,6 +480,34 @@ def test_norm_qkv_rope(batch, n_q, n_kv, hd, K):
     assert torch.equal((k_dev != pg.dev()[0]).any(-1), (k2 != pg.dev()[0]).any(-1))
 
 
+def test_attention_decode_merge_reads_fresh_partials():
+    """The block that merges the runs of a sequence must see the other blocks' partial results of THIS
+    launch. Few query heads make the partial maxima of many sequences share a 128-byte line, the scratch
+    area is reused launch after launch with other inputs, and many merging blocks share an SM: a merge
+    that read a line through a stale L1 copy would be far from the merge by a second kernel."""
+    o = ops()
+    dtype, n_q, n_kv, hd = torch.bfloat16, 3, 1, 32
+    g = torch.Generator().manual_seed(5)
+    lens = [int(x) for x in torch.randint(65, 256, (300,), generator=g)]
+    pg = Paged(lens, n_kv, hd, dtype, seed=9)
+    pg.fill()
+    k_dev, v_dev, bt = pg.dev()
+    slots = torch.tensor(pg.slots, dtype=torch.int32, device=DEV)
+    kvlen = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    n_runs = 4
+    counters = torch.zeros(o.decode_counter_ints(len(lens), n_q, n_kv), dtype=torch.int32, device=DEV)
+    scratch = torch.zeros(o.decode_scratch_floats(len(lens), n_q, hd, n_runs), dtype=torch.float32, device=DEV)
+    for it in range(12):
+        q = (torch.randn(len(lens), n_q * hd, generator=g) * (1 + it)).to(dtype).to(DEV)
+        fused = torch.empty_like(q)
+        o.attention_decode(q, k_dev, v_dev, fused, slots, kvlen, bt, 64, n_q, n_kv, hd, hd ** -0.5, 0, 64, n_runs,
+                           scratch=scratch, counters=counters)
+        two = torch.empty_like(q)
+        o.attention_decode(q, k_dev, v_dev, two, slots, kvlen, bt, 64, n_q, n_kv, hd, hd ** -0.5, 0, 64, n_runs)
+        assert torch.allclose(fused.float(), two.float(), atol=3e-2, rtol=3e-2), (it, float((fused.float() - two.float()).abs().max()))
+    assert int(counters.abs().sum()) == 0
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("n_q,n_kv,hd", [(32, 8, 64), (6, 2, 128), (4, 4, 16)])
 def test_attention_decode_many_sequences(dtype, n_q, n_kv, hd):
