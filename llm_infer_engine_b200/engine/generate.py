@@ -125,7 +125,28 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
         graph = None
         host_view = host_tokens.numpy()              # the same pinned memory, without tensor overheads
         stream = torch.cuda.current_stream()
+        slack = 0          # steps for which no live sequence can end by a length limit (0 = look at each)
         while True:
+            # --- the common step: nobody can end by length, nobody drew a stop token, the captured step
+            # still serves. The next step is launched first; the bookkeeping runs while it does.
+            if slack > 0 and graph is not None and longest < graph.kv_limit and stop.isdisjoint(new):
+                in_view[:n] = new
+                for s in live_slots:
+                    cache.reserve(s, cache.lengths[s] + 1)
+                graph.replay()
+                if on_tokens is not None:
+                    on_tokens([batch[i] for i in live], list(new))
+                for i, tok in zip(live, new):
+                    outputs[batch[i]].append(tok)
+                for s in live_slots:
+                    cache.note_appended(s, cache.lengths[s] + 1, device_updated=True)
+                slack -= 1
+                longest += 1
+                stream.synchronize()
+                new = out_view[:n].tolist()
+                stats.decode_steps += 1
+                stats.decode_tokens += n
+                continue
             # --- decide on the host
             if on_tokens is not None:
                 on_tokens([batch[i] for i in live], list(new))
@@ -167,6 +188,9 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
                     graph.counters[:n].copy_(torch.tensor([len(outputs[batch[i]]) for i in live], dtype=torch.int32))
                 in_view[:n] = still_tokens
                 graph.replay()
+                # after this step every live sequence has one token more drawn and one more cached
+                slack = min(min(max_new_tokens - len(outputs[batch[i]]), engine.max_seq_len - cache.lengths[slots[i]])
+                            for i in live) - 1
                 for s in live_slots:
                     cache.note_appended(s, cache.lengths[s] + 1, device_updated=True)
                 stream.synchronize()
