@@ -120,6 +120,37 @@ def test_captured_step_equals_eager_step(dtype):
     assert int(graphed.cache.seq_lens[graphed.cache.scratch_slot]) == 0
 
 
+def test_capture_survives_a_collectable_engine():
+    """An engine that only the garbage collector can free (a reference cycle) holds pinned memory; if
+    it were collected in the middle of a graph capture, the capture would be invalidated. The capture
+    collects first and keeps the collector off meanwhile, however eager the collector is set."""
+    import gc
+    from llm_infer_engine_b200 import Engine
+    folder = helpers.model_folder("c")
+    cfg = helpers.read_config(folder)
+    prompt = helpers.random_tokens(cfg["vocab_size"], 40, seed=77)
+    old = Engine(folder, dtype="bfloat16", max_batch=2, cuda_graph=False)
+    s = old.open()
+    old.step([s], [prompt])                       # its pinned upload buffer has been used by a copy
+    old.close(s)
+    old.keeps_itself_alive = old
+    del old
+    thresholds = gc.get_threshold()
+    gc.set_threshold(1)                           # collect at every opportunity
+    try:
+        engine = Engine(folder, dtype="bfloat16", max_batch=2, cuda_graph=True)
+        slot = engine.open()
+        engine.step([slot], [prompt])
+        g = engine.decode_graph(2)
+        g.set_lanes([slot])
+        g.tokens[:1].copy_(torch.tensor([5], dtype=torch.int32))
+        engine.cache.reserve(slot, engine.cache.lengths[slot] + 1)
+        logits = g.replay()[:1].cpu()
+    finally:
+        gc.set_threshold(*thresholds)
+    assert torch.isfinite(logits).all()
+
+
 def test_seeded_sampling_does_not_depend_on_batching():
     from llm_infer_engine_b200 import Engine, SamplingParams, generate, uniform_for
     folder = helpers.model_folder("b", std=0.12)                 # livelier logits than N(0, 0.03) gives
