@@ -245,15 +245,8 @@ def run_ours(args):
         "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), "
         "uniform-random token ids", "impl": "ours",
-        "config": {
-            "model": "Llama-3.2-1B shape", "global_batch": args.batch, "seq_len": CONTEXT, "parallelism": "single GPU",
-            "layers": n_layers, "layers_full": full_layers, "hidden_size": CONFIG_1B["hidden_size"],
-            "heads": CONFIG_1B["num_attention_heads"], "kv_heads": CONFIG_1B["num_key_value_heads"],
-            "head_dim": CONFIG_1B["head_dim"], "intermediate_size": CONFIG_1B["intermediate_size"],
-            "vocab_size": CONFIG_1B["vocab_size"], "prompt_len": PROMPT_LEN, "new_tokens": args.steps,
-            "tied_head": True, "cuda_graph": True, "sampling": "greedy",
-            "l2": "weights 2.5 GB per step >> 126 MB L2, no flush needed", "peaks": pk["source"],
-        },
+        "config": workload_config(args, n_layers, pk),
+        "impl_notes": {"path": "generate() / captured one-token steps", "head": "tied to the embedding"},
         "gpu_launches": int(launches),
     }
     if args.batch in results:
@@ -278,11 +271,79 @@ def run_ours(args):
     return 0
 
 
+def workload_config(args, n_layers: int, pk: dict) -> dict:
+    """The `config` of the JSON line: the workload and every layer size, the same for both arms."""
+    c = CONFIG_1B
+    return {
+        "model": "Llama-3.2-1B shape", "global_batch": args.batch, "seq_len": CONTEXT, "parallelism": "single GPU",
+        "layers": n_layers, "layers_full": c["num_hidden_layers"], "hidden_size": c["hidden_size"],
+        "heads": c["num_attention_heads"], "kv_heads": c["num_key_value_heads"], "head_dim": c["head_dim"],
+        "intermediate_size": c["intermediate_size"], "vocab_size": c["vocab_size"], "prompt_len": PROMPT_LEN,
+        "new_tokens": args.steps, "prefill_tokens": PREFILL_TOKENS, "sampling": "greedy",
+        "l2": "weights 2.5 GB per step >> 126 MB L2, no flush needed", "peaks": pk["source"],
+    }
+
+
 def run_reference(args):
-    # `python -m pip install --no-index --no-build-isolation --find-links /opt/wheelhouse --target baseline/_ref
-    # <reference>` fails: the reference has neither setup.py nor pyproject.toml, so nothing can be installed.
-    print(json.dumps({"impl": "reference", "unavailable": "pip cannot install the reference: the directory has "
-                      "neither setup.py nor pyproject.toml (not installable)"}))
+    """The unmodified reference on the same workload (baseline/reference_arm.py): the same JSON keys, with
+    `"impl": "reference"`. Whatever stops it is reported with its own text in an `unavailable` line."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device")
+        import reference_arm
+        n_layers = args.layers or CONFIG_1B["num_hidden_layers"]
+        arm = reference_arm.ReferenceArm(CONFIG_1B, n_layers, CONTEXT)
+        pk = peaks()
+        arm.compile_pass(args.batch, PROMPT_LEN)
+        sampler = ClockSampler(0)
+        sampler.start()
+        sec, mean_ctx = arm.decode(args.batch, PROMPT_LEN, args.steps, args.warmup, seed=10 + args.batch,
+                                   host_io=False)
+        points = {}
+        prefill_s = e2e_sec = None
+        if args.only == "all":
+            e2e_sec, _ = arm.decode(args.batch, PROMPT_LEN, args.steps, args.warmup, seed=10 + args.batch,
+                                    host_io=True)
+            for b in (1, 64):
+                arm.compile_pass(b, PROMPT_LEN)
+                s_b, _ = arm.decode(b, PROMPT_LEN, args.steps, args.warmup, seed=10 + b, host_io=True)
+                points[f"decode_b{b}"] = round(b * args.steps / s_b, 1)
+            s_g, _ = arm.decode(1, PROMPT_LEN, args.steps, args.warmup, seed=11, host_io=True, graph=True)
+            points["decode_b1_graph"] = round(args.steps / s_g, 1)
+            prefill_s = arm.prefill(PREFILL_TOKENS, warmup=3, reps=5, seed=99)
+        sampler.stop()
+    except Exception as exc:                                   # noqa: BLE001 - the reason goes into the line
+        text = " ".join(f"{type(exc).__name__}: {exc}".split())[:400]
+        print(json.dumps({"impl": "reference", "unavailable": text}))
+        return 0
+    step_bytes = arm.weight_bytes_per_step() + arm.kv_bytes_per_token() * mean_ctx * args.batch
+    achieved = step_bytes / (sec / args.steps) / 1e9
+    out = {
+        "metric": METRIC, "value": round(args.batch * args.steps / sec, 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec / args.steps * 1e3, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: the reference's own random initialisation, uniform-random token ids",
+        "impl": "reference", "config": workload_config(args, n_layers, pk),
+        "impl_notes": {"path": "Llama3.forward + KVCache + sample, eager (its graph runner serves batch 1 only: "
+                               "points.decode_b1_graph)", "head": "separate output matrix (its random mode)"},
+        "gpu_launches": 0,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+    }
+    if e2e_sec is not None:
+        out["e2e"] = {"value": round(args.batch * args.steps / e2e_sec, 1), "unit": "tokens/s",
+                      "h2d_bytes_per_step": 8 * args.batch, "d2h_bytes_per_step": 8 * args.batch}
+    if prefill_s is not None:
+        flops = prefill_flops(CONFIG_1B, n_layers, PREFILL_TOKENS)
+        out["prefill"] = {"value": round(PREFILL_TOKENS / prefill_s, 1), "tokens": PREFILL_TOKENS,
+                          "ms": round(prefill_s * 1e3, 3),
+                          "frac": round(flops / prefill_s / (pk["bf16_tflops"] * 1e12), 4)}
+    if points:
+        out["points"] = points
+    out["clocks"] = sampler.summary()
+    print(json.dumps(out))
     return 0
 
 

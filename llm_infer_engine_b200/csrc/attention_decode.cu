@@ -73,6 +73,14 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, cons
   const int ng = min(GMAX, G - g0);
 
   const int len = seq_kvlen[seq];
+  if (len <= 0) {
+    // a sequence without keys: its output rows are zeros (written here only in the one-launch form;
+    // the separate merge kernel does the same)
+    if (counters != nullptr && run == 0)
+      for (int i = threadIdx.x; i < ng * HD; i += kDecThreads)
+        out[((size_t)seq * n_q + (size_t)hk * G + g0) * HD + i] = from_f32<T>(0.f);
+    return;
+  }
   const int lo = first_visible(len, window);
   const int begin = max(run * kRun, lo);
   const int end = min(len, (run + 1) * kRun);
@@ -285,8 +293,12 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_m, const floa
   pdl_wait();
   const int seq = blockIdx.y, h = blockIdx.x;
   const int len = seq_kvlen[seq];
+  if (len <= 0) {        // no keys: no block wrote partial results for this sequence; its output is zeros
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) out[((size_t)seq * n_q + h) * hd + d] = from_f32<T>(0.f);
+    return;
+  }
   const int lo = first_visible(len, window);
-  const int r0 = lo / run_len, r1 = (len - 1) / run_len;      // len >= 1 always
+  const int r0 = lo / run_len, r1 = (len - 1) / run_len;
   const size_t base = ((size_t)seq * n_q + h) * n_runs;
   float M = -INFINITY;
   for (int r = r0; r <= r1; ++r) M = fmaxf(M, part_m[base + r]);
@@ -308,7 +320,7 @@ static int launch_split(const void* q, const void* k_cache, const void* v_cache,
   const int G = n_q / n_kv;
   const int chunks = (G + GMAX - 1) / GMAX;
   dim3 grid(n_runs, n_kv * chunks, n_seqs);
-  if (run_len != 64) return LLMIE_ERR_BAD_ARG;
+  if (run_len != 64) return LLMIE_ERR_UNSUPPORTED_SIZE;
   launch_k(decode_split_kernel<T, HD, GMAX>, dim3(grid), dim3(kDecThreads), 0, stream, (const T*)q, (const T*)k_cache,
            (const T*)v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen, block_table, max_pages, page_size, n_q,
            n_kv, scale, window, run_len, n_runs, counters, (T*)out);
@@ -379,7 +391,7 @@ extern "C" int llmie_attention_decode(const void* q, const void* k_cache, const 
                                       int n_runs, int dtype, cudaStream_t stream) {
   if (n_seqs < 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv || page_size <= 0 || max_pages <= 0) return LLMIE_ERR_BAD_ARG;
   if (n_runs <= 0) return LLMIE_ERR_BAD_ARG;
-  if (page_size != 64 || run_len % 64) return LLMIE_ERR_UNSUPPORTED_SIZE;     // a run is whole cache pages
+  if (page_size != 64 || run_len != 64) return LLMIE_ERR_UNSUPPORTED_SIZE;    // a run is one cache page of 64 keys
   if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache)) return LLMIE_ERR_ALIGNMENT;
   if (n_seqs == 0) return LLMIE_OK;
   if (n_seqs > 65535 || n_runs > 0x7fffffff / 1) return LLMIE_ERR_UNSUPPORTED_SIZE;
@@ -420,7 +432,7 @@ extern "C" int llmie_attention_decode_fused(const void* q, const void* k_cache, 
   if (n_seqs < 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv || page_size <= 0 || max_pages <= 0 || !counters)
     return LLMIE_ERR_BAD_ARG;
   if (n_runs <= 0) return LLMIE_ERR_BAD_ARG;
-  if (page_size != 64 || run_len % 64) return LLMIE_ERR_UNSUPPORTED_SIZE;
+  if (page_size != 64 || run_len != 64) return LLMIE_ERR_UNSUPPORTED_SIZE;
   if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache)) return LLMIE_ERR_ALIGNMENT;
   if (n_seqs == 0) return LLMIE_OK;
   if (n_seqs > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;

@@ -16,6 +16,9 @@
 // Cost and limits:
 //   * Every GPU on which this library is loaded holds LLMIE_NOALLOC_SCRATCH_BYTES (16 MiB) of
 //     device memory from load until the process exits, whether or not this function is called.
+//   * page_size and run_len must both be 64 (a run is one cache page); anything else is refused with
+//     LLMIE_ERR_UNSUPPORTED_SIZE (-2). n_runs * 64 must cover the longest length in seq_kvlen.
+//   * A sequence whose seq_kvlen is 0 (or negative) has no keys: its rows of `out` are set to zero.
 //   * n_seqs * n_q * n_runs * (hd + 2) floats must fit in the array; a larger problem is refused
 //     with LLMIE_ERR_SCRATCH_TOO_SMALL (-5) and nothing is launched.
 //   * The FIRST call on each device looks the array's device address up

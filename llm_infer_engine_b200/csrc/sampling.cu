@@ -59,10 +59,16 @@ __device__ MaxIdx block_argmax(const float* row, int V, MaxIdx* scratch) {
 
 __global__ void __launch_bounds__(kSampleThreads)
 sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature, float top_p,
-              unsigned long long seed, const int* __restrict__ seq_ids, int* __restrict__ counters,
-              int* __restrict__ out) {
+              unsigned long long seed, const unsigned* __restrict__ dev_params, const int* __restrict__ seq_ids,
+              int* __restrict__ counters, int* __restrict__ out) {
   pdl_launch_dependents();
   pdl_wait();
+  if (dev_params) {
+    // settings kept in device memory: a captured launch then serves every temperature, top_p and seed
+    temperature = __uint_as_float(dev_params[0]);
+    top_p = __uint_as_float(dev_params[1]);
+    seed = (unsigned long long)dev_params[2] | ((unsigned long long)dev_params[3] << 32);
+  }
   __shared__ MaxIdx arg_scratch[32];
   __shared__ float red[32];
   __shared__ float chunk_sum[kSampleThreads];
@@ -212,15 +218,17 @@ __global__ void copy_int_kernel(const int* __restrict__ src, int* __restrict__ d
 using namespace llmie;
 
 // logits: [n_rows, ld] float32 with V <= ld valid columns. seq_ids / counters: [n_rows] (unused when
-// temperature <= 0, may then be null). out: [n_rows] int32.
+// temperature <= 0, may then be null). out: [n_rows] int32. dev_params: null, or four 32-bit words in device
+// memory [bits of temperature, bits of top_p, low and high half of the seed] that stand for the three
+// arguments; seq_ids and counters are then always required.
 extern "C" int llmie_sample(const float* logits, int n_rows, int V, int ld, float temperature, float top_p,
-                            unsigned long long seed, const int* seq_ids, int* counters, int* out,
-                            cudaStream_t stream) {
+                            unsigned long long seed, const unsigned* dev_params, const int* seq_ids, int* counters,
+                            int* out, cudaStream_t stream) {
   if (n_rows < 0 || V <= 0 || ld < V) return LLMIE_ERR_BAD_ARG;
-  if (temperature > 0.f && (!seq_ids || !counters)) return LLMIE_ERR_BAD_ARG;
+  if ((temperature > 0.f || dev_params) && (!seq_ids || !counters)) return LLMIE_ERR_BAD_ARG;
   if (n_rows == 0) return LLMIE_OK;
-  launch_k(sample_kernel, dim3(n_rows), dim3(kSampleThreads), 0, stream, logits, ld, V, temperature, top_p, seed, seq_ids, counters,
-                                                       out);
+  launch_k(sample_kernel, dim3(n_rows), dim3(kSampleThreads), 0, stream, logits, ld, V, temperature, top_p, seed,
+           dev_params, seq_ids, counters, out);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }

@@ -216,18 +216,22 @@ class Engine:
         tokens after the step (default: the engine's limit). Kept per (lanes, length bucket): the
         attention grid of a captured step is sized for the bucket, not for the longest possible sequence.
         With `sampling` (a SamplingParams) the draw of the next tokens is part of the captured step:
-        `sampled` then holds them after a replay. With `host_io` as well, the captured step begins with the
+        `sampled` then holds them after a replay. Greedy and drawing steps are two captures; temperature,
+        top_p and seed of a drawing step live in device memory (`set_sampling`), so one capture serves every
+        setting. With `host_io` as well, the captured step begins with the
         upload of `host_in` (pinned) into `tokens` and ends with the download of `sampled` into `host_out`
         (pinned): a generation loop then needs one launch per step and no copy calls of its own."""
         limit = kv_bucket_for(self.max_seq_len if kv_len is None else kv_len, self.max_seq_len)
         if host_io and sampling is None:
             raise EngineError("decode_graph: host_io needs the draw inside the captured step (give sampling)")
-        key = (n_lanes, limit, None if sampling is None else (sampling.temperature, sampling.top_p, sampling.seed),
-               bool(host_io))
+        mode = None if sampling is None else ("greedy" if sampling.temperature <= 0 else "draw")
+        key = (n_lanes, limit, mode, bool(host_io))
         g = self._graphs.get(key)
         if g is None:
             g = DecodeGraph(self, n_lanes, limit, sampling, host_io)
             self._graphs[key] = g
+        elif sampling is not None:
+            g.set_sampling(sampling)
         return g
 
     def stacked_decode(self):
@@ -300,6 +304,12 @@ class DecodeGraph:
         self.sampled = torch.zeros(n_lanes, **i32)
         self.seq_ids = torch.zeros(n_lanes, **i32)
         self.counters = torch.zeros(n_lanes, **i32)
+        # temperature, top_p and seed of a drawing step, read by the sampling kernel when it runs
+        self.draws = sampling is not None and sampling.temperature > 0
+        self.sample_params = torch.zeros(4, **i32) if self.draws else None
+        self._uploaded = None
+        if self.draws:
+            self.set_sampling(sampling)
         # pinned host memory that the captured step reads its tokens from and leaves the drawn ones in
         self.host_in = torch.zeros(n_lanes, dtype=torch.int32).pin_memory() if self.host_io else None
         self.host_out = torch.zeros(n_lanes, dtype=torch.int32).pin_memory() if self.host_io else None
@@ -315,9 +325,10 @@ class DecodeGraph:
         if self.host_io:
             self.tokens.copy_(self.host_in, non_blocking=True)
         logits = self._forward()
-        if self.sampling is not None:
-            s = self.sampling
-            ops.sample(logits, self.sampled, s.temperature, s.top_p, s.seed, self.seq_ids, self.counters)
+        if self.draws:
+            ops.sample(logits, self.sampled, seq_ids=self.seq_ids, counters=self.counters, params=self.sample_params)
+        elif self.sampling is not None:
+            ops.sample(logits, self.sampled)
         if self.host_io:
             self.host_out.copy_(self.sampled, non_blocking=True)
         return logits
@@ -360,6 +371,17 @@ class DecodeGraph:
             if gc_was_on:
                 gc.enable()
         self.launches_per_replay = ops.LAUNCHES - before      # this library's kernels inside one replay
+
+    def set_sampling(self, sampling) -> None:
+        """The settings the next replays draw with. A greedy capture takes only greedy settings and a
+        drawing capture only temperatures above zero: the two differ in their kernels."""
+        if (sampling.temperature > 0) != self.draws:
+            raise EngineError("set_sampling: a greedy and a drawing step are different captures")
+        if self.draws and sampling != self._uploaded:
+            self.sample_params.copy_(torch.tensor(ops.sampling_words(sampling.temperature, sampling.top_p,
+                                                                     sampling.seed), dtype=torch.int32))
+            self._uploaded = sampling
+        self.sampling = sampling
 
     def set_lanes(self, slots: Sequence[int]) -> None:
         """Which sequences the lanes continue; the rest are padding."""

@@ -12,16 +12,24 @@ from ..kernels import ops
 
 
 class KernelPlan:
+    MIN_COUNTERS = 4096            # counters allocated at least; more than any one-token step of 64 lanes needs
+
     def __init__(self, engine):
         self.engine = engine
         self.bf16 = engine.dtype == torch.bfloat16
         self._counters = None          # zeroed once; the decode attention kernel leaves them zero
+        self._retired = []             # outgrown counter tensors that captured steps may still point to
         # LLMIE_DECODE_ATTN=split keeps the CUDA-core split-KV kernel for every one-token step (for comparisons)
         self.decode_attention = os.environ.get("LLMIE_DECODE_ATTN", "auto")
 
     def _decode_counters(self, need: int, device) -> torch.Tensor:
+        """Zeroed counters for the merge of a decode attention launch. A captured step keeps the address
+        it was captured with, so a tensor that has been handed out is never freed: when a later step needs
+        more, the smaller tensor stays alive beside the new one."""
         if self._counters is None or self._counters.numel() < need:
-            self._counters = torch.zeros(max(need, 1024), dtype=torch.int32, device=device)
+            if self._counters is not None:
+                self._retired.append(self._counters)
+            self._counters = torch.zeros(max(need, self.MIN_COUNTERS), dtype=torch.int32, device=device)
         return self._counters
 
     @staticmethod

@@ -585,19 +585,35 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def sampling_words(temperature: float, top_p: float, seed: int) -> list:
+    """The four 32-bit words (as Python ints) that `sample(..., params=)` reads from device memory."""
+    import struct
+    t, p = struct.unpack("<2I", struct.pack("<2f", float(temperature), float(top_p)))
+    seed = int(seed) & 0xFFFFFFFFFFFFFFFF
+    as_i32 = lambda w: w - (1 << 32) if w >= (1 << 31) else w
+    return [as_i32(t), as_i32(p), as_i32(seed & 0xFFFFFFFF), as_i32(seed >> 32)]
+
+
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float = 0.0, top_p: float = 1.0, seed: int = 0,
-           seq_ids: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None) -> torch.Tensor:
+           seq_ids: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None,
+           params: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One token per row of float32 logits [R, V]: argmax when temperature <= 0 (lowest index wins a
     tie), else a draw from softmax(logits / T) cut by top_p, with the uniform number of
-    (seed, seq_ids[r], counters[r]); counters[r] is then incremented. out int32 [R]."""
+    (seed, seq_ids[r], counters[r]); counters[r] is then incremented. out int32 [R].
+    With `params` (int32 [4] on the device, filled from `sampling_words`) temperature, top_p and seed
+    are read from there when the kernel runs, so a captured launch serves any setting."""
     R, V = logits.shape
-    if temperature <= 0 and V >= 4096 and logits.is_contiguous():
+    if params is not None:
+        _need(params, "params", torch.int32, (4,))
+        if seq_ids is None or counters is None:
+            raise KernelError("sample: seq_ids and counters are required with params")
+    elif temperature <= 0 and V >= 4096 and logits.is_contiguous():
         return argmax(logits, out)
     _need(logits, "logits", torch.float32)
     _need(out, "out", torch.int32)
     if out.shape[0] < R:
         raise KernelError("sample: out is shorter than the number of rows")
-    if temperature > 0:
+    if temperature > 0 or params is not None:
         if seq_ids is None or counters is None:
             raise KernelError("sample: seq_ids and counters are required when temperature > 0")
         _need(seq_ids, "seq_ids", torch.int32)
@@ -606,9 +622,10 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float = 0.0, to
             raise KernelError("sample: seq_ids / counters shorter than the number of rows")
     f = _fn("sampling", "llmie_sample",
             [_c_void_p, _c_int, _c_int, _c_int, _c_float, _c_float, ctypes.c_ulonglong, _c_void_p, _c_void_p,
-             _c_void_p, _c_void_p])
+             _c_void_p, _c_void_p, _c_void_p])
     _check(f(logits.data_ptr(), R, V, logits.stride(0), float(temperature), float(top_p),
-             int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(seq_ids), _ptr(counters), out.data_ptr(), _stream()), "sample")
+             int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(params), _ptr(seq_ids), _ptr(counters), out.data_ptr(), _stream()),
+           "sample")
     return out
 
 

@@ -100,6 +100,54 @@ def plan_batched(requests: dict, batch_size: int, prompt_frac: float = 0.5):
     return steps
 
 
+def plan_chunked(requests: dict, chunk: int):
+    """Each request alone, its tokens in steps of `chunk` tokens: every step after the first brings several
+    tokens at a start position above zero (a prompt taken in pieces)."""
+    steps = []
+    for rid, toks in requests.items():
+        for lo in range(0, len(toks), chunk):
+            part = toks[lo:lo + chunk]
+            steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": part, "want": list(range(len(part)))}],
+                          "end": []})
+        steps[-1]["end"] = [rid]
+    return steps
+
+
+def plan_mixed(requests: dict, chunk: int):
+    """The first request sends its tokens in pieces of `chunk` while all the others, started together with a
+    part of their prompts, go on by one token a step: steps in which one sequence brings many tokens at a
+    start position above zero and the others bring one."""
+    ids = list(requests)
+    long_id, others = ids[0], ids[1:]
+    cut = {rid: max(1, len(requests[rid]) // 2) for rid in others}
+    steps = [{"step": 0, "entries": [{"id": rid, "tokens": requests[rid][:cut[rid]], "want": list(range(cut[rid]))}
+                                     for rid in others],
+              "end": [rid for rid in others if cut[rid] == len(requests[rid])]}]
+    pos = dict(cut)
+    pos[long_id] = 0
+    live = [rid for rid in ids if pos.get(rid, 0) < len(requests[rid])]
+    while live:
+        entries = []
+        for rid in live:
+            n = chunk if rid == long_id else 1
+            part = requests[rid][pos[rid]:pos[rid] + n]
+            entries.append({"id": rid, "tokens": part, "want": list(range(len(part)))})
+            pos[rid] += len(part)
+        done = [rid for rid in live if pos[rid] == len(requests[rid])]
+        steps.append({"step": len(steps), "entries": entries, "end": done})
+        live = [rid for rid in live if rid not in done]
+    return steps
+
+
+def logit_bound(dtype: str, want: torch.Tensor) -> float:
+    """How far an engine's logits of one request may lie from the plain implementation's. float32 is a true
+    32-bit path: rounding of sums of a few hundred terms. bfloat16 rounds every activation between kernels
+    to 8 bits of mantissa, so its bound scales with the logits themselves: 1.5 % of the request's largest."""
+    if dtype == "float32":
+        return 2e-5 * max(1.0, float(want.abs().max()))
+    return 0.015 * float(want.abs().max())
+
+
 def run_plan_engine(engine, steps):
     """Drives Engine.step directly the way bin/trace_run does; returns {id: [T, V] logits}."""
     slots, got = {}, {}
