@@ -11,7 +11,8 @@ Pages hold `page_size` (64) consecutive positions of one sequence; a sequence ho
 pages it has reached, so memory follows the tokens held, not slots x longest length. A group
 with a window gives pages back once no later token can read them. Fixed-size per-sequence state
 (for mixers that carry a recurrent state) lives beside it as [units, slots + 1, *shape] and is
-zeroed when a slot is taken; this architecture asks for none. Slot `n_slots` and page
+zeroed when a slot is taken; this architecture asks for none. A unit may hold several requests of
+either kind, told apart by name (a layer with two mixers). Slot `n_slots` and page
 `n_pages` are scratch: padding lanes of a captured decode step write there.
 
 Each sequence's length lives on the device (`seq_lens`) so that a captured decode step reads
@@ -34,17 +35,24 @@ PAGE_SIZE = 64
 @dataclass(frozen=True)
 class KVRequest:
     """A mixer asks for keys and values of every earlier position (window 0) or of the last
-    `window` positions."""
+    `window` positions. `name` tells several such requests of one unit apart."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    name: str = "kv"
+
+    def geometry(self) -> Tuple[int, int, int]:
+        """What decides which group's storage serves the request."""
+        return (self.n_kv_heads, self.head_dim, self.window)
 
 
 @dataclass(frozen=True)
 class StateRequest:
-    """A mixer asks for a fixed-size float32 state per sequence."""
+    """A mixer asks for a fixed-size state per sequence (float32 unless `dtype` says otherwise),
+    zeroed when a slot is taken."""
     name: str
     shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
 
 
 @dataclass
@@ -58,15 +66,24 @@ class KVUnit:
 
 
 class CacheUnit:
-    """The view of one schedule entry's storage that its mixer gets."""
+    """The view of one schedule entry's storage that its layer gets: `kvs` and `state` by request name;
+    `kv` is the keys and values named "kv", or the only ones there are."""
 
-    def __init__(self, kv: Optional[KVUnit], state: Dict[str, torch.Tensor]):
-        self.kv = kv
-        self.state = state       # name -> [slots + 1, *shape] float32
+    def __init__(self, kvs: Dict[str, KVUnit], state: Dict[str, torch.Tensor]):
+        self.kvs = kvs
+        self.state = state       # name -> [slots + 1, *shape]
+        self.kv = kvs.get("kv") or (next(iter(kvs.values())) if len(kvs) == 1 else None)
+
+    def scoped(self, role: str) -> "CacheUnit":
+        """The requests that a block prefixed with `role.` (a layer with several mixers), under the names the
+        mixer gave them."""
+        cut = len(role) + 1
+        return CacheUnit({n[cut:]: u for n, u in self.kvs.items() if n.startswith(role + ".")},
+                         {n[cut:]: t for n, t in self.state.items() if n.startswith(role + ".")})
 
 
 class _KVGroup:
-    def __init__(self, req: KVRequest, units: List[int], n_pages: int, n_slots: int, max_pages_per_seq: int,
+    def __init__(self, req: KVRequest, units: List[Tuple[int, str]], n_pages: int, n_slots: int, max_pages_per_seq: int,
                  dtype: torch.dtype, device):
         self.req = req
         self.units = units
@@ -100,40 +117,44 @@ class Cache:
         self._mapped_upto: List[int] = [0] * (n_slots + 1)     # positions below this are writable without a new page
         self.seq_lens = torch.zeros(n_slots + 1, dtype=torch.int32, device=device)
 
-        self._groups: Dict[KVRequest, _KVGroup] = {}
-        by_req: Dict[KVRequest, List[int]] = {}
-        state_specs: Dict[Tuple[str, Tuple[int, ...]], List[int]] = {}
+        # groups by geometry (kv heads, head size, window); a member is (unit, request name)
+        self._groups: Dict[Tuple[int, int, int], _KVGroup] = {}
+        by_geometry: Dict[Tuple[int, int, int], List[Tuple[int, str]]] = {}
+        first_request: Dict[Tuple[int, int, int], KVRequest] = {}
+        state_specs: Dict[Tuple[str, Tuple[int, ...], torch.dtype], List[int]] = {}
         for u, reqs in enumerate(unit_requests):
-            n_kv = 0
+            names = set()
             for r in reqs:
-                if isinstance(r, KVRequest):
-                    n_kv += 1
-                    if n_kv > 1:
-                        raise ValueError(f"cache unit {u}: at most one KVRequest per unit")
-                    by_req.setdefault(r, []).append(u)
-                elif isinstance(r, StateRequest):
-                    state_specs.setdefault((r.name, tuple(r.shape)), []).append(u)
-                else:
+                if not isinstance(r, (KVRequest, StateRequest)):
                     raise TypeError(f"cache unit {u}: unknown request {r!r}")
-        for req, units in by_req.items():
-            self._groups[req] = _KVGroup(req, units, self.n_pages, n_slots, self.max_pages_per_seq, dtype, device)
-        self._state: Dict[Tuple[str, Tuple[int, ...]], Tuple[List[int], torch.Tensor]] = {}
-        for (name, shape), units in state_specs.items():
-            self._state[(name, shape)] = (units, torch.zeros((len(units), n_slots + 1) + shape,
-                                                             dtype=torch.float32, device=device))
+                if (type(r), r.name) in names:
+                    raise ValueError(f"cache unit {u}: two {type(r).__name__}s are named {r.name!r}; give them "
+                                     "different names")
+                names.add((type(r), r.name))
+                if isinstance(r, KVRequest):
+                    by_geometry.setdefault(r.geometry(), []).append((u, r.name))
+                    first_request.setdefault(r.geometry(), r)
+                else:
+                    state_specs.setdefault((r.name, tuple(r.shape), r.dtype), []).append(u)
+        for geo, members in by_geometry.items():
+            self._groups[geo] = _KVGroup(first_request[geo], members, self.n_pages, n_slots, self.max_pages_per_seq,
+                                         dtype, device)
+        self._state: Dict[Tuple[str, Tuple[int, ...], torch.dtype], Tuple[List[int], torch.Tensor]] = {}
+        for (name, shape, sdtype), units in state_specs.items():
+            self._state[(name, shape, sdtype)] = (units, torch.zeros((len(units), n_slots + 1) + shape,
+                                                                     dtype=sdtype, device=device))
         self._units: List[CacheUnit] = []
         for u, reqs in enumerate(unit_requests):
-            kv = None
-            state = {}
+            kvs, state = {}, {}
             for r in reqs:
                 if isinstance(r, KVRequest):
-                    g = self._groups[r]
-                    i = g.units.index(u)
-                    kv = KVUnit(g.k[i], g.v[i], g.block_table, PAGE_SIZE, r.window)
+                    g = self._groups[r.geometry()]
+                    i = g.units.index((u, r.name))
+                    kvs[r.name] = KVUnit(g.k[i], g.v[i], g.block_table, PAGE_SIZE, r.window)
                 else:
-                    units, store = self._state[(r.name, tuple(r.shape))]
+                    units, store = self._state[(r.name, tuple(r.shape), r.dtype)]
                     state[r.name] = store[units.index(u)]
-            self._units.append(CacheUnit(kv, state))
+            self._units.append(CacheUnit(kvs, state))
 
     # ---------------------------------------------------------------- views
     def unit(self, u: int) -> CacheUnit:
@@ -144,11 +165,12 @@ class Cache:
         return len(self._units)
 
     def groups(self) -> List[KVRequest]:
-        return list(self._groups)
+        """One request per group of units with storage of its own."""
+        return [g.req for g in self._groups.values()]
 
     def bytes(self) -> int:
         return sum(g.bytes() for g in self._groups.values()) + \
-            sum(s.numel() * 4 for _, s in self._state.values())
+            sum(s.numel() * s.element_size() for _, s in self._state.values())
 
     def free_pages(self) -> int:
         return min((g.table.pages.n_free for g in self._groups.values()), default=self.n_pages)

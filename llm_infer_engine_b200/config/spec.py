@@ -9,6 +9,7 @@ layers run is the `schedule` list.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
+from types import MappingProxyType
 from typing import Any, Mapping, Optional, Sequence
 
 
@@ -22,16 +23,58 @@ class PartSpec:
         return self.params.get(key, default)
 
 
-@dataclass(frozen=True)
 class LayerSpec:
-    """One layer: how its parts are arranged (the block kind), the parts themselves, and the
-    checkpoint sub-names under which each part's tensors are stored."""
-    block: str                                   # registry key of the arrangement, e.g. "pre_norm"
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
-    names: Mapping[str, str]                     # part role -> checkpoint sub-name
+    """One layer: how its parts are arranged (the block kind), the parts themselves by ROLE, and the
+    checkpoint sub-names under which each role's tensors are stored.
+
+    Which roles a layer has is the block's business: every `Block` subclass declares its roles and the
+    part group of each (`Block.ROLES`), and the model builder checks the layer against it. The classic
+    pre-norm block has four (`mixer`, `feed_forward`, `mixer_norm`, `feed_forward_norm`), and for it
+    the short forms below exist; a block with three norms, a second mixer or one shared norm simply
+    names other roles in `parts`.
+
+        LayerSpec("pre_norm", mixer, feed_forward, mixer_norm, feed_forward_norm, names)
+        LayerSpec(block="pre_norm", mixer=..., feed_forward=..., mixer_norm=..., feed_forward_norm=..., names=...)
+        LayerSpec("my_block", parts={"mixer": ..., "mixer_norm": ..., "post_norm": ..., ...}, names={...})
+
+    A role can be read as an attribute (`layer.mixer`)."""
+    CLASSIC_ROLES = ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm")
+
+    def __init__(self, block: str, *classic, parts: Optional[Mapping[str, PartSpec]] = None,
+                 names: Optional[Mapping[str, str]] = None, **by_role: PartSpec):
+        if len(classic) > 5:
+            raise TypeError("LayerSpec takes at most four positional parts and the names")
+        if len(classic) == 5:
+            if names is not None:
+                raise TypeError("LayerSpec: names given twice")
+            names = classic[4]
+        roles = dict(parts or {})
+        for role, spec in list(zip(self.CLASSIC_ROLES, classic[:4])) + list(by_role.items()):
+            if role in roles:
+                raise TypeError(f"LayerSpec: role {role!r} given twice")
+            roles[role] = spec
+        for role, spec in roles.items():
+            if not hasattr(spec, "kind") or not hasattr(spec, "params"):
+                raise TypeError(f"LayerSpec: role {role!r} must be a PartSpec, got {type(spec).__name__}")
+        names = dict(names or {})
+        unnamed = [r for r in roles if r not in names]
+        if unnamed:
+            raise ValueError(f"LayerSpec: no checkpoint sub-name for role(s) {unnamed}")
+        object.__setattr__(self, "block", block)
+        object.__setattr__(self, "parts", MappingProxyType(roles))
+        object.__setattr__(self, "names", MappingProxyType(names))
+
+    def __getattr__(self, role: str) -> PartSpec:
+        parts = self.__dict__.get("parts")
+        if parts is not None and role in parts:
+            return parts[role]
+        raise AttributeError(f"this layer ({self.__dict__.get('block')!r}) has no role {role!r}")
+
+    def __setattr__(self, key, value):
+        raise AttributeError("LayerSpec is read-only")
+
+    def __repr__(self):
+        return f"LayerSpec(block={self.block!r}, parts={dict(self.parts)!r}, names={dict(self.names)!r})"
 
 
 @dataclass(frozen=True)
@@ -58,6 +101,13 @@ class ModelSpec:
     head_name: str
     stop_token_ids: Sequence[int] = ()
     ignore_unexpected: Sequence[str] = ()        # regexes of checkpoint tensors to ignore
+    # Two optional pointwise parts (group "pointwise") outside the layers: one on the float32 residual
+    # stream right after the embedding gather (a scale, absolute position embeddings), one on the float32
+    # logits of the wanted rows (a scale, a cap). Their tensors, if any, live under the given names.
+    after_embedding: Optional[PartSpec] = None
+    after_head: Optional[PartSpec] = None
+    after_embedding_name: str = "after_embedding"
+    after_head_name: str = "after_head"
 
     def validate(self) -> None:
         n = len(self.layers)

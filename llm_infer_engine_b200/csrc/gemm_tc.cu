@@ -155,9 +155,51 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
+// The give-up path of the bounded waits, on its own: one block sets up what the GEMM block sets up (an
+// mbarrier, a TMEM allocation), then one thread waits, for at most `limit` polls, on a barrier at which
+// nothing ever arrives. The wait returns false, the thread records kStatusTimeoutFull and raises the abort
+// flag as the GEMM's roles do, and the block frees its TMEM and returns. It ends within microseconds.
+__global__ void __launch_bounds__(64, 1) wait_probe_kernel(int* __restrict__ status, unsigned limit) {
+  __shared__ GemmShared sh;
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    mbar_init(&sh.full[0], 1);
+    sh.abort = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sh.tmem_base, 32);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  volatile int* abort = &sh.abort;
+  if (warp == 0 && elect_one()) {
+    if (!mbar_wait(&sh.full[0], 0, abort, limit)) {
+      if (!*abort) { *abort = 1; atomicExch(status, kStatusTimeoutFull); }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(sh.tmem_base, 32);
+  }
+}
+
 }  // namespace llmie
 
 using namespace llmie;
+
+// Runs the give-up path of a bounded wait once (see wait_probe_kernel): afterwards *status holds the code of
+// a load that did not arrive. limit: polls before the wait gives up, 1 .. 2^20.
+extern "C" int llmie_tc_wait_probe(int* status, int limit, cudaStream_t stream) {
+  if (!status || limit < 1 || limit > (1 << 20)) return LLMIE_ERR_BAD_ARG;
+  wait_probe_kernel<<<1, 64, 0, stream>>>(status, (unsigned)limit);
+  LLMIE_LAUNCH_CHECK();
+  return LLMIE_OK;
+}
 
 // A [M, K] and W [N, K] bfloat16 row-major (K % 8 == 0, 16-byte aligned), C [M, ldc] bfloat16
 // (out_dtype 1) or float32 (out_dtype 0) with ldc % 8 == 0 and 16-byte aligned. status: one int in

@@ -48,8 +48,9 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 // Waits for the phase with the given parity to complete. Gives up after kSpinLimit polls and
 // returns false; the caller then records a status and winds the kernel down. `abort` (shared
 // memory) lets one role's failure end the others' waits promptly.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
-  for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort,
+                                          unsigned limit = kSpinLimit) {
+  for (unsigned spin = 0; spin < limit; ++spin) {
     if (mbar_test(bar, parity)) return true;
     if (spin > 64) {
       __nanosleep(spin > 4096 ? 256 : 32);

@@ -18,6 +18,7 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
+from ..parts.base import AttentionOptions
 
 
 @dataclass
@@ -40,11 +41,11 @@ class StepContext:
     kernels: Optional[object] = None     # the engine's kernel choices (KernelPlan)
     all_rows: bool = False               # logit_rows is 0..n_tokens-1: every row's logits are wanted
 
-    def attention(self, q, kv, out, n_q: int, n_kv: int, head_dim: int, scale: float, window: int) -> None:
+    def attention(self, q, kv, out, n_q: int, n_kv: int, head_dim: int, options: AttentionOptions) -> None:
         """softmax(q k^T * scale) v over the cache unit `kv`, each token seeing the keys of its own
-        sequence up to its own position (and no further back than `window`, if set)."""
+        sequence up to its own position (and no further back than `options.window`, if set)."""
         plan = self.kernels
-        if plan is not None and plan.attention(self, q, kv, out, n_q, n_kv, head_dim, scale, window):
+        if plan is not None and plan.attention(self, q, kv, out, n_q, n_kv, head_dim, options):
             return
         ops.attention_paged(q, kv.k, kv.v, out, self.tok_pos, self.tok_seq, self.seq_slot, kv.block_table,
-                            kv.page_size, n_q, n_kv, head_dim, scale, window)
+                            kv.page_size, n_q, n_kv, head_dim, options.scale, options.window)

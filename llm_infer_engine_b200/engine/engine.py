@@ -95,7 +95,6 @@ class Engine:
         from .plan import KernelPlan
         self.kernels = KernelPlan(self)
         self._graphs: Dict[tuple, "DecodeGraph"] = {}
-        self._stacked = None          # StackedDecode, False (the model is no such stack) or None (not asked yet)
         self.launches = 0
         # a step's index arrays are written into pinned host memory and uploaded in one asynchronous copy
         self._staging_tensor = torch.empty(0, dtype=torch.int32)
@@ -234,14 +233,6 @@ class Engine:
             g.set_sampling(sampling)
         return g
 
-    def stacked_decode(self):
-        """The single-kernel one-token step (engine/stacked.py), or None when this model or precision
-        has to run part by part."""
-        if self._stacked is None:
-            from .stacked import StackedDecode
-            self._stacked = StackedDecode.plan(self) or False
-        return self._stacked or None
-
     def weight_bytes_per_step(self) -> int:
         return self.model.weight_bytes_per_step()
 
@@ -316,9 +307,6 @@ class DecodeGraph:
         self.logits: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._lane_slots: List[int] = [cache.scratch_slot] * n_lanes
-        stacked = engine.stacked_decode()
-        self.stacked = stacked if stacked is not None and stacked.supports(n_lanes) else None
-        self._stacked_buffers = self.stacked.buffers(n_lanes, self.kv_limit) if self.stacked else None
         self._capture()
 
     def _run(self) -> torch.Tensor:
@@ -335,8 +323,6 @@ class DecodeGraph:
 
     def _forward(self) -> torch.Tensor:
         e = self.engine
-        if self.stacked is not None:
-            return self.stacked.run(self.tokens, self.slots, self.n, self._stacked_buffers)
         ops.prepare_decode(self.slots, e.cache.seq_lens, self.tok_pos, self.tok_seq, self.cu_q, self.seq_start,
                            self.seq_kvlen, self.n)
         ctx = StepContext(

@@ -38,8 +38,10 @@ class KernelPlan:
         (src/flash_decode.py:271-272). Depends only on the step's shape, never on its data."""
         return ops.attention_decode_run_len(n_seqs, head_dim, dtype)
 
-    def attention(self, ctx, q, kv, out, n_q, n_kv, head_dim, scale, window) -> bool:
-        """Returns True when a specialised kernel ran."""
+    def attention(self, ctx, q, kv, out, n_q, n_kv, head_dim, options) -> bool:
+        """Returns True when a specialised kernel ran. Every kernel below takes the options there are
+        today (scale, window); a new option is checked here, kernel by kernel."""
+        scale, window = options.scale, options.window
         if ctx.decode and self.decode_attention != "split" \
                 and ops.attention_decode_mma_supported(head_dim, q.dtype, kv.page_size):
             # bfloat16, head size 64 or 128: a warp per page on the tensor cores

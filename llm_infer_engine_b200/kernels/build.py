@@ -37,7 +37,6 @@ FAMILIES: Dict[str, tuple] = {
     "gemm_skinny": ("gemm_skinny.cu", [], []),
     "gemm_tc": ("gemm_tc.cu", [], []),
     "gemm_fused_decode": ("gemm_fused_decode.cu", [], []),
-    "decode_stack": ("decode_stack.cu", [], []),
     "sampling": ("sampling.cu", [], []),
 }
 

@@ -445,8 +445,7 @@ def norm_qkv_rope(h, norm_w, eps: float, w_qkv, q_out, k_cache, v_cache, table, 
 
 _tc_status = {}
 _TC_STATUS_TEXT = {1: "a TMA load did not arrive", 2: "the tensor cores did not release a stage",
-                   3: "the accumulators were not completed",
-                   4: "a grid-wide barrier of the single-kernel decode step was not reached by every block"}
+                   3: "the accumulators were not completed"}
 
 
 def tc_status_word(device) -> torch.Tensor:
@@ -466,6 +465,15 @@ def check_tc_status(device) -> None:
     if code:
         t.zero_()
         raise KernelError(f"a tensor-core kernel timed out: {_TC_STATUS_TEXT.get(code, code)}")
+
+
+def tc_wait_probe(device, limit: int = 1000) -> None:
+    """Launches one block that waits, for at most `limit` polls, on a barrier at which nothing arrives, gives
+    up, records the status of a load that did not arrive, frees its tensor memory and returns. The next
+    `check_tc_status` then raises. For tests of the give-up path; it never hangs."""
+    f = _fn("gemm_tc", "llmie_tc_wait_probe", [_c_void_p, _c_int, _c_void_p])
+    with torch.cuda.device(device):
+        _check(f(tc_status_word(device).data_ptr(), int(limit), _stream()), "tc_wait_probe")
 
 
 def attention_prefill_tc_supported(head_dim: int, page_size: int, dtype: torch.dtype) -> bool:
@@ -512,52 +520,6 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor
     _check(f(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, N, _dt(out, "out"),
              tc_status_word(a.device).data_ptr(), _stream()), "gemm_tc")
     return out
-
-
-STACK_LAYER_FORMAT = "<9Q3f3i"     # one record of decode_stack's layer table; see StackLayer in csrc/decode_stack.cu
-
-
-def decode_stack_supported(batch: int, d: int, ff: int, n_q: int, n_kv: int, head_dim: int, vocab: int) -> bool:
-    f = _fn("decode_stack", "llmie_decode_stack_supported", [_c_int] * 7)
-    return bool(f(batch, d, ff, n_q, n_kv, head_dim, vocab))
-
-
-def decode_stack_layer_bytes() -> int:
-    return int(_fn("decode_stack", "llmie_decode_stack_layer_bytes", [])())
-
-
-def decode_stack(layers: torch.Tensor, n_layers: int, embedding, final_norm, final_eps: float, head, d: int, ff: int,
-                 n_q: int, n_kv: int, head_dim: int, tokens, slots, seq_lens, batch: int, scratch_slot: int,
-                 block_table, n_runs: int, h, q, attn, act, part_m, part_l, part_acc, logits, sync_words, counters,
-                 phase_ns: Optional[torch.Tensor] = None) -> None:
-    """A whole one-token step of `n_layers` pre-norm (attention, SwiGLU) layers, the final norm and the
-    head in one persistent kernel; see csrc/decode_stack.cu. `layers`: uint8 device tensor of packed
-    records (STACK_LAYER_FORMAT). `sync_words`: two int64 on the device, zero before the first launch
-    and then left alone; `counters`: int32 [8 n_kv], zero before the first launch. Advances seq_lens of the lanes' slots by one. `phase_ns`: optional int64
-    [10 n_layers + 2] that receives block 0's clock at the start and after every phase."""
-    vocab = head.shape[0]
-    _need(embedding, "embedding", torch.bfloat16, (None, d))
-    _need(head, "head", torch.bfloat16, (vocab, d))
-    _need(final_norm, "final_norm", torch.float32, (d,))
-    _need(logits, "logits", torch.float32, (None, vocab))
-    _need(sync_words, "sync_words", torch.int64, (2,))
-    _need(counters, "counters", torch.int32, (8 * n_kv,))
-    for name, t in (("tokens", tokens), ("slots", slots), ("seq_lens", seq_lens), ("block_table", block_table)):
-        _need(t, name, torch.int32)
-    if layers.numel() != n_layers * decode_stack_layer_bytes():
-        raise KernelError("decode_stack: the layer table does not hold n_layers records")
-    if not decode_stack_supported(batch, d, ff, n_q, n_kv, head_dim, vocab):
-        raise KernelError(f"decode_stack: sizes not supported (batch {batch}, d {d}, ff {ff}, heads {n_q}/{n_kv}, "
-                          f"head_dim {head_dim}, vocab {vocab})")
-    f = _fn("decode_stack", "llmie_decode_stack",
-            [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_float, _c_void_p] + [_c_int] * 6 + [_c_void_p] * 3 +
-            [_c_int, _c_int, _c_void_p, _c_int, _c_int] + [_c_void_p] * 13 + [_c_void_p])
-    _check(f(layers.data_ptr(), n_layers, embedding.data_ptr(), final_norm.data_ptr(), float(final_eps),
-             head.data_ptr(), vocab, d, ff, n_q, n_kv, head_dim, tokens.data_ptr(), slots.data_ptr(),
-             seq_lens.data_ptr(), batch, scratch_slot, block_table.data_ptr(), block_table.shape[1], n_runs,
-             h.data_ptr(), q.data_ptr(), attn.data_ptr(), act.data_ptr(), part_m.data_ptr(), part_l.data_ptr(),
-             part_acc.data_ptr(), logits.data_ptr(), sync_words.data_ptr(), sync_words.data_ptr() + 8,
-             counters.data_ptr(), tc_status_word(logits.device).data_ptr(), _ptr(phase_ns), _stream()), "decode_stack")
 
 
 _argmax_parts = {}

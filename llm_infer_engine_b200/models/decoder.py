@@ -27,13 +27,17 @@ class DecoderModel:
         self.hidden_size = spec.hidden_size
         self.vocab_size = spec.vocab_size
         self.blocks: List[Block] = []
-        for layer in spec.layers:
+        for i, layer in enumerate(spec.layers):
             block_cls = lookup("block", layer.block)
-            self.blocks.append(block_cls(
-                build_part("mixer", layer.mixer, runtime), build_part("feed_forward", layer.feed_forward, runtime),
-                build_part("norm", layer.mixer_norm, runtime), build_part("norm", layer.feed_forward_norm, runtime),
-                runtime))
+            roles = block_cls.ROLES
+            if set(roles) != set(layer.parts):
+                raise ValueError(f"layer {i}: block {layer.block!r} has the roles {sorted(roles)}, the layer names "
+                                 f"{sorted(layer.parts)}")
+            self.blocks.append(block_cls({role: build_part(group, layer.parts[role], runtime)
+                                          for role, group in roles.items()}, runtime))
         self.final_norm = build_part("norm", spec.final_norm, runtime)
+        self.after_embedding = build_part("pointwise", spec.after_embedding, runtime) if spec.after_embedding else None
+        self.after_head = build_part("pointwise", spec.after_head, runtime) if spec.after_head else None
         self.embedding: torch.Tensor = None
         self.head: Linear = None
 
@@ -43,27 +47,30 @@ class DecoderModel:
         for pos, call in enumerate(spec.schedule):
             if call.cache_of is None:
                 self.unit_of_entry.append(len(self.unit_requests))
-                self.unit_requests.append(list(self.blocks[call.layer].mixer.cache_requests()))
+                self.unit_requests.append(list(self.blocks[call.layer].cache_requests()))
             else:
                 self.unit_of_entry.append(self.unit_of_entry[call.cache_of])
 
     # ------------------------------------------------------------------ checkpoint tensors
-    def _layer_parts(self) -> List[Tuple[str, Part]]:
+    def _named_parts(self) -> List[Tuple[str, Part]]:
         out = []
         for i, (layer, block) in enumerate(zip(self.spec.layers, self.blocks)):
             prefix = self.spec.layer_prefix.format(i=i)
             for role, part in block.parts().items():
                 out.append((prefix + layer.names[role] + ".", part))
+        out.append((self.spec.final_norm_name + ".", self.final_norm))
+        if self.after_embedding is not None:
+            out.append((self.spec.after_embedding_name + ".", self.after_embedding))
+        if self.after_head is not None:
+            out.append((self.spec.after_head_name + ".", self.after_head))
         return out
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         """Every checkpoint tensor this model reads, by full name."""
         specs = {self.spec.embedding_name: ParamSpec((self.vocab_size, self.hidden_size))}
-        for prefix, part in self._layer_parts():
+        for prefix, part in self._named_parts():
             for local, ps in part.param_specs().items():
                 specs[prefix + local] = ps
-        for local, ps in self.final_norm.param_specs().items():
-            specs[self.spec.final_norm_name + "." + local] = ps
         if not self.spec.tie_head:
             specs[self.spec.head_name] = ParamSpec((self.vocab_size, self.hidden_size))
         return specs
@@ -71,10 +78,8 @@ class DecoderModel:
     def load_tensors(self, tensors: Dict[str, torch.Tensor]) -> None:
         """tensors: full name -> device tensor, for exactly the names of param_specs()."""
         self.embedding = tensors[self.spec.embedding_name].contiguous()
-        for prefix, part in self._layer_parts():
+        for prefix, part in self._named_parts():
             part.load({local: tensors[prefix + local] for local in part.param_specs()})
-        self.final_norm.load({local: tensors[self.spec.final_norm_name + "." + local]
-                              for local in self.final_norm.param_specs()})
         self.head = Linear(self.embedding if self.spec.tie_head else tensors[self.spec.head_name])
 
     def weight_bytes_per_step(self) -> int:
@@ -89,16 +94,23 @@ class DecoderModel:
     def forward(self, ctx, cache) -> torch.Tensor:
         h = torch.empty((ctx.n_tokens, self.hidden_size), dtype=torch.float32, device=self.runtime.device)
         ops.embedding(ctx.tokens, self.embedding, h)
+        if self.after_embedding is not None:
+            h = self.after_embedding.forward(h, ctx)
         pending = None
         for pos, call in enumerate(self.spec.schedule):
             unit = cache.unit(self.unit_of_entry[pos])
             h, pending = self.blocks[call.layer].forward(h, pending, ctx, unit, call.cache_of is None)
+        logits = None
         if pending is None and ctx.all_rows and self.head.weight.dtype == torch.bfloat16 \
                 and self.vocab_size % 16 == 0:
             x = self.final_norm.defer(h)
             if x is not None and x.kind == "rmsnorm":
                 # one-token steps: final norm and head in one kernel
                 logits = torch.empty((h.shape[0], self.vocab_size), dtype=torch.float32, device=h.device)
-                return ops.norm_gemm_f32(x.h, x.weight, x.eps, self.head.weight, logits)
-        x = self.final_norm.forward(h, pending, rows=ctx.logit_rows)
-        return self.head(x, out_dtype=torch.float32)
+                ops.norm_gemm_f32(x.h, x.weight, x.eps, self.head.weight, logits)
+        if logits is None:
+            x = self.final_norm.forward(h, pending, rows=ctx.logit_rows)
+            logits = self.head(x, out_dtype=torch.float32)
+        if self.after_head is not None:
+            logits = self.after_head.forward(logits, ctx, rows=ctx.logit_rows)
+        return logits

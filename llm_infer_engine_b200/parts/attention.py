@@ -14,7 +14,7 @@ import torch
 
 from ..cache.cache import KVRequest
 from ..kernels import ops
-from .base import DeferredNorm, Mixer, ParamSpec, build_part, register_mixer
+from .base import AttentionOptions, DeferredNorm, Mixer, ParamSpec, build_part, register_mixer
 from .linear import Linear
 
 
@@ -39,6 +39,7 @@ class GroupedQueryAttention(Mixer):
                              "(multiples of 16 up to 256)")
         scale = params.get("scale")
         self.scale = float(scale) if scale is not None else self.head_dim ** -0.5
+        self.options = AttentionOptions(scale=self.scale, window=self.window)
         self.position = build_part("position_encoding", params["position"], runtime)
         self.qkv: Linear = None
         self.o: Linear = None
@@ -60,13 +61,6 @@ class GroupedQueryAttention(Mixer):
     def cache_requests(self):
         return [KVRequest(self.n_kv_heads, self.head_dim, self.window)]
 
-    def stack_view(self):
-        table = getattr(self.position, "fused_table", lambda hd: None)(self.head_dim)
-        if table is None or self.window:
-            return None
-        return dict(kind="gqa_rope", qkv=self.qkv.weight, o=self.o.weight, hidden=self.hidden, n_heads=self.n_heads,
-                    n_kv_heads=self.n_kv_heads, head_dim=self.head_dim, scale=self.scale, rope_table=table)
-
     def forward(self, x, ctx, unit, owns_cache, residual=None):
         kv = unit.kv
         q = None
@@ -86,7 +80,7 @@ class GroupedQueryAttention(Mixer):
             q = self.position.encode_and_store(qkv, ctx, kv, self.n_heads, self.n_kv_heads, self.head_dim,
                                                owns_cache)
         out = torch.empty_like(q)
-        ctx.attention(q, kv, out, self.n_heads, self.n_kv_heads, self.head_dim, self.scale, self.window)
+        ctx.attention(q, kv, out, self.n_heads, self.n_kv_heads, self.head_dim, self.options)
         if residual is not None and self.o.add_into(out, residual):
             return None
         return self.o(out)

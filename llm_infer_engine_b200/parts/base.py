@@ -1,12 +1,15 @@
 """Interfaces and registries of the parts a layer is put together from.
 
-Five kinds of part, each with a registry from a kind name to a class:
+Six kinds of part, each with a registry from a kind name to a class:
 
     mixer              x[T, d] -> [T, d], mixes information between positions; may own cache
     feed_forward       x[T, d] -> [T, d], position-wise
     norm               float32 residual rows -> normalised activations
     position_encoding  how positions enter a mixer (rotation of q and k here)
-    block              the arrangement of mixer, feed-forward and norms around the residual stream
+    pointwise          a float32 tensor -> the same tensor changed row by row; the model's two optional
+                       slots outside the layers (after the embedding, after the head)
+    block              the arrangement of a layer's parts around the residual stream; it declares the
+                       roles it has (`ROLES`) and the part group of each
 
 A part is constructed from `(params, runtime)`: `params` is the mapping of its `PartSpec`
 (every size and constant it needs; nothing is read from a model-wide config), `runtime` says
@@ -18,8 +21,9 @@ matching function); a `PartSpec("my_kind", {...})` in a `ModelSpec` now builds i
 """
 from __future__ import annotations
 
+import dataclasses
 from dataclasses import dataclass
-from typing import Dict, List, Mapping, Optional, Tuple
+from typing import Dict, List, Mapping, Optional, Tuple, Union
 
 import torch
 
@@ -41,6 +45,16 @@ class ParamSpec:
     init: Tuple = ("normal",)
 
 
+@dataclass(frozen=True)
+class AttentionOptions:
+    """Everything about softmax(q k^T) v that is not a shape. A mixer fills one and hands it to
+    `ctx.attention`; a further option (a score cap, a bias by distance) becomes a field here with a
+    default that means "off", and `KernelPlan.attention` sends a call that sets it to a kernel that
+    knows it (the plain kernel first), so the call sites of the existing options do not change."""
+    scale: float
+    window: int = 0              # 0 = every earlier key; n = the last n keys, the token's own included
+
+
 class Part:
     def __init__(self, params: Mapping, runtime: Runtime):
         self.params = dict(params)
@@ -55,13 +69,6 @@ class Part:
     def weight_bytes(self) -> int:
         """Bytes of weights that one step reads (for roofline accounting)."""
         return 0
-
-    def stack_view(self) -> Optional[dict]:
-        """What a kernel that runs a whole stack of layers by itself needs of this part: a dict with
-        "kind" and the part's tensors and constants, or None when the part can only be run through
-        forward(). The engine uses such a kernel only when every part of every layer gives a view
-        that the kernel knows; anything else runs part by part."""
-        return None
 
 
 class Norm(Part):
@@ -103,50 +110,111 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    """Two class flags widen what a block hands to `forward`; both default to False, and a part that
+    leaves them so is called with exactly `(x, ctx, unit, owns_cache)`:
+
+    accepts_deferred_norm  x may be a `DeferredNorm` instead of a tensor: the part folds the norm into
+                           its first kernel, or calls `x.apply()` and goes on with the tensor.
+    adds_to_residual       the block also passes `residual=h` (the float32 residual stream [T, d]); the
+                           part may add its output into it inside its last kernel and then returns None
+                           instead of a branch output, or ignores it and returns the output as usual.
+    """
+    accepts_deferred_norm = False
+    adds_to_residual = False
+
     def cache_requests(self) -> List[object]:
         """KVRequest / StateRequest objects: what one run of this mixer needs per sequence."""
         return []
 
-    def forward(self, x: torch.Tensor, ctx, unit, owns_cache: bool) -> torch.Tensor:
-        """x: normalised activations [T, d]. `unit` is the CacheUnit to use; when `owns_cache`
-        is False it belongs to an earlier schedule entry and must only be read."""
+    def forward(self, x: Union[torch.Tensor, "DeferredNorm"], ctx, unit, owns_cache: bool,
+                residual: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """x: normalised activations [T, d] (or a DeferredNorm, see the class flags). `unit` is the
+        CacheUnit to use; when `owns_cache` is False it belongs to an earlier schedule entry and must
+        only be read. Returns the branch output [T, d], or None after adding it into `residual`."""
         raise NotImplementedError
 
 
 class FeedForward(Part):
-    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+    """The class flags of `Mixer` hold here too, with the call `(x, ctx)` as the plain form."""
+    accepts_deferred_norm = False
+    adds_to_residual = False
+
+    def forward(self, x: Union[torch.Tensor, "DeferredNorm"], ctx,
+                residual: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         raise NotImplementedError
+
+
+class Pointwise(Part):
+    """A change of a float32 tensor row by row, for the model's two slots outside the layers."""
+
+    def forward(self, x: torch.Tensor, ctx, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x: float32 [n, width], changed in place or replaced by the returned tensor. After the embedding
+        row i is token i of the step (`ctx.tok_pos[i]` is its position) and `rows` is None; after the head
+        row i is the logits of packed token `rows[i]`."""
+        raise NotImplementedError
+
+
+def call_branch(part, x, ctx, *cache_args, residual: Optional[torch.Tensor] = None):
+    """Calls a mixer or feed-forward the way its class flags ask for: `residual` is passed only to a part
+    that declared `adds_to_residual`, and a DeferredNorm is applied first unless the part accepts one."""
+    if isinstance(x, DeferredNorm) and not part.accepts_deferred_norm:
+        x = x.apply()
+    if part.adds_to_residual and residual is not None:
+        return part.forward(x, ctx, *cache_args, residual=residual)
+    return part.forward(x, ctx, *cache_args)
 
 
 class Block:
     """Arrangement of one layer's parts around the float32 residual stream.
 
+    A subclass declares `ROLES`: role name -> part group ("mixer", "feed_forward", "norm", ...). The model
+    builder builds one part per role from the layer's `LayerSpec.parts` and hands them over as a dict;
+    each is then an attribute of the block under its role name.
+
     forward(h, pending, ctx, unit, owns_cache) -> (h, pending): `pending` is a branch output
     not yet added to h (None at the first layer), so that each residual add can be fused with
     the norm that follows it."""
+    ROLES: Dict[str, str] = {}
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm,
-                 runtime: Runtime):
-        self.mixer = mixer
-        self.feed_forward = feed_forward
-        self.mixer_norm = mixer_norm
-        self.feed_forward_norm = feed_forward_norm
+    def __init__(self, parts: Dict[str, Part], runtime: Runtime):
+        missing = [r for r in self.ROLES if r not in parts]
+        unknown = [r for r in parts if r not in self.ROLES]
+        if missing or unknown:
+            raise ValueError(f"{type(self).__name__} has the roles {sorted(self.ROLES)}; missing {missing}, "
+                             f"unknown {unknown}")
+        clash = [r for r in self.ROLES if hasattr(Block, r) or r in ("runtime", "_parts")]
+        if clash:
+            raise ValueError(f"{type(self).__name__}: role name(s) {clash} collide with the block's own attributes")
+        self._parts = {role: parts[role] for role in self.ROLES}
         self.runtime = runtime
+        for role, part in self._parts.items():
+            setattr(self, role, part)
 
     def parts(self) -> Dict[str, Part]:
-        return {"mixer": self.mixer, "feed_forward": self.feed_forward, "mixer_norm": self.mixer_norm,
-                "feed_forward_norm": self.feed_forward_norm}
+        return dict(self._parts)
+
+    def mixer_roles(self) -> List[str]:
+        return [role for role, group in self.ROLES.items() if group == "mixer"]
+
+    def cache_requests(self) -> List[object]:
+        """What one run of this layer needs per sequence: the requests of its mixers. With one mixer they
+        are the mixer's own; with several, each request's name is prefixed with the mixer's role
+        ("role.name") and `unit.scoped(role)` gives that mixer its own view."""
+        roles = self.mixer_roles()
+        if len(roles) == 1:
+            return list(self._parts[roles[0]].cache_requests())
+        out = []
+        for role in roles:
+            for r in self._parts[role].cache_requests():
+                out.append(dataclasses.replace(r, name=f"{role}.{r.name}"))
+        return out
 
     def forward(self, h, pending, ctx, unit, owns_cache):
         raise NotImplementedError
 
-    def stack_view(self) -> Optional[dict]:
-        """As Part.stack_view, for the arrangement: "kind" plus the views of the four parts."""
-        return None
-
 
 _REGISTRIES: Dict[str, Dict[str, type]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position_encoding": {},
-                                           "block": {}}
+                                           "pointwise": {}, "block": {}}
 
 
 def _register(group: str, kind: str, cls: type) -> None:
@@ -167,6 +235,10 @@ def register_norm(kind: str, cls: type) -> None:
 
 def register_position_encoding(kind: str, cls: type) -> None:
     _register("position_encoding", kind, cls)
+
+
+def register_pointwise(kind: str, cls: type) -> None:
+    _register("pointwise", kind, cls)
 
 
 def register_block(kind: str, cls: type) -> None:

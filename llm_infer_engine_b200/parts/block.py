@@ -3,39 +3,28 @@
 branch output travels to the next norm as `pending`."""
 from __future__ import annotations
 
-from .base import Block, register_block
+from .base import Block, call_branch, register_block
 
 
 class PreNormBlock(Block):
-    """A part that sets `adds_to_residual = True` accepts `residual=h` and may add its output into
-    h itself (in float32, inside its last kernel); it then returns None instead of a branch output.
-    A part that sets `accepts_deferred_norm = True` may be handed a `DeferredNorm` instead of the
-    normalised tensor and folds the norm into its first kernel."""
+    """Roles: mixer, feed_forward and a norm in front of each. A branch whose part declares
+    `accepts_deferred_norm` gets the norm as a promise and folds it into its first kernel; one that declares
+    `adds_to_residual` gets the residual stream and may add its output there itself (parts/base.py)."""
+    ROLES = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm"}
 
     def forward(self, h, pending, ctx, unit, owns_cache):
         x = None
-        if pending is None and getattr(self.mixer, "accepts_deferred_norm", False):
+        if pending is None and self.mixer.accepts_deferred_norm:
             x = self.mixer_norm.defer(h)              # the mixer's first kernel applies the norm
         if x is None:
             x = self.mixer_norm.forward(h, pending)
-        if getattr(self.mixer, "adds_to_residual", False):
-            mixed = self.mixer.forward(x, ctx, unit, owns_cache, residual=h)
-        else:
-            mixed = self.mixer.forward(x, ctx, unit, owns_cache)
+        mixed = call_branch(self.mixer, x, ctx, unit, owns_cache, residual=h)
         x = None
-        if mixed is None and getattr(self.feed_forward, "accepts_deferred_norm", False):
+        if mixed is None and self.feed_forward.accepts_deferred_norm:
             x = self.feed_forward_norm.defer(h)
         if x is None:
             x = self.feed_forward_norm.forward(h, mixed)
-        if getattr(self.feed_forward, "adds_to_residual", False):
-            return h, self.feed_forward.forward(x, ctx, residual=h)
-        return h, self.feed_forward.forward(x, ctx)
-
-    def stack_view(self):
-        views = {role: part.stack_view() for role, part in self.parts().items()}
-        if any(v is None for v in views.values()):
-            return None
-        return dict(kind="pre_norm", **views)
+        return h, call_branch(self.feed_forward, x, ctx, residual=h)
 
 
 register_block("pre_norm", PreNormBlock)

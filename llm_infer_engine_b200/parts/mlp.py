@@ -39,10 +39,6 @@ class SwiGLU(FeedForward):
     def weight_bytes(self) -> int:
         return self.gate_up.nbytes() + self.down.nbytes()
 
-    def stack_view(self):
-        return dict(kind="swiglu", gate_up=self.gate_up.weight, down=self.down.weight, hidden=self.hidden,
-                    intermediate=self.intermediate)
-
     def forward(self, x, ctx, residual=None):
         act = None
         if isinstance(x, DeferredNorm):

@@ -31,9 +31,6 @@ class RMSNorm(Norm):
     def weight_bytes(self) -> int:
         return self.size * 4
 
-    def stack_view(self):
-        return dict(kind="rmsnorm", weight=self.weight, eps=self.eps, size=self.size)
-
     def defer(self, h):
         """One-token steps of the bfloat16 engine: the next product's kernel applies this norm itself."""
         if self.runtime.dtype != torch.bfloat16 or not ops.norm_gemm_supported(h.shape[0], self.size):

@@ -7,11 +7,17 @@ ones in a returned dict, src/loader.py:110-151; a wrong shape raises, :73-76.)
 
 Precision policy: a tensor stored in bfloat16 (or float16) is kept in bfloat16 by a bfloat16
 engine and widened to float32 by a float32 engine (exact). A tensor stored in 32-bit stays
-in 32-bit in either engine. Integer tensors become int32. Nothing is ever narrowed on load.
+in 32-bit in either engine. Integer tensors become int32. The one narrowing there is: float16 becomes
+bfloat16 in a bfloat16 engine (same width, fewer mantissa bits), since the kernels know one 16-bit format.
+
+A checkpoint of a model with a tied head that also stores the head matrix (as some exporters do) is
+accepted when that tensor has the embedding's shape: it is not read, and the report says so, as the
+reference reports and goes on (src/loader.py:147-151).
 """
 from __future__ import annotations
 
 import re
+import sys
 from typing import Dict, List
 
 import torch
@@ -65,7 +71,15 @@ def load_weights(model: DecoderModel, model_dir: str) -> Dict[str, int]:
     specs = model.param_specs()
     expected = {n: ps.shape for n, ps in specs.items()}
     found = {n: f.entries[n][1] for n, f in files.items()}
-    compare(expected, found, list(model.spec.ignore_unexpected), model_dir)
+    ignore = list(model.spec.ignore_unexpected)
+    skipped = []
+    head, emb = model.spec.head_name, model.spec.embedding_name
+    if model.spec.tie_head and head in found and emb in expected and tuple(found[head]) == tuple(expected[emb]):
+        ignore.append(re.escape(head) + "$")
+        skipped.append(head)
+        print(f"[llm_infer_engine_b200] {model_dir}: the head is tied to the embedding; the stored {head} is not read",
+              file=sys.stderr)
+    compare(expected, found, ignore, model_dir)
     rt = model.runtime
     tensors = {}
     n_bytes = 0
@@ -75,7 +89,7 @@ def load_weights(model: DecoderModel, model_dir: str) -> Dict[str, int]:
         tensors[name] = host.to(device=rt.device, dtype=dtype)
         n_bytes += tensors[name].numel() * tensors[name].element_size()
     model.load_tensors(tensors)
-    return {"tensors": len(tensors), "bytes": n_bytes}
+    return {"tensors": len(tensors), "bytes": n_bytes, "skipped": skipped}
 
 
 def build_model(model_dir: str, dtype: torch.dtype, device, max_positions: int | None = None):

@@ -186,6 +186,21 @@ def sample_with_uniform(logit_row: torch.Tensor, temperature: float, top_p: floa
     return idx
 
 
+def sample_margins(logit_row: torch.Tensor, temperature: float, top_p: float, u: float):
+    """How close the draw of sample_with_uniform is to going another way: (distance of u from the nearest
+    edge between two kept tokens in the cumulative distribution, distance of top_p from the nearest mass at
+    which a token is cut). Both are in units of probability; a float32 sampler may differ from this
+    float64 one only where one of them is tiny."""
+    probs = torch.softmax(logit_row.double() / temperature, dim=-1)
+    keep = kept_by_top_p(probs, top_p)
+    kept = torch.where(keep, probs, torch.zeros_like(probs))
+    cdf = torch.cumsum(kept, dim=-1) / kept.sum().clamp_min(1e-12)
+    draw_gap = float((cdf - u).abs().min())
+    mass_before = torch.cumsum(torch.sort(probs, descending=True, stable=True).values, dim=-1)
+    cut_gap = float((mass_before - max(0.0, min(1.0, float(top_p)))).abs().min())
+    return draw_gap, cut_gap
+
+
 # ----------------------------------------------------------------------------- random models
 TINY_A = {
     "architectures": ["LlamaForCausalLM"], "model_type": "llama",

@@ -9,10 +9,10 @@ import plain_llama as plain
 
 pytestmark = pytest.mark.gpu
 
-# float32: the path is true 32-bit, so it must agree to rounding of a ~1-magnitude logit.
-# bfloat16: activations between kernels are rounded to 8 bits of mantissa; the bound is on the
-# logits' own scale and is the same for every way of cutting the work.
-TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+# The bounds are helpers.logit_bound's: float32 agrees to rounding; bfloat16 within 1.5 % of the request's
+# largest logit, the same for every way of cutting the work. Random small weights give nearly flat attention, so
+# on these models a lost key hides inside the bfloat16 bound; test_far_keys_and_page_edges_matter (sharpened
+# weights, all three configurations) is where a lost key shows in both precisions.
 LENGTHS = {"a": [5, 11, 17, 40, 64, 65, 100], "b": [1, 9, 33, 70, 128, 129, 200], "c": [3, 127, 128, 129, 300, 700, 64]}
 
 _engines = {}
@@ -39,11 +39,12 @@ def oracle(tag, requests):
     return {rid: plain.logits(w, cfg, toks) for rid, toks in requests.items()}
 
 
-def check(got, want, tol, what):
+def check(got, want, dtype, what):
     for rid in want:
         assert got[rid].shape == want[rid].shape, (what, rid, got[rid].shape, want[rid].shape)
         diff = (got[rid] - want[rid]).abs()
         worst = int(diff.max(dim=1).values.argmax())
+        tol = helpers.logit_bound(dtype, want[rid])
         assert float(diff.max()) <= tol, (f"{what}: request {rid} differs by {float(diff.max()):.3e} "
                                           f"(tolerance {tol}), first at token {int((diff.max(dim=1).values > tol).nonzero()[0])}, "
                                           f"worst at token {worst} of {len(diff)}")
@@ -63,7 +64,7 @@ def test_replay_matches_plain(tag, dtype, mode):
         steps = helpers.plan_batched(requests, batch_size=3)
     engine = engine_for(tag, dtype)
     got = helpers.run_plan_engine(engine, steps)
-    check(got, want, TOL[dtype], f"{tag}/{dtype}/{mode}")
+    check(got, want, dtype, f"{tag}/{dtype}/{mode}")
     if dtype == "bfloat16":
         from llm_infer_engine_b200.kernels import ops
         ops.check_tc_status("cuda")
@@ -80,7 +81,7 @@ def test_trace_run_program(dtype):
     steps = helpers.plan_batched(requests, batch_size=4)
     got = helpers.run_plan_trace_run(helpers.model_folder(tag), dtype, steps, helpers.max_tokens_for(steps),
                                      helpers.TINY[tag]["cfg"]["vocab_size"])
-    check(got, want, TOL[dtype], f"trace_run/{dtype}")
+    check(got, want, dtype, f"trace_run/{dtype}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -101,7 +102,7 @@ def test_wide_batches_match_plain(dtype, n_requests):
     steps = helpers.plan_batched(requests, batch_size=n_requests, prompt_frac=0.8)
     engine = Engine(folder, dtype=dtype, max_batch=n_requests, max_tokens=64 * 3 * n_requests, cuda_graph=False)
     got = helpers.run_plan_engine(engine, steps)
-    check(got, want, TOL[dtype], f"{tag}/{dtype}/wide{n_requests}")
+    check(got, want, dtype, f"{tag}/{dtype}/wide{n_requests}")
     if dtype == "bfloat16":
         from llm_infer_engine_b200.kernels import ops
         ops.check_tc_status("cuda")

@@ -28,14 +28,14 @@ def plain_greedy(w, cfg, prompt, n_new, stop=()):
 
 def agree_or_near_tie(w, cfg, prompt, got, want_fn, gap):
     """Greedy tokens must match the plain implementation; where they part, the plain logits of
-    the two candidates must be within `gap` (a near-tie), and comparison stops there."""
+    the two candidates must be within `gap` (a near-tie). The engine's token is then followed, so
+    that every later token is still compared, each against the plain logits of the engine's own history."""
     seq = list(prompt)
     for tok in got:
         row = plain.logits(w, cfg, seq)[-1]
         best = plain.greedy(row)
         if tok != best:
             assert float(row[best] - row[tok]) < gap, (len(seq), tok, best, float(row[best] - row[tok]))
-            return
         seq.append(tok)
 
 
@@ -162,52 +162,71 @@ def test_seeded_sampling_does_not_depend_on_batching():
     assert together == one_by_one
     assert together != generate(Engine(folder, dtype="float32", max_batch=4), prompts, 12,
                                 SamplingParams(temperature=0.8, top_p=0.9, seed=100), stop_ids=[])
-    # each token is the plain draw at the uniform number of (seed, request index, draw index)
+    # each token is the plain draw at the uniform number of (seed, request index, draw index). The kernel draws
+    # in float32 and the plain implementation in float64: they may part only where the uniform number lies within
+    # 1e-5 of an edge of the cumulative distribution, or top_p within 1e-5 of a mass at which a token is cut.
+    # After such an edge the engine's own token is followed, so every later draw is still compared.
+    edges = 0
     for r, (p, out) in enumerate(zip(prompts, together)):
         seq = list(p)
         for i, tok in enumerate(out):
-            want = plain.sample_with_uniform(plain.logits(w, cfg, seq)[-1], 0.8, 0.9, uniform_for(99, r, i))
+            row = plain.logits(w, cfg, seq)[-1]
+            u = uniform_for(99, r, i)
+            want = plain.sample_with_uniform(row, 0.8, 0.9, u)
             if tok != want:
-                return_ok = abs(i) >= 0                              # a rounding edge: stop comparing this request
-                assert return_ok
-                break
+                draw_gap, cut_gap = plain.sample_margins(row, 0.8, 0.9, u)
+                assert min(draw_gap, cut_gap) < 1e-5, (r, i, tok, want, draw_gap, cut_gap)
+                edges += 1
             seq.append(tok)
-        else:
-            continue
+    assert edges <= 2, edges
     assert sum(len(set(o)) for o in together) > 20               # it does sample, not repeat one token
 
 
-@pytest.mark.parametrize("dtype,tol", [("float32", 1e-4), ("bfloat16", 0.08)])
-def test_far_keys_and_page_edges_matter(dtype, tol):
+# per configuration: the factor on the q and k projections, the lengths, the bfloat16 bound. Sharper scores cost
+# bfloat16 accuracy by themselves (a score of 30 carries the rounding of q and k as 0.1), so the factor is
+# chosen per model to keep the bound several times below what a lost page of keys would change.
+SHARP = {"a": (12.0, [128, 65, 100, 64], 0.03), "b": (6.0, [200, 130, 256, 65], 0.08),
+         "c": (2.0, [300, 130, 700, 65], 0.08)}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("tag", ["a", "b", "c"])
+def test_far_keys_and_page_edges_matter(tag, dtype):
     """Random small weights give nearly flat attention, which would hide a lost key. Here q and k
     projections are scaled up so that each query looks hard at a few keys, many of them far away
     or across page edges; one token at a time over several pages, slots used again."""
     from safetensors.torch import load_file, save_file
     import json
     from llm_infer_engine_b200 import Engine
-    src = helpers.model_folder("b")
+    scale, lens, tol = SHARP[tag]
+    if dtype == "float32":
+        tol = 1e-4
+    src = helpers.model_folder(tag)
     t = load_file(os.path.join(src, "model.safetensors"))
     for name in t:
         if "q_proj" in name or "k_proj" in name:
-            t[name] = (t[name].float() * 6.0).to(torch.bfloat16)
+            t[name] = (t[name].float() * scale).to(torch.bfloat16)
     folder = helpers.scratch_folder("llmie_sharp_")
     save_file(t, os.path.join(folder, "model.safetensors"))
     json.dump(helpers.read_config(src), open(os.path.join(folder, "config.json"), "w"))
     w, cfg = helpers.plain_weights(folder), helpers.read_config(folder)
-    requests = {f"s{i}": helpers.random_tokens(cfg["vocab_size"], n, seed=600 + i) for i, n in enumerate([200, 130, 256, 65])}
+    requests = {f"s{i}": helpers.random_tokens(cfg["vocab_size"], n, seed=600 + i) for i, n in enumerate(lens)}
     want = {rid: plain.logits(w, cfg, toks) for rid, toks in requests.items()}
-    # attention is sharp: the largest softmax weight of a late query is far from 1/T
-    engine = Engine(folder, dtype=dtype, max_batch=2, max_tokens=64 * 8, cuda_graph=False)
-    for plan in (helpers.plan_whole(requests), helpers.plan_tail(requests, 100), helpers.plan_batched(requests, 2, 0.3)):
+    engine = Engine(folder, dtype=dtype, max_batch=2, max_tokens=64 * 16, cuda_graph=False)
+    worst = 0.0
+    for plan in (helpers.plan_whole(requests), helpers.plan_tail(requests, 100), helpers.plan_batched(requests, 2, 0.3),
+                 helpers.plan_chunked(requests, 50)):
         got = helpers.run_plan_engine(engine, plan)
         for rid in requests:
             err = float((got[rid] - want[rid]).abs().max())
+            worst = max(worst, err)
             assert err <= tol, (rid, err)
+    print(f"sharp {tag} {dtype}: worst {worst:.3e}")
     # and the sharpness is real: dropping the first page of keys changes the logits by far more than tol
     toks = requests["s0"]
     full = plain.logits(w, cfg, toks)[-1]
     cut = plain.logits(w, cfg, toks[64:])[-1]
-    assert float((full - cut).abs().max()) > max(0.5, 5 * tol)
+    assert float((full - cut).abs().max()) > 5 * tol, float((full - cut).abs().max())
 
 
 def test_long_decoding_in_float32():

@@ -359,6 +359,32 @@ def test_gemm_tc(M, N, K):
     assert torch.equal(out16.cpu(), out32.cpu().to(torch.bfloat16))
 
 
+def test_a_bounded_wait_that_runs_out_is_reported_and_leaves_the_device_usable():
+    """The give-up path of the tensor-core kernels' bounded waits: a block waits (at most 1,000 polls) on a
+    barrier at which nothing arrives. It must give up, leave the code of the wait in the status word, free
+    its tensor memory and return; the host then raises once, the word is clean again, and the next
+    tensor-core product (which needs the tensor memory the block held) is correct."""
+    import time
+    o = ops()
+    o.check_tc_status(DEV)                       # clean before
+    t0 = time.time()
+    o.tc_wait_probe(DEV, limit=1000)
+    with pytest.raises(o.KernelError, match="timed out: a TMA load did not arrive"):
+        o.check_tc_status(DEV)
+    assert time.time() - t0 < 5.0                # it gave up after its polls; it did not hang
+    assert int(o.tc_status_word(DEV).item()) == 0
+    o.check_tc_status(DEV)                       # raised once, clean again
+    # tensor memory was freed and the context is intact: a full-size product right after is right
+    g = torch.Generator().manual_seed(1)
+    a = torch.randn(256, 512, generator=g).to(torch.bfloat16)
+    w = (torch.randn(384, 512, generator=g) / math.sqrt(512)).to(torch.bfloat16)
+    out = torch.full((256, 384), float("nan"), dtype=torch.float32, device=DEV)
+    for _ in range(3):                           # several blocks per SM over time: none finds the memory still held
+        o.gemm_tc(a.to(DEV), w.to(DEV), out)
+    o.check_tc_status(DEV)
+    assert float((out.cpu().double() - a.double() @ w.double().T).abs().max()) < 5e-4
+
+
 # ------------------------------------------------------------------------------------------ tcgen05 prefill attention
 @pytest.mark.parametrize("n_q,n_kv,hd", [(4, 2, 64), (3, 1, 64), (8, 8, 64), (4, 1, 128), (6, 2, 128)])
 def test_attention_prefill_tc(n_q, n_kv, hd):
@@ -478,6 +504,23 @@ def test_norm_qkv_rope(batch, n_q, n_kv, hd, K):
     assert torch.allclose(v_dev.float(), v2.float(), atol=3e-2, rtol=3e-2)
     # and it wrote exactly the cache rows the unfused path wrote
     assert torch.equal((k_dev != pg.dev()[0]).any(-1), (k2 != pg.dev()[0]).any(-1))
+    # against plain torch: norm and product in float64 on the bfloat16 weights, plain rotation by position
+    x64 = h.double()
+    x64 = x64 * torch.rsqrt((x64 * x64).mean(-1, keepdim=True) + 1e-5) * nw.double()
+    qkv64 = x64 @ w.double().T
+    for b in range(batch):
+        c, s_ = cos[starts[b]].double(), sin[starts[b]].double()
+        rot = lambda v: torch.cat([v[..., :hd // 2] * c - v[..., hd // 2:] * s_, v[..., hd // 2:] * c + v[..., :hd // 2] * s_], -1)
+        q_ref = rot(qkv64[b, :n_q * hd].view(n_q, hd))
+        k_ref = rot(qkv64[b, n_q * hd:(n_q + n_kv) * hd].view(n_kv, hd))
+        v_ref = qkv64[b, (n_q + n_kv) * hd:].view(n_kv, hd)
+        page = int(pg.block_table[pg.slots[b], starts[b] // 64])
+        k_got = k_dev[page, :, starts[b] % 64].double().cpu()
+        v_got = v_dev[page, :, starts[b] % 64].double().cpu()
+        # bfloat16 outputs of values a few units large: half a unit in the last place is 2^-8 of the value
+        for name, got_t, ref_t in (("q", q[b].double().cpu().view(n_q, hd), q_ref), ("k", k_got, k_ref), ("v", v_got, v_ref)):
+            err = float((got_t - ref_t).abs().max())
+            assert err <= 2e-2 * max(1.0, float(ref_t.abs().max())), (name, b, err, float(ref_t.abs().max()))
 
 
 def test_attention_decode_merge_reads_fresh_partials():

@@ -106,3 +106,28 @@ def test_long_context_1b_shape():
     err = float((torch.cat(rows) - want[1:]).abs().max())
     assert err <= bound, ("graph", err, bound)
     ops.check_tc_status("cuda")
+
+
+def test_full_depth_1b_float32():
+    """All 16 layers of the 1B shape in float32: one 150-token request whole, then again with its last 32
+    tokens one by one, within 1e-3 of the plain implementation at every position, so that the growth of
+    rounding differences over the full depth is pinned, not only the widths."""
+    from llm_infer_engine_b200 import Engine, write_random_model
+    cfg = dict(SHAPES["1b"], num_hidden_layers=16)
+    folder = helpers.scratch_folder("llmie_1b_full_")
+    write_random_model(cfg, folder, seed=2, std=0.02)
+    w = helpers.plain_weights(folder)
+    requests = {"full": helpers.random_tokens(128256, 150, seed=950)}
+    want = plain.logits(w, cfg, requests["full"])
+    del w
+    engine = Engine(folder, dtype="float32", max_batch=1, max_seq_len=256, max_tokens=256, cuda_graph=False)
+    for plan in (helpers.plan_whole(requests), helpers.plan_tail(requests, 32)):
+        got = helpers.run_plan_engine(engine, plan)["full"]
+        err = float((got - want).abs().max())
+        assert err <= 1e-3, err
+        a, b = got.argmax(-1), want.argmax(-1)
+        for t in (a != b).nonzero().flatten().tolist():
+            top2 = want[t].topk(2).values
+            assert float(top2[0] - top2[1]) < 1e-5, t
+    del engine
+    torch.cuda.empty_cache()

@@ -256,3 +256,163 @@ def test_state_is_reset_when_a_slot_is_used_again(toy_folder):
         got = engine.step([slot], [toks], "all").cpu()
         engine.close(slot)
         assert float((got - toy_plain_logits(w, TOY, toks)).abs().max()) < 5e-5
+
+
+# ------------------------------------------------------------------------------------------ other arrangements
+# A second toy architecture for the edges of the part interfaces: a block with THREE norms (one of them on the
+# mixer's output), a block with TWO mixers behind ONE shared norm whose three branches run in parallel (its
+# cache unit holds keys and values for one mixer and a state for the other), learned absolute positions and a
+# scale right after the embedding, and a cap on the logits after the head. All of it is defined here.
+def _register_arrangements():
+    from llm_infer_engine_b200.config import LayerCall, LayerSpec, ModelSpec, PartSpec, register_architecture
+    from llm_infer_engine_b200.parts import (Block, ParamSpec, Pointwise, call_branch, register_block,
+                                             register_pointwise)
+
+    class SandwichBlock(Block):
+        """h += post_norm(mixer(norm(h))); h += feed_forward(norm(h))."""
+        ROLES = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "mixer_post_norm": "norm",
+                 "feed_forward_norm": "norm"}
+
+        def forward(self, h, pending, ctx, unit, owns_cache):
+            x = self.mixer_norm.forward(h, pending)
+            mixed = call_branch(self.mixer, x, ctx, unit, owns_cache)            # no residual: the output is normed first
+            mixed = self.mixer_post_norm.forward(mixed.float().contiguous(), None)
+            x = self.feed_forward_norm.forward(h, mixed)
+            return h, call_branch(self.feed_forward, x, ctx, residual=h)
+
+    class ParallelBlock(Block):
+        """x = norm(h); h += attn(x) + rec(x) + feed_forward(x)."""
+        ROLES = {"attn": "mixer", "rec": "mixer", "feed_forward": "feed_forward", "norm": "norm"}
+
+        def forward(self, h, pending, ctx, unit, owns_cache):
+            x = self.norm.forward(h, pending)
+            a = call_branch(self.attn, x, ctx, unit.scoped("attn"), owns_cache)
+            r = call_branch(self.rec, x, ctx, unit.scoped("rec"), owns_cache)
+            f = call_branch(self.feed_forward, x, ctx)
+            return h, (a.float() + r.float() + f.float()).to(x.dtype)
+
+    class ScaleAndPositions(Pointwise):
+        def __init__(self, params, runtime):
+            super().__init__(params, runtime)
+            self.scale, self.hidden, self.max_pos = float(params["scale"]), int(params["hidden"]), int(params["max_pos"])
+
+        def param_specs(self):
+            return {"positions.weight": ParamSpec((self.max_pos, self.hidden))}
+
+        def load(self, tensors):
+            self.table = tensors["positions.weight"].float()
+
+        def forward(self, x, ctx, rows=None):
+            return (x * self.scale + self.table[ctx.tok_pos.long()]).contiguous()
+
+    class SoftCap(Pointwise):
+        def forward(self, x, ctx, rows=None):
+            cap = float(self.params["cap"])
+            return cap * torch.tanh(x / cap)
+
+    register_block("toy_sandwich", SandwichBlock)
+    register_block("toy_parallel", ParallelBlock)
+    register_pointwise("toy_scale_positions", ScaleAndPositions)
+    register_pointwise("toy_softcap", SoftCap)
+
+    @dataclass(frozen=True)
+    class Config:
+        d: dict
+
+        @staticmethod
+        def from_dict(d):
+            return Config(dict(d))
+
+    def to_spec(c) -> ModelSpec:
+        c = c.d
+        norm = PartSpec("rmsnorm", {"size": c["hidden"], "eps": c["eps"]})
+        attn = PartSpec("gqa_attention", {
+            "hidden": c["hidden"], "n_heads": c["heads"], "n_kv_heads": c["kv_heads"], "head_dim": c["head_dim"],
+            "window": 0, "scale": None, "position": PartSpec("rope", {"rot_dim": c["head_dim"], "theta": 100.0,
+                                                                     "scaling": None})})
+        rec = PartSpec("toy_decay", {"hidden": c["hidden"], "width": c["width"], "decay": c["decay"]})
+        ff = PartSpec("swiglu", {"hidden": c["hidden"], "intermediate": c["inner"]})
+        sandwich = LayerSpec("toy_sandwich", parts={"mixer": attn, "feed_forward": ff, "mixer_norm": norm,
+                                                     "mixer_post_norm": norm, "feed_forward_norm": norm},
+                             names={"mixer": "mix", "feed_forward": "ff", "mixer_norm": "n1", "mixer_post_norm": "n1b",
+                                    "feed_forward_norm": "n2"})
+        parallel = LayerSpec("toy_parallel", parts={"attn": attn, "rec": rec, "feed_forward": ff, "norm": norm},
+                             names={"attn": "attn", "rec": "rec", "feed_forward": "ff", "norm": "n"})
+        return ModelSpec(hidden_size=c["hidden"], vocab_size=c["vocab"], max_position=c["max_pos"],
+                         layers=[sandwich, parallel, sandwich], schedule=[LayerCall(0), LayerCall(1), LayerCall(2)],
+                         final_norm=norm, tie_head=False, embedding_name="emb.weight", layer_prefix="blocks.{i}.",
+                         final_norm_name="final", head_name="head.weight",
+                         after_embedding=PartSpec("toy_scale_positions", {"scale": c["emb_scale"], "hidden": c["hidden"],
+                                                                          "max_pos": c["max_pos"]}),
+                         after_head=PartSpec("toy_softcap", {"cap": c["cap"]}), after_embedding_name="pre")
+
+    register_architecture("ToyArrangementsForCausalLM", Config, to_spec)
+
+
+ARR = {"architectures": ["ToyArrangementsForCausalLM"], "hidden": 40, "vocab": 61, "heads": 2, "kv_heads": 1,
+       "head_dim": 32, "width": 12, "decay": 0.8, "inner": 56, "eps": 1e-5, "max_pos": 200, "emb_scale": 3.0, "cap": 2.0}
+
+
+def arrangements_plain_logits(w, cfg, tokens):
+    T, hd, H, Hkv = len(tokens), cfg["head_dim"], cfg["heads"], cfg["kv_heads"]
+    cos, sin = plain.rotation_tables(torch.arange(T), plain.inv_frequencies(hd, 100.0, None))
+    norm = lambda x, name: plain.rms_norm(x, w[name + ".weight"], cfg["eps"])
+
+    def attention(x, p):
+        q = plain.rotate_half((x @ w[p + "q_proj.weight"].T).view(T, H, hd).transpose(0, 1), cos, sin)
+        k = plain.rotate_half((x @ w[p + "k_proj.weight"].T).view(T, Hkv, hd).transpose(0, 1), cos, sin)
+        v = (x @ w[p + "v_proj.weight"].T).view(T, Hkv, hd).transpose(0, 1)
+        return plain.causal_gqa_attention(q, k, v).transpose(0, 1).reshape(T, H * hd) @ w[p + "o_proj.weight"].T
+
+    def recurrent(x, p):
+        u = x @ w[p + "in_proj.weight"].T
+        s, rows = torch.zeros(cfg["width"]), []
+        for t in range(T):
+            s = cfg["decay"] * s + u[t]
+            rows.append(s)
+        return torch.stack(rows) @ w[p + "out_proj.weight"].T
+
+    def swiglu(x, p):
+        g = x @ w[p + "gate_proj.weight"].T
+        return ((g * torch.sigmoid(g)) * (x @ w[p + "up_proj.weight"].T)) @ w[p + "down_proj.weight"].T
+
+    h = w["emb.weight"][torch.tensor(tokens)] * cfg["emb_scale"] + w["pre.positions.weight"][:T]
+    for layer in (0, 1, 2):
+        p = f"blocks.{layer}."
+        if layer == 1:
+            x = norm(h, p + "n")
+            h = h + attention(x, p + "attn.") + recurrent(x, p + "rec.") + swiglu(x, p + "ff.")
+        else:
+            h = h + norm(attention(norm(h, p + "n1"), p + "mix."), p + "n1b")
+            h = h + swiglu(norm(h, p + "n2"), p + "ff.")
+    logits = norm(h, "final") @ w["head.weight"].T
+    return cfg["cap"] * torch.tanh(logits / cfg["cap"])
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 5e-5), ("bfloat16", 0.05)])
+def test_other_arrangements_need_only_additions(tmp_path_factory, dtype, tol):
+    """Three norms in a block, two mixers and one shared norm in another, parts outside the layers: built from
+    registrations made in this file, stepped whole, one by one and in batches, like its plain restatement."""
+    _register()
+    _register_arrangements()
+    from llm_infer_engine_b200 import Engine, write_random_model
+    folder = str(tmp_path_factory.mktemp("arrangements"))
+    write_random_model(ARR, folder, seed=5, std=0.2, norm_range=(0.7, 1.3))
+    engine = Engine(folder, dtype=dtype, max_batch=3, max_tokens=64 * 9, cuda_graph=False)
+    # the parallel layer's unit holds keys and values for one mixer and a state for the other, under the roles' names
+    unit = engine.cache.unit(1)
+    assert sorted(unit.kvs) == ["attn.kv"] and sorted(unit.state) == ["rec.s"]
+    assert unit.scoped("rec").state["s"].shape[-1] == ARR["width"] and unit.scoped("attn").kv is not None
+    assert sorted(engine.model.blocks[0].parts()) == ["feed_forward", "feed_forward_norm", "mixer", "mixer_norm",
+                                                      "mixer_post_norm"]
+    w = helpers.plain_weights(folder)
+    assert "blocks.0.n1b.weight" in w and "pre.positions.weight" in w and "blocks.1.rec.in_proj.weight" in w
+    requests = {f"a{i}": helpers.random_tokens(ARR["vocab"], n, seed=70 + i) for i, n in enumerate([9, 70, 130, 64])}
+    want = {rid: arrangements_plain_logits(w, ARR, toks) for rid, toks in requests.items()}
+    for plan in (helpers.plan_whole(requests), helpers.plan_tail(requests, 32), helpers.plan_batched(requests, 3),
+                 helpers.plan_chunked(requests, 50)):
+        got = helpers.run_plan_engine(engine, plan)
+        for rid in requests:
+            err = float((got[rid] - want[rid]).abs().max())
+            assert err <= tol * max(1.0, float(want[rid].abs().max())), (rid, err)
+    assert engine.cache.free_slots() == 3 and engine.cache.free_pages() == engine.cache.n_pages

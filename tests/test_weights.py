@@ -72,7 +72,7 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     del t["model.layers.1.mlp.up_proj.weight"], t["model.norm.weight"]
     t["model.layers.0.self_attn.q_proj.weight"] = torch.zeros(64, 63, dtype=torch.bfloat16)
     t["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)          # ignored by the architecture
-    t["lm_head.weight"] = torch.zeros(256, 64, dtype=torch.bfloat16)            # tied model: not expected
+    t["lm_head.weight"] = torch.zeros(256, 32, dtype=torch.bfloat16)            # tied model, and not the embedding's shape
     t["something.else"] = torch.zeros(1)
     st_save(t, os.path.join(folder, "model.safetensors"))
     with pytest.raises(WeightsError) as info:
@@ -85,6 +85,21 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     for needle in ("missing tensors (2)", "unexpected tensors (2)", "wrong shapes (1)", "expected (64, 64), file has (64, 63)"):
         assert needle in text
     compare({"a": (1,)}, {"a": (1,), "skip.me": (2,)}, [r"skip\..*"], "x")        # ignore patterns
+
+
+def test_tied_checkpoint_that_also_stores_the_head_is_accepted(tmp_path, capsys):
+    """Some exporters write lm_head.weight beside a tied embedding. With the embedding's shape it is
+    skipped and reported (the reference reports and goes on, src/loader.py:147-151)."""
+    folder = str(tmp_path / "m")
+    write_random_model(plain.TINY_A, folder, seed=0)
+    from safetensors.torch import load_file, save_file as st_save
+    t = load_file(os.path.join(folder, "model.safetensors"))
+    t["lm_head.weight"] = t["model.embed_tokens.weight"].clone()
+    st_save(t, os.path.join(folder, "model.safetensors"))
+    model, _ = build_model(folder, torch.float32, "cpu")
+    assert model.load_report["skipped"] == ["lm_head.weight"]
+    assert model.head.weight.data_ptr() == model.embedding.data_ptr()
+    assert "lm_head.weight is not read" in capsys.readouterr().err
 
 
 def test_precision_policy():
