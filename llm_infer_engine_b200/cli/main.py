@@ -6,7 +6,8 @@ Differences that follow from this library's design: model sizes come from config
 in --model, or in --tokenizer as the reference does, main.py:374); the size flags --dim,
 --n-layers, ... are read only in random-weights mode when there is no config.json;
 --quantization is not offered; --dtype chooses the bfloat16 or the true float32 path;
---prompt-ids runs without a tokenizer.
+--prompt-ids and --prompt-ids-file run without a tokenizer; --init-std sets the spread of random
+weights; stop ids come from config.json, generation_config.json and the tokenizer together.
 """
 from __future__ import annotations
 
@@ -28,12 +29,15 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--prompt", type=str, default=None, help="Input prompt")
     p.add_argument("--prompt-file", type=str, default=None, help="Path to a UTF-8 text file used as input prompt")
     p.add_argument("--prompt-ids", type=str, default=None, help="Prompt as comma-separated token ids (no tokenizer)")
+    p.add_argument("--prompt-ids-file", type=str, default=None,
+                   help="File of token ids separated by commas or white space (no tokenizer)")
     p.add_argument("--system-prompt", type=str, default=None, help="System prompt for chat template")
     p.add_argument("--max-new-tokens", type=int, default=None, help="Maximum generated tokens")
     p.add_argument("--temperature", type=float, default=None, help="Sampling temperature (<= 0: greedy)")
     p.add_argument("--top-p", type=float, default=None, help="Nucleus sampling threshold")
     p.add_argument("--device", type=str, default=None, help="CUDA device, e.g. cuda, cuda:0 or 0")
     p.add_argument("--seed", type=int, default=None, help="Random seed (sampling and random weights)")
+    p.add_argument("--init-std", type=float, default=None, help="Standard deviation of random weights, default 0.02")
     p.add_argument("--dim", type=int, default=None)
     p.add_argument("--n-layers", type=int, default=None)
     p.add_argument("--n-heads", type=int, default=None)
@@ -44,70 +48,73 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--max-batch", type=int, default=None, help="Sequences held at once")
     p.add_argument("--cuda-graph", type=str, default=None, choices=["on", "off"], help="CUDA Graph for decode")
     p.add_argument("--dtype", type=str, default=None, choices=["bfloat16", "float32"])
+    p.add_argument("--nvtx", action="store_true", help="Mark the stages of every step with NVTX ranges")
     return p
 
 
 def parse_env_file(env_file: Optional[str]) -> dict:
-    """KEY=VALUE lines; `export KEY=VALUE`, quotes and # comments are accepted (main.py:46-70)."""
-    if not env_file:
+    """The settings of a .env file as a dict of strings. One `KEY=VALUE` a line; a leading `export`, one pair
+    of quotes round the value and `#` comment lines are taken, anything else is passed over; a file that is
+    not there gives no settings (the format the reference reads, main.py:46-70)."""
+    try:
+        text = Path(env_file).read_text(encoding="utf-8") if env_file else ""
+    except OSError:
         return {}
-    path = Path(env_file)
-    if not path.is_file():
-        return {}
-    out = {}
-    for raw in path.read_text(encoding="utf-8").splitlines():
-        line = raw.strip()
-        if not line or line.startswith("#"):
+    settings = {}
+    for body in (line.strip() for line in text.splitlines()):
+        if body.startswith("#"):
             continue
-        if line.startswith("export "):
-            line = line[len("export "):].strip()
-        if "=" not in line:
+        if body.startswith("export "):
+            body = body[7:].lstrip()
+        key, eq, value = body.partition("=")
+        if not eq:
             continue
-        key, value = line.split("=", 1)
         value = value.strip()
-        if len(value) >= 2 and value[0] == value[-1] and value[0] in "\"'":
+        if len(value) > 1 and value[0] in "'\"" and value[-1] == value[0]:
             value = value[1:-1]
-        out[key.strip()] = value
-    return out
+        settings[key.strip()] = value
+    return settings
+
+
+# option -> (environment name, default, type). The environment names and the defaults are the reference's
+# (main.py:89-121) where it has the option; an empty setting counts as not given.
+OPTIONS = {
+    "model": ("LLM_MODEL", None, str), "tokenizer": ("LLM_TOKENIZER", None, str), "weights": ("LLM_WEIGHTS", "", str),
+    "prompt": ("LLM_PROMPT", None, str), "prompt_file": ("LLM_PROMPT_FILE", None, str),
+    "prompt_ids": ("LLM_PROMPT_IDS", None, str), "prompt_ids_file": ("LLM_PROMPT_IDS_FILE", None, str),
+    "system_prompt": ("LLM_SYSTEM_PROMPT", "You are a helpful assistant.", str),
+    "max_new_tokens": ("LLM_MAX_NEW_TOKENS", 256, int), "temperature": ("LLM_TEMPERATURE", 0.0, float),
+    "top_p": ("LLM_TOP_P", 1.0, float), "cuda_graph": ("LLM_CUDA_GRAPH", "on", str), "device": ("LLM_DEVICE", "cuda", str),
+    "seed": ("LLM_SEED", None, int), "init_std": ("LLM_INIT_STD", 0.02, float), "dim": ("LLM_DIM", None, int),
+    "n_layers": ("LLM_N_LAYERS", None, int), "n_heads": ("LLM_N_HEADS", None, int),
+    "n_kv_heads": ("LLM_N_KV_HEADS", None, int), "hidden_dim": ("LLM_HIDDEN_DIM", None, int),
+    "vocab_size": ("LLM_VOCAB_SIZE", None, int), "max_seq_len": ("LLM_MAX_SEQ_LEN", 4096, int),
+    "max_batch": ("LLM_MAX_BATCH", 1, int), "dtype": ("LLM_DTYPE", "bfloat16", str),
+}
 
 
 def resolve(cli_value, env_key: str, env_file: dict, default, cast):
+    """One option from its sources, the nearest first: command line, .env file, environment, default."""
     if cli_value is not None:
         return cli_value
-    raw = env_file.get(env_key)
-    if raw is None:
-        raw = os.environ.get(env_key)
-    if raw is None or raw == "":
-        return default
-    return raw if cast is str else cast(raw)
+    text = env_file[env_key] if env_key in env_file else os.environ.get(env_key)
+    return default if text in (None, "") else cast(text)
 
 
 def resolve_all(args, env_file: dict) -> dict:
-    r = lambda v, k, d, c: resolve(v, k, env_file, d, c)   # noqa: E731
-    return {
-        "model": r(args.model, "LLM_MODEL", None, str),
-        "tokenizer": r(args.tokenizer, "LLM_TOKENIZER", None, str),
-        "weights": r(args.weights, "LLM_WEIGHTS", "", str),
-        "prompt": r(args.prompt, "LLM_PROMPT", None, str),
-        "prompt_file": r(args.prompt_file, "LLM_PROMPT_FILE", None, str),
-        "prompt_ids": r(args.prompt_ids, "LLM_PROMPT_IDS", None, str),
-        "system_prompt": r(args.system_prompt, "LLM_SYSTEM_PROMPT", "You are a helpful assistant.", str),
-        "max_new_tokens": r(args.max_new_tokens, "LLM_MAX_NEW_TOKENS", 256, int),
-        "temperature": r(args.temperature, "LLM_TEMPERATURE", 0.0, float),
-        "top_p": r(args.top_p, "LLM_TOP_P", 1.0, float),
-        "cuda_graph": r(args.cuda_graph, "LLM_CUDA_GRAPH", "on", str),
-        "device": r(args.device, "LLM_DEVICE", "cuda", str),
-        "seed": r(args.seed, "LLM_SEED", None, int),
-        "dim": r(args.dim, "LLM_DIM", None, int),
-        "n_layers": r(args.n_layers, "LLM_N_LAYERS", None, int),
-        "n_heads": r(args.n_heads, "LLM_N_HEADS", None, int),
-        "n_kv_heads": r(args.n_kv_heads, "LLM_N_KV_HEADS", None, int),
-        "hidden_dim": r(args.hidden_dim, "LLM_HIDDEN_DIM", None, int),
-        "vocab_size": r(args.vocab_size, "LLM_VOCAB_SIZE", None, int),
-        "max_seq_len": r(args.max_seq_len, "LLM_MAX_SEQ_LEN", 4096, int),
-        "max_batch": r(args.max_batch, "LLM_MAX_BATCH", 1, int),
-        "dtype": r(args.dtype, "LLM_DTYPE", "bfloat16", str),
-    }
+    return {name: resolve(getattr(args, name), key, env_file, default, cast)
+            for name, (key, default, cast) in OPTIONS.items()}
+
+
+def read_ids_file(path: str) -> str:
+    """Token ids from a file, separated by commas or white space, as the comma-separated text of --prompt-ids."""
+    words = Path(path).expanduser().read_text(encoding="utf-8").replace(",", " ").split()
+    if not words:
+        raise ValueError(f"{path} holds no token ids")
+    bad = [w for w in words if not w.isdigit()]
+    if bad:
+        raise ValueError(f"{path}: {bad[0]!r} is not a token id")
+    return ",".join(words)
 
 
 def device_index(text: str) -> int:
@@ -163,7 +170,7 @@ def prepare_model_folder(opts: dict, log=print) -> str:
         config_json = config_from_flags(opts)
     folder = scratch_folder("llmie_random_")
     t0 = time.time()
-    write_random_model(config_json, folder, seed=opts["seed"] or 0)
+    write_random_model(config_json, folder, seed=opts["seed"] or 0, std=opts["init_std"])
     log(f"    Random init: {time.time() - t0:.4f}s")
     return folder
 
@@ -206,8 +213,13 @@ def main(argv: Optional[List[str]] = None) -> int:
         opts["prompt"] = path.read_text(encoding="utf-8")
         if not opts["prompt"].strip():
             parser.error(f"Prompt file is empty: {path}")
+    if opts["prompt_ids_file"] and not opts["prompt_ids"]:
+        try:
+            opts["prompt_ids"] = read_ids_file(opts["prompt_ids_file"])
+        except (OSError, ValueError) as e:
+            parser.error(f"--prompt-ids-file: {e}")
     if not opts["prompt"] and not opts["prompt_ids"]:
-        parser.error("Missing prompt. Provide --prompt, --prompt-file or --prompt-ids (or LLM_PROMPT).")
+        parser.error("Missing prompt. Provide --prompt, --prompt-file, --prompt-ids or --prompt-ids-file (or LLM_PROMPT).")
     tokenizer_dir = opts["tokenizer"] or opts["model"]
     if opts["prompt"] and not opts["prompt_ids"] and not tokenizer_dir:
         parser.error("Missing tokenizer. Provide --tokenizer or --model, or give the prompt as --prompt-ids.")
@@ -242,7 +254,7 @@ def main(argv: Optional[List[str]] = None) -> int:
         parser.error(str(e))
     t0 = time.time()
     engine = Engine(folder, dtype=opts["dtype"], device=device, max_batch=opts["max_batch"],
-                    max_seq_len=opts["max_seq_len"], cuda_graph=opts["cuda_graph"] == "on")
+                    max_seq_len=opts["max_seq_len"], cuda_graph=opts["cuda_graph"] == "on", nvtx=args.nvtx)
     report = engine.model.load_report
     print(f"    Model: loaded={report['tensors']} tensors, {report['bytes'] / 1e9:.3f} GB in {time.time() - t0:.4f}s")
 

@@ -64,9 +64,41 @@ def read_config_json(model_dir: str) -> dict:
     return data
 
 
+def _id_list(value, where: str):
+    if value is None:
+        return []
+    ids = [value] if isinstance(value, int) and not isinstance(value, bool) else value
+    if not isinstance(ids, (list, tuple)) or not all(isinstance(e, int) and not isinstance(e, bool) for e in ids):
+        raise ConfigError(f"{where}: eos_token_id must be an integer or a list of integers, got {value!r}")
+    return list(ids)
+
+
+def merge_generation_config(config_json: dict, model_dir: str) -> dict:
+    """Checkpoints keep the ids at which generation stops in two places: `eos_token_id` of config.json and of
+    generation_config.json (often a longer list there). Both are taken: the union, config.json's first."""
+    path = os.path.join(model_dir, "generation_config.json")
+    if not os.path.isfile(path):
+        return config_json
+    try:
+        with open(path, "r", encoding="utf-8") as f:
+            gen = json.load(f)
+    except json.JSONDecodeError as e:
+        raise ConfigError(f"{path}: not valid JSON ({e})") from e
+    if not isinstance(gen, dict):
+        raise ConfigError(f"{path}: top level must be an object")
+    ids = _id_list(config_json.get("eos_token_id"), "config.json")
+    ids += [e for e in _id_list(gen.get("eos_token_id"), "generation_config.json") if e not in ids]
+    if ids:
+        config_json = dict(config_json, eos_token_id=ids if len(ids) > 1 else ids[0])
+    return config_json
+
+
 def load_config(source):
-    """`source` is a model folder or an already parsed config.json dict.
-    Returns (architecture, typed config)."""
-    config_json = read_config_json(source) if isinstance(source, (str, os.PathLike)) else dict(source)
+    """`source` is a model folder (config.json, and generation_config.json for further stop ids if it is
+    there) or an already parsed config.json dict. Returns (architecture, typed config)."""
+    if isinstance(source, (str, os.PathLike)):
+        config_json = merge_generation_config(read_config_json(source), source)
+    else:
+        config_json = dict(source)
     arch = architecture_of(config_json)
     return arch, arch.config_cls.from_dict(config_json)

@@ -97,7 +97,8 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 // earlier kernel wrote (the wait returns when all earlier kernels have completed and their
 // writes are visible). What a kernel does before pdl_wait() - index arithmetic, loads of
 // weights that no kernel writes - overlaps the previous kernel's tail. Both calls are no-ops
-// in a kernel launched the ordinary way. LLMIE_PDL=0 in the environment turns the attribute off.
+// in a kernel launched the ordinary way. llmie_set_pdl(0) turns the attribute off for this library's launches
+// (each kernel library has its own copy of the switch).
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
@@ -108,14 +109,8 @@ __device__ __forceinline__ void l2_prefetch(const void* p, unsigned bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 
-static inline bool pdl_enabled() {
-  static int on = -1;
-  if (on < 0) {
-    const char* e = getenv("LLMIE_PDL");
-    on = (e && e[0] == '0') ? 0 : 1;
-  }
-  return on != 0;
-}
+static int g_pdl_on = 1;      // per library; llmie_set_pdl changes it
+static inline bool pdl_enabled() { return g_pdl_on != 0; }
 
 template <typename... KArgs, typename... Args>
 static inline void launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
@@ -134,4 +129,28 @@ static inline void launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
   cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);   // errors surface in cudaGetLastError()
 }
 
+// The same for a kernel whose blocks form thread-block clusters of `cluster_x` along x (grid.x a multiple of it).
+template <typename... KArgs, typename... Args>
+static inline void launch_k_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    unsigned cluster_x, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster_x;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace llmie
+
+// Programmatic dependent launch on (1, the default) or off (0) for every launch of this library.
+extern "C" void llmie_set_pdl(int on) { llmie::g_pdl_on = on ? 1 : 0; }

@@ -163,11 +163,24 @@ argmax_partial_kernel(const float* __restrict__ logits, int ld, int V, int slice
   pdl_wait();
   __shared__ MaxIdx scratch[32];
   const int s = blockIdx.x, r = blockIdx.y;
-  const int chunk = (V + slices - 1) / slices;
+  const int chunk = ((V + slices - 1) / slices + 3) & ~3;      // whole groups of four, so that slices stay aligned
   const int begin = min(V, s * chunk), end = min(V, begin + chunk);
   const float* row = logits + (size_t)r * ld;
   MaxIdx best{-INFINITY, 0x7fffffff};
-  for (int i = begin + threadIdx.x; i < end; i += blockDim.x) best = better(best, MaxIdx{row[i], i});
+  if ((ld & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15u) == 0) {
+    // 16-byte loads; within a thread and between threads the lowest index still wins a tie
+    const int end4 = begin + ((end - begin) & ~3);
+    for (int i = begin + 4 * threadIdx.x; i < end4; i += 4 * blockDim.x) {
+      const float4 q = *reinterpret_cast<const float4*>(row + i);
+      best = better(best, MaxIdx{q.x, i});
+      best = better(best, MaxIdx{q.y, i + 1});
+      best = better(best, MaxIdx{q.z, i + 2});
+      best = better(best, MaxIdx{q.w, i + 3});
+    }
+    for (int i = end4 + threadIdx.x; i < end; i += blockDim.x) best = better(best, MaxIdx{row[i], i});
+  } else {
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) best = better(best, MaxIdx{row[i], i});
+  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     MaxIdx other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};

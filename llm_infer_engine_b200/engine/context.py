@@ -40,6 +40,7 @@ class StepContext:
     device: torch.device
     kernels: Optional[object] = None     # the engine's kernel choices (KernelPlan)
     all_rows: bool = False               # logit_rows is 0..n_tokens-1: every row's logits are wanted
+    entry: int = 0                       # which entry of the run order is running (set by the model, for traces)
 
     def attention(self, q, kv, out, n_q: int, n_kv: int, head_dim: int, options: AttentionOptions) -> None:
         """softmax(q k^T * scale) v over the cache unit `kv`, each token seeing the keys of its own

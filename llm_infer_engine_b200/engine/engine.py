@@ -21,11 +21,14 @@ import numpy as np
 import torch
 
 from ..cache.cache import Cache
-from ..kernels import ops
+from ..kernels import ops, trace
 from ..weights.loader import build_model
 from .context import StepContext
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+DEFAULT_MAX_SEQ_LEN = 4096
 
 
 class EngineError(RuntimeError):
@@ -71,10 +74,14 @@ def _flatten_tokens(tokens, lens) -> np.ndarray:
 class Engine:
     def __init__(self, model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16", device: Union[str, int] = 0,
                  max_batch: int = 8, max_seq_len: Optional[int] = None, max_tokens: Optional[int] = None,
-                 cuda_graph: bool = True):
-        """max_batch: sequences held at once (slots). max_seq_len: longest sequence (default and
-        upper bound: the model's max_position_embeddings). max_tokens: positions all live sequences
-        may hold together, in whole pages of 64 (default: max_batch * max_seq_len)."""
+                 cuda_graph: bool = True, nvtx: bool = False, decode_attention: str = "auto"):
+        """max_batch: sequences held at once (slots). max_seq_len: longest sequence; the upper bound is the
+        model's max_position_embeddings, the default is that bound but at most DEFAULT_MAX_SEQ_LEN (4096, the
+        reference's default, main.py:40): a real checkpoint allows 131,072 positions, and a cache sized for
+        that by default would take tens of gigabytes. max_tokens: positions all live sequences may hold
+        together, in whole pages of 64 (default: max_batch * max_seq_len). nvtx: mark the stages of every
+        step with NVTX ranges under the reference's names. decode_attention: "auto", or "split" to keep
+        the CUDA-core split-KV kernel for every one-token step (for comparisons)."""
         if not torch.cuda.is_available():
             raise EngineError("no CUDA device: this library runs on a GPU only (there is no CPU path)")
         self.device = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
@@ -82,7 +89,13 @@ class Engine:
             raise EngineError(f"device {device!r} is not a CUDA device")
         torch.cuda.set_device(self.device)
         self.dtype = resolve_dtype(dtype)
-        self.model, self.config = build_model(model_dir, self.dtype, self.device, max_seq_len)
+        if decode_attention not in ("auto", "split"):
+            raise EngineError(f"decode_attention must be 'auto' or 'split', got {decode_attention!r}")
+        self.decode_attention = decode_attention
+        if nvtx:
+            trace.enable_ranges(True)
+        self.model, self.config = build_model(model_dir, self.dtype, self.device,
+                                              DEFAULT_MAX_SEQ_LEN if max_seq_len is None else max_seq_len)
         self.max_seq_len = self.model.runtime.max_positions
         self.max_batch = int(max_batch)
         page = 64
@@ -151,7 +164,8 @@ class Engine:
             start = cache.lengths[s]
             if start + l > self.max_seq_len:
                 raise EngineError(f"step: slot {s} would hold {start + l} tokens, more than max_seq_len "
-                                  f"{self.max_seq_len}")
+                                  f"{self.max_seq_len} (an Engine argument; its default is the model's limit, "
+                                  f"capped at {DEFAULT_MAX_SEQ_LEN})")
             starts.append(start)
         for s, st, l in zip(slots, starts, lens):
             cache.reserve(s, st + l)
@@ -202,7 +216,12 @@ class Engine:
             tokens=view[0], tok_pos=view[1], tok_seq=view[2], cu_q=view[3], seq_slot=view[4], seq_start=view[5],
             seq_kvlen=view[6], logit_rows=view[7], dtype=self.dtype, device=self.device, kernels=self.kernels,
             all_rows=R == T and rows == list(range(T)))
+        if trace.timer is not None:      # the per-kernel timer counts attention work from the real lengths
+            ops.STEP_HINT["kv_total"] = sum(kvlen)
+            ops.STEP_HINT["pairs"] = sum(l * (st + (l + 1) / 2.0) for st, l in zip(starts, lens))
+        trace.push("ModelForward")
         logits = self.model.forward(ctx, cache)
+        trace.pop()
         ops.advance_lengths(ctx.seq_slot, ctx.seq_kvlen, cache.seq_lens, n, cache.scratch_slot)
         for s, new_len in zip(slots, kvlen):
             cache.note_appended(s, new_len, device_updated=True)

@@ -16,7 +16,7 @@ from typing import Callable, List, Optional, Sequence
 
 import torch
 
-from ..kernels import ops
+from ..kernels import ops, trace
 from ..sampling.sampler import SamplingParams
 from .engine import Engine, EngineError, bucket_for
 
@@ -106,6 +106,7 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
         t0 = torch.cuda.Event(enable_timing=True)
         t1 = torch.cuda.Event(enable_timing=True)
         t0.record()
+        trace.push("Prefill")
         logits = engine.step(slots, [prompts[r] for r in batch], "last")
         n = len(batch)
         sampled = torch.empty(n, dtype=torch.int32, device=dev)
@@ -113,6 +114,7 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
         counters = torch.zeros(n, dtype=torch.int32, device=dev)
         ops.sample(logits, sampled, sampling.temperature, sampling.top_p, sampling.seed, seq_ids, counters)
         host_tokens[:n].copy_(sampled, non_blocking=True)
+        trace.pop()
         t1.record()
         t1.synchronize()
         stats.prefill_tokens += sum(len(prompts[r]) for r in batch)
@@ -122,6 +124,7 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
         d0 = torch.cuda.Event(enable_timing=True)
         d1 = torch.cuda.Event(enable_timing=True)
         d0.record()
+        trace.push("Decode")
         graph = None
         host_view = host_tokens.numpy()              # the same pinned memory, without tensor overheads
         stream = torch.cuda.current_stream()
@@ -208,6 +211,7 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
                 new = host_view[:n].tolist()
             stats.decode_steps += 1
             stats.decode_tokens += n
+        trace.pop()
         d1.record()
         d1.synchronize()
         stats.decode_seconds += d0.elapsed_time(d1) / 1e3

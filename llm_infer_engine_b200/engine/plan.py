@@ -4,8 +4,6 @@ in which case the caller falls back to the plain kernel of the same math (never 
 library path)."""
 from __future__ import annotations
 
-import os
-
 import torch
 
 from ..kernels import ops
@@ -19,8 +17,7 @@ class KernelPlan:
         self.bf16 = engine.dtype == torch.bfloat16
         self._counters = None          # zeroed once; the decode attention kernel leaves them zero
         self._retired = []             # outgrown counter tensors that captured steps may still point to
-        # LLMIE_DECODE_ATTN=split keeps the CUDA-core split-KV kernel for every one-token step (for comparisons)
-        self.decode_attention = os.environ.get("LLMIE_DECODE_ATTN", "auto")
+        self.decode_attention = engine.decode_attention      # "auto", or "split": always the CUDA-core kernel
 
     def _decode_counters(self, need: int, device) -> torch.Tensor:
         """Zeroed counters for the merge of a decode attention launch. A captured step keeps the address

@@ -36,6 +36,7 @@ FAMILIES: Dict[str, tuple] = {
     "gemm_simt": ("gemm_simt.cu", [], []),
     "gemm_skinny": ("gemm_skinny.cu", [], []),
     "gemm_tc": ("gemm_tc.cu", [], []),
+    "gemm_stream": ("gemm_stream.cu", [], []),
     "gemm_fused_decode": ("gemm_fused_decode.cu", [], []),
     "sampling": ("sampling.cu", [], []),
 }

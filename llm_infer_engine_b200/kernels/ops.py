@@ -9,12 +9,11 @@ raises.
 from __future__ import annotations
 
 import ctypes
-import os
 from typing import Optional
 
 import torch
 
-from . import build
+from . import build, trace
 
 _c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 _ERRORS = {-1: "bad argument", -2: "size not supported by this kernel", -3: "pointer not aligned",
@@ -29,16 +28,77 @@ class KernelError(RuntimeError):
     pass
 
 
-def _fn(family: str, name: str, argtypes):
+PDL = True        # programmatic dependent launch between this library's kernels (see csrc/common.cuh)
+
+
+def set_pdl(on: bool) -> None:
+    """Turns programmatic dependent launch on or off for every kernel library, loaded or yet to be."""
+    global PDL
+    PDL = bool(on)
+    for family in list(_pdl_state):
+        _apply_pdl(family)
+
+
+_pdl_state = {}
+
+
+def _apply_pdl(family: str) -> None:
+    if _pdl_state.get(family) != PDL:
+        lib = build.load(family)
+        lib.llmie_set_pdl.argtypes = [_c_int]
+        lib.llmie_set_pdl.restype = None
+        lib.llmie_set_pdl(1 if PDL else 0)
+        _pdl_state[family] = PDL
+
+
+def _fn(family: str, name: str, argtypes, query: bool = False):
+    """The exported function `name` of a kernel family. `query=True` marks a host-side question (no launch),
+    which the per-kernel timer leaves alone."""
     key = (family, name)
     f = _fn_cache.get(key)
     if f is None:
         lib = build.load(family)
-        f = getattr(lib, name)
-        f.argtypes = argtypes
-        f.restype = _c_int
+        raw = getattr(lib, name)
+        raw.argtypes = argtypes
+        raw.restype = _c_int
+        _apply_pdl(family)
+        short = name[6:] if name.startswith("llmie_") else name
+        if query:
+            _fn_cache[key] = raw
+            return raw
+
+        def f(*args, _raw=raw, _name=short):
+            t = trace.timer
+            return _raw(*args) if t is None else t.run(_name, _raw, args)
+
         _fn_cache[key] = f
     return f
+
+
+def _work(nbytes: float = 0.0, flops: float = 0.0) -> None:
+    """Tells an installed per-kernel timer what the next launch moves and computes."""
+    if trace.timer is not None:
+        trace.timer.note(nbytes, flops)
+
+
+def _nbytes(*tensors) -> int:
+    return sum(t.numel() * t.element_size() for t in tensors if t is not None)
+
+
+def library_mm(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """x [T, K] @ w[N, K]^T through the library GEMM (cuBLAS), for the products the reference leaves to
+    nn.Linear; seen by the per-kernel timer like this library's own launches."""
+    def run():
+        if out_dtype == x.dtype:
+            return torch.mm(x, w.t())
+        return torch.mm(x, w.t(), out_dtype=out_dtype)
+    t = trace.timer
+    if t is None:
+        return run()
+    T, K = x.shape
+    N = w.shape[0]
+    t.note(_nbytes(x, w) + T * N * (2 if out_dtype == torch.bfloat16 else 4), 2.0 * T * N * K)
+    return t.run("library_mm", run, ())
 
 
 LAUNCHES = 0      # kernels of this library launched so far (captured launches count once, at capture)
@@ -95,6 +155,7 @@ def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> t
     _need(tokens, "tokens", torch.int32, (T,))
     _need(table, "table")
     _need(out, "out", torch.float32, (T, d))
+    _work(T * 4 + T * d * table.element_size() + _nbytes(out))
     f = _fn("elementwise", "llmie_embedding",
             [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
     _check(f(tokens.data_ptr(), table.data_ptr(), _dt(table, "table"), out.data_ptr(), T, d, V, _stream()),
@@ -117,6 +178,7 @@ def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
         _need(delta, "delta", out.dtype, (T, d))
     if rows is not None:
         _need(rows, "rows", torch.int32, (n_out,))
+    _work((2 * _nbytes(h) if rows is None else n_out * d * 4) + _nbytes(delta, out))
     f = _fn("elementwise", "llmie_add_rmsnorm",
             [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_int, _c_void_p])
     _check(f(h.data_ptr(), _ptr(delta), weight.data_ptr(), out.data_ptr(), _ptr(rows), n_out, d, float(eps),
@@ -138,6 +200,7 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     T, ff = out.shape
     _need(out, "out")
     _need(gate_up, "gate_up", out.dtype, (T, 2 * ff))
+    _work(_nbytes(gate_up, out))
     f = _fn("elementwise", "llmie_swiglu", [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
     _check(f(gate_up.data_ptr(), out.data_ptr(), T, ff, _dt(out, "out"), _stream()), "swiglu")
     return out
@@ -166,6 +229,7 @@ def rope_store(qkv, q_out, k_cache, v_cache, table, tok_pos, tok_seq, seq_slot, 
     if write_kv:
         _need(k_cache, "k_cache", qkv.dtype, (None, n_kv, page_size, head_dim))
         _need(v_cache, "v_cache", qkv.dtype, tuple(k_cache.shape))
+    _work(_nbytes(qkv, q_out) + (2 * T * n_kv * head_dim * qkv.element_size() if write_kv else 0))
     f = _fn("elementwise", "llmie_rope_store",
             [_c_void_p] * 9 + [_c_int] * 10 + [_c_void_p])
     _check(f(qkv.data_ptr(), q_out.data_ptr(), _ptr(k_cache) if write_kv else None,
@@ -188,6 +252,8 @@ def attention_paged(q, k_cache, v_cache, out, tok_pos, tok_seq, seq_slot, block_
         _need(t, name, torch.int32)
     if head_dim % 16 or head_dim > 256:
         raise KernelError(f"attention_paged: head_dim {head_dim} must be a multiple of 16 and at most 256")
+    _work(2 * _nbytes(q) + 2.0 * STEP_HINT["kv_total"] * n_kv * head_dim * q.element_size(),
+          4.0 * n_q * head_dim * STEP_HINT["pairs"])
     f = _fn("attention_simt", "llmie_attention_paged",
             [_c_void_p] * 8 + [_c_int] * 6 + [_c_float, _c_int, _c_int, _c_void_p])
     _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), tok_pos.data_ptr(),
@@ -256,6 +322,8 @@ def attention_decode(q, k_cache, v_cache, out, seq_slot, seq_kvlen, block_table,
         _need(counters, "counters", torch.int32)
         if counters.numel() < decode_counter_ints(n, n_q, n_kv):
             raise KernelError("attention_decode: too few counters")
+        _work(2 * _nbytes(q) + 2.0 * STEP_HINT["kv_total"] * n_kv * head_dim * q.element_size(),
+              4.0 * n_q * head_dim * STEP_HINT["pairs"])
         f = _fn("attention_decode", "llmie_attention_decode_fused",
                 [_c_void_p] * 11 + [_c_int] * 6 + [_c_float] + [_c_int] * 4 + [_c_void_p])
         _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), base, base + 4 * n_ml,
@@ -272,13 +340,18 @@ def attention_decode(q, k_cache, v_cache, out, seq_slot, seq_kvlen, block_table,
     return out
 
 
-MMA_MAX_BLOCKS = int(os.environ.get("LLMIE_MMA_MAX_BLOCKS", 148 * 2))
+# What a step's attention really reads is known to the caller, not to the launcher (which is sized for upper
+# bounds): when a per-kernel timer is installed the engine leaves here, for the timer's counts, the keys all
+# sequences of the step hold together and the (query, key) pairs the step's causal attention visits.
+STEP_HINT = {"kv_total": 0, "pairs": 0}
+
+MMA_MAX_BLOCKS = 148 * 2        # blocks the decode attention aims at: two per SM
 
 
 def attention_decode_mma_supported(head_dim: int, dtype: torch.dtype, page_size: int) -> bool:
     if dtype != torch.bfloat16:
         return False
-    f = _fn("attention_decode_mma", "llmie_attention_decode_mma_supported", [_c_int] * 3)
+    f = _fn("attention_decode_mma", "llmie_attention_decode_mma_supported", [_c_int] * 3, query=True)
     return bool(f(head_dim, _DT[dtype], page_size))
 
 
@@ -286,7 +359,7 @@ def attention_decode_mma_pages(n_seqs: int, n_q: int, n_kv: int, max_kv_len: int
                                max_blocks: Optional[int] = None) -> int:
     """Cache pages per block that attention_decode_mma wants for this step's shape."""
     groups = n_kv * ((n_q // n_kv + 15) // 16)
-    f = _fn("attention_decode_mma", "llmie_attention_decode_mma_pages", [_c_int] * 4)
+    f = _fn("attention_decode_mma", "llmie_attention_decode_mma_pages", [_c_int] * 4, query=True)
     return int(f(n_seqs, groups, max_kv_len, MMA_MAX_BLOCKS if max_blocks is None else max_blocks))
 
 
@@ -318,6 +391,7 @@ def attention_decode_mma(q, k_cache, v_cache, out, seq_slot, seq_kvlen, block_ta
             raise KernelError("attention_decode_mma: counters are needed when a sequence spans several runs")
         _need(counters, "counters", torch.int32)
         base, n_ml, cptr = scratch.data_ptr(), n * n_q * n_runs, counters.data_ptr()
+    _work(2 * _nbytes(q) + 2.0 * STEP_HINT["kv_total"] * n_kv * head_dim * 2, 4.0 * n_q * head_dim * STEP_HINT["pairs"])
     f = _fn("attention_decode_mma", "llmie_attention_decode_mma",
             [_c_void_p] * 11 + [_c_int] * 6 + [_c_float] + [_c_int] * 3 + [_c_void_p])
     _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), base or None,
@@ -336,6 +410,7 @@ def gemm_f32_nt(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = 
     if out is None:
         out = torch.empty((M, N), dtype=torch.float32, device=a.device)
     _need(out, "out", torch.float32, (M, N))
+    _work(_nbytes(a, w) + a.shape[0] * w.shape[0] * 4, 2.0 * a.shape[0] * w.shape[0] * w.shape[1])
     f = _fn("gemm_simt", "llmie_gemm_f32_nt", [_c_void_p] * 3 + [_c_int] * 6 + [_c_void_p])
     _check(f(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, K, K, N, _stream()), "gemm_f32_nt")
     return out
@@ -369,6 +444,7 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
     cols = N // 2 if epilogue == SKINNY_SWIGLU else N
     want = torch.float32 if epilogue in (SKINNY_STORE_F32, SKINNY_ADD_F32) else torch.bfloat16
     _need(out, "out", want, (batch, cols))
+    _work(_nbytes(x, w, out), 2.0 * x.shape[0] * w.shape[0] * w.shape[1])
     f = _fn("gemm_skinny", "llmie_gemm_skinny", [_c_void_p] * 3 + [_c_int] * 5 + [_c_void_p])
     _check(f(x.data_ptr(), w.data_ptr(), out.data_ptr(), batch, N, K, cols, epilogue, _stream()), "gemm_skinny")
     return out
@@ -397,6 +473,7 @@ def norm_gate_swiglu(h, norm_w, eps: float, w_gate_up, act):
     _need(act, "act", torch.bfloat16, (batch, ff))
     if w_gate_up.shape[0] % 2 or ff % 8:
         raise KernelError("norm_gate_swiglu: the feed-forward width must be a multiple of 8")
+    _work(_nbytes(h, w_gate_up, act), 2.0 * batch * w_gate_up.shape[0] * K)
     f = _fn("gemm_fused_decode", "llmie_norm_gate_swiglu",
             [_c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
     _check(f(h.data_ptr(), norm_w.data_ptr(), float(eps), w_gate_up.data_ptr(), act.data_ptr(), batch, ff, K,
@@ -411,6 +488,7 @@ def norm_gemm_f32(h, norm_w, eps: float, w, out):
     _need(out, "out", torch.float32, (batch, N))
     if N % 16:
         raise KernelError("norm_gemm_f32: N must be a multiple of 16")
+    _work(_nbytes(h, w, out), 2.0 * batch * w.shape[0] * K)
     f = _fn("gemm_fused_decode", "llmie_norm_gemm_f32",
             [_c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
     _check(f(h.data_ptr(), norm_w.data_ptr(), float(eps), w.data_ptr(), out.data_ptr(), batch, N, K, _stream()),
@@ -433,6 +511,7 @@ def norm_qkv_rope(h, norm_w, eps: float, w_qkv, q_out, k_cache, v_cache, table, 
     if write_kv:
         _need(k_cache, "k_cache", torch.bfloat16, (None, n_kv, page_size, head_dim))
         _need(v_cache, "v_cache", torch.bfloat16, tuple(k_cache.shape))
+    _work(_nbytes(h, w_qkv, q_out) + 2 * batch * n_kv * head_dim * 2, 2.0 * batch * w_qkv.shape[0] * K)
     f = _fn("gemm_fused_decode", "llmie_norm_qkv_rope",
             [_c_void_p, _c_void_p, _c_float] + [_c_void_p] * 9 + [_c_int] * 9 + [_c_void_p])
     _check(f(h.data_ptr(), norm_w.data_ptr(), float(eps), w_qkv.data_ptr(), q_out.data_ptr(),
@@ -498,6 +577,7 @@ def attention_prefill_tc(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, bl
         raise KernelError(f"attention_prefill_tc: head_dim {head_dim} / page size {page_size} is not supported")
     if cu_q.numel() < n_seqs + 1 or seq_slot.numel() < n_seqs or seq_start.numel() < n_seqs:
         raise KernelError("attention_prefill_tc: a per-sequence array is shorter than n_seqs")
+    _work(2 * _nbytes(q) + 2.0 * STEP_HINT["kv_total"] * n_kv * head_dim * 2, 4.0 * n_q * head_dim * STEP_HINT["pairs"])
     f = _fn("attention_prefill_tc", "llmie_attention_prefill_tc",
             [_c_void_p] * 8 + [_c_int] * 8 + [_c_float, _c_int, _c_void_p, _c_void_p])
     _check(f(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), cu_q.data_ptr(),
@@ -516,6 +596,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor
     _need(out, "out", None, (M, N))
     if K % 8 or N % 8:
         raise KernelError(f"gemm_tc: K ({K}) and N ({N}) must be multiples of 8")
+    _work(_nbytes(a, w, out), 2.0 * M * N * K)
     f = _fn("gemm_tc", "llmie_gemm_tc", [_c_void_p] * 3 + [_c_int] * 5 + [_c_void_p, _c_void_p])
     _check(f(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, N, _dt(out, "out"),
              tc_status_word(a.device).data_ptr(), _stream()), "gemm_tc")
@@ -525,6 +606,58 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor
 _argmax_parts = {}
 
 
+STREAM_STORE_BF16, STREAM_STORE_F32, STREAM_ADD_F32 = 0, 1, 2
+STREAM_MAX_ROWS = 64
+_sm_count = {}
+
+
+def _sms(device) -> int:
+    key = torch.device(device).index or 0
+    n = _sm_count.get(key)
+    if n is None:
+        n = torch.cuda.get_device_properties(key).multi_processor_count
+        _sm_count[key] = n
+    return n
+
+
+def gemm_stream_ok(rows: int, n: int, k: int) -> bool:
+    """Whether gemm_stream takes this shape: up to 64 rows, K a multiple of 8."""
+    return 0 < rows <= STREAM_MAX_ROWS and k % 8 == 0 and n > 0
+
+
+def gemm_stream_wins(rows: int, n: int, k: int) -> bool:
+    """Where gemm_stream beat the library GEMM when measured on a B200 (captured launches, weights rotated through
+    more than the L2 holds): only very tall matrices at 33 to 64 rows (a 128,256 x 2,048 head: 84 us against
+    92 us). From 9 to 32 rows and for the layer matrices (2,048 to 28,672 rows of weights) the library is equal
+    or faster (qkv 6 us against 9-12 us, down 13 us against 13-18 us), so those stay with it."""
+    return 32 < rows <= STREAM_MAX_ROWS and k % 8 == 0 and n * k >= 128 * 1024 * 1024
+
+
+def gemm_stream(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STREAM_STORE_BF16,
+                splits: int = 0) -> torch.Tensor:
+    """out = x @ w^T (mode STREAM_STORE_BF16 / STREAM_STORE_F32) or out += x @ w^T (STREAM_ADD_F32, out float32)
+    for up to 64 rows of x, on the tcgen05 tensor cores with the weights as the streamed operand. x [M, K] and
+    w [N, K] bfloat16. Needs no workspace: slices of K meet in the shared memory of a thread-block cluster.
+    splits: 0 = the launcher chooses into how many slices K is cut; 1, 2, 4 or 8 fixes it."""
+    M, K = x.shape
+    N = w.shape[0]
+    _need(x, "x", torch.bfloat16)
+    _need(w, "w", torch.bfloat16, (N, K))
+    _need(out, "out", torch.bfloat16 if mode == STREAM_STORE_BF16 else torch.float32, (M, N))
+    if not gemm_stream_ok(M, N, K):
+        raise KernelError(f"gemm_stream: {M} rows x K {K} is not supported (up to {STREAM_MAX_ROWS} rows, K % 8 == 0)")
+    _work(_nbytes(x, w, out) + (_nbytes(out) if mode == STREAM_ADD_F32 else 0), 2.0 * M * N * K)
+    f = _fn("gemm_stream", "llmie_gemm_stream", [_c_void_p] * 3 + [_c_int] * 6 + [_c_void_p, _c_void_p])
+    _check(f(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, int(mode), _sms(x.device), int(splits),
+             tc_status_word(x.device).data_ptr(), _stream()), "gemm_stream")
+    return out
+
+
+def _check_query(status: int, name: str) -> None:
+    if status != 0:
+        raise KernelError(f"{name}: {_ERRORS.get(status, 'error ' + str(status))}")
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """Greedy token per row of float32 logits [R, V] (lowest index wins a tie), many blocks per row."""
     R, V = logits.shape
@@ -532,7 +665,7 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     _need(out, "out", torch.int32)
     if out.shape[0] < R:
         raise KernelError("argmax: out is shorter than the number of rows")
-    slices = max(1, min(128, V // 1024))
+    slices = max(1, min(128, V // 1024, max(8, 1184 // R)))     # about a thousand blocks, each with a few thousand logits
     key = (logits.device, R * slices)
     parts = _argmax_parts.get(key)
     if parts is None:        # kept: a generation loop calls this once per step (calls on one stream are ordered)
@@ -540,6 +673,7 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
                  torch.empty(R * slices, dtype=torch.int32, device=logits.device))
         _argmax_parts[key] = parts
     part_val, part_idx = parts
+    _work(R * V * 4)
     f = _fn("sampling", "llmie_argmax", [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p,
                                          _c_void_p])
     _check(f(logits.data_ptr(), R, V, logits.stride(0), slices, part_val.data_ptr(), part_idx.data_ptr(),
@@ -582,6 +716,7 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float = 0.0, to
         _need(counters, "counters", torch.int32)
         if seq_ids.shape[0] < R or counters.shape[0] < R:
             raise KernelError("sample: seq_ids / counters shorter than the number of rows")
+    _work(R * V * 4)
     f = _fn("sampling", "llmie_sample",
             [_c_void_p, _c_int, _c_int, _c_int, _c_float, _c_float, ctypes.c_ulonglong, _c_void_p, _c_void_p,
              _c_void_p, _c_void_p, _c_void_p])

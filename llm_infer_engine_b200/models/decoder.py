@@ -14,7 +14,7 @@ from typing import Dict, List, Tuple
 import torch
 
 from ..config.spec import ModelSpec
-from ..kernels import ops
+from ..kernels import ops, trace
 from ..parts.base import Block, ParamSpec, Part, Runtime, build_part, lookup
 from ..parts.linear import Linear
 
@@ -93,13 +93,19 @@ class DecoderModel:
     # ------------------------------------------------------------------ one step
     def forward(self, ctx, cache) -> torch.Tensor:
         h = torch.empty((ctx.n_tokens, self.hidden_size), dtype=torch.float32, device=self.runtime.device)
+        trace.push("Embed")
         ops.embedding(ctx.tokens, self.embedding, h)
         if self.after_embedding is not None:
             h = self.after_embedding.forward(h, ctx)
+        trace.pop()
         pending = None
+        trace.push("Layers")
         for pos, call in enumerate(self.spec.schedule):
             unit = cache.unit(self.unit_of_entry[pos])
+            ctx.entry = pos
             h, pending = self.blocks[call.layer].forward(h, pending, ctx, unit, call.cache_of is None)
+        trace.pop()
+        trace.push("Output")
         logits = None
         if pending is None and ctx.all_rows and self.head.weight.dtype == torch.bfloat16 \
                 and self.vocab_size % 16 == 0:
@@ -113,4 +119,5 @@ class DecoderModel:
             logits = self.head(x, out_dtype=torch.float32)
         if self.after_head is not None:
             logits = self.after_head.forward(logits, ctx, rows=ctx.logit_rows)
+        trace.pop()
         return logits

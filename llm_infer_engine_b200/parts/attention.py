@@ -13,7 +13,7 @@ from typing import Dict
 import torch
 
 from ..cache.cache import KVRequest
-from ..kernels import ops
+from ..kernels import ops, trace
 from .base import AttentionOptions, DeferredNorm, Mixer, ParamSpec, build_part, register_mixer
 from .linear import Linear
 
@@ -64,6 +64,7 @@ class GroupedQueryAttention(Mixer):
     def forward(self, x, ctx, unit, owns_cache, residual=None):
         kv = unit.kv
         q = None
+        trace.push("QKV_proj")
         if isinstance(x, DeferredNorm):
             table = getattr(self.position, "fused_table", lambda hd: None)(self.head_dim)
             w = self.qkv.weight
@@ -77,13 +78,20 @@ class GroupedQueryAttention(Mixer):
                 x = x.apply()
         if q is None:
             qkv = self.qkv(x)
+            trace.pop()
+            trace.push("RoPE+KV_cache")
             q = self.position.encode_and_store(qkv, ctx, kv, self.n_heads, self.n_kv_heads, self.head_dim,
                                                owns_cache)
+        trace.pop()
         out = torch.empty_like(q)
+        trace.push("FlashDecode" if ctx.decode else "FlashAttn")
         ctx.attention(q, kv, out, self.n_heads, self.n_kv_heads, self.head_dim, self.options)
-        if residual is not None and self.o.add_into(out, residual):
-            return None
-        return self.o(out)
+        trace.pop()
+        trace.push("Output_proj")
+        done = residual is not None and self.o.add_into(out, residual)
+        y = None if done else self.o(out)
+        trace.pop()
+        return y
 
 
 register_mixer("gqa_attention", GroupedQueryAttention)

@@ -3,6 +3,7 @@
 branch output travels to the next norm as `pending`."""
 from __future__ import annotations
 
+from ..kernels import trace
 from .base import Block, call_branch, register_block
 
 
@@ -13,18 +14,27 @@ class PreNormBlock(Block):
     ROLES = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm"}
 
     def forward(self, h, pending, ctx, unit, owns_cache):
+        tracing = trace.active()
+        if tracing:
+            trace.push(f"Attn_{ctx.entry}")           # the reference's range names (src/model.py:112,126)
         x = None
         if pending is None and self.mixer.accepts_deferred_norm:
             x = self.mixer_norm.defer(h)              # the mixer's first kernel applies the norm
         if x is None:
             x = self.mixer_norm.forward(h, pending)
         mixed = call_branch(self.mixer, x, ctx, unit, owns_cache, residual=h)
+        if tracing:
+            trace.pop()
+            trace.push(f"FFN_{ctx.entry}")
         x = None
         if mixed is None and self.feed_forward.accepts_deferred_norm:
             x = self.feed_forward_norm.defer(h)
         if x is None:
             x = self.feed_forward_norm.forward(h, mixed)
-        return h, call_branch(self.feed_forward, x, ctx, residual=h)
+        out = call_branch(self.feed_forward, x, ctx, residual=h)
+        if tracing:
+            trace.pop()
+        return h, out
 
 
 register_block("pre_norm", PreNormBlock)

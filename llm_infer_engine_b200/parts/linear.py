@@ -1,7 +1,9 @@
 """Matrix products y = x W^T of the parts (no bias), chosen by the weight's precision.
 
-bfloat16 weights: the library GEMM (cuBLAS through torch.mm), as the reference does with
-nn.Linear (src/model.py:17-19,34-37,137), accumulating in float32. float32 weights: this
+bfloat16 weights: up to 8 (16 with the add) rows this library's skinny kernel; above that the library
+GEMM (cuBLAS through torch.mm), as the reference does with nn.Linear (src/model.py:17-19,34-37,137),
+accumulating in float32, except where this library's weight-streaming tcgen05 kernel measured faster
+(`ops.gemm_stream_wins`: a vocabulary-sized head at 33 to 64 rows). float32 weights: this
 library's own FMA kernel, true 32-bit with a fixed summation order; that is the whole of
 the 32-bit path, and also what a bfloat16 engine does with a tensor that its checkpoint
 stores in 32-bit.
@@ -40,9 +42,11 @@ class Linear:
             f32 = out_dtype == torch.float32
             out = torch.empty((T, self.out_features), dtype=out_dtype, device=x.device)
             return ops.gemm_skinny(xb, w, out, ops.SKINNY_STORE_F32 if f32 else ops.SKINNY_STORE_BF16)
-        if out_dtype == torch.bfloat16:
-            return torch.mm(xb, w.t())
-        return torch.mm(xb, w.t(), out_dtype=torch.float32)
+        if ops.gemm_stream_wins(T, self.out_features, self.in_features):
+            out = torch.empty((T, self.out_features), dtype=out_dtype, device=x.device)
+            return ops.gemm_stream(xb, w, out, ops.STREAM_STORE_F32 if out_dtype == torch.float32
+                                   else ops.STREAM_STORE_BF16)
+        return ops.library_mm(xb, w, out_dtype)
 
     def add_into(self, x: torch.Tensor, h: torch.Tensor) -> bool:
         """h (float32 [T, out]) += x W^T inside the product's kernel, when a kernel for this shape

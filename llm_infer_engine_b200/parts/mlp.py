@@ -7,7 +7,7 @@ from typing import Dict
 
 import torch
 
-from ..kernels import ops
+from ..kernels import ops, trace
 from .base import DeferredNorm, FeedForward, ParamSpec, register_feed_forward
 from .linear import Linear
 
@@ -40,6 +40,13 @@ class SwiGLU(FeedForward):
         return self.gate_up.nbytes() + self.down.nbytes()
 
     def forward(self, x, ctx, residual=None):
+        trace.push("FFN")
+        try:
+            return self._forward(x, ctx, residual)
+        finally:
+            trace.pop()
+
+    def _forward(self, x, ctx, residual):
         act = None
         if isinstance(x, DeferredNorm):
             w = self.gate_up.weight

@@ -9,7 +9,7 @@ from typing import Dict, Optional
 
 import torch
 
-from ..kernels import ops
+from ..kernels import ops, trace
 from .base import DeferredNorm, Norm, ParamSpec, register_norm
 
 
@@ -41,7 +41,10 @@ class RMSNorm(Norm):
         n_out = h.shape[0] if rows is None else rows.shape[0]
         if out is None:
             out = torch.empty((n_out, self.size), dtype=self.runtime.dtype, device=h.device)
-        return ops.add_rmsnorm(h, delta, self.weight, self.eps, out, rows)
+        trace.push("RMSNorm")
+        ops.add_rmsnorm(h, delta, self.weight, self.eps, out, rows)
+        trace.pop()
+        return out
 
 
 register_norm("rmsnorm", RMSNorm)

@@ -66,3 +66,16 @@ def test_prepare_model_folder(tmp_path):
     assert os.path.isfile(os.path.join(folder, "model.safetensors"))
     with pytest.raises(FileNotFoundError):
         cli.prepare_model_folder(dict(base, tokenizer=str(tok), weights="/no/such/file"), log=lambda s: None)
+
+
+def test_prompt_ids_file_and_init_std(tmp_path):
+    ids = tmp_path / "ids.txt"
+    ids.write_text("5, 17 3\n9,\n")
+    assert cli.read_ids_file(str(ids)) == "5,17,3,9"
+    ids.write_text("5 x")
+    with pytest.raises(ValueError, match="not a token id"):
+        cli.read_ids_file(str(ids))
+    args = cli.build_parser().parse_args(["--init-std", "0.05", "--prompt-ids-file", str(ids)])
+    opts = cli.resolve_all(args, {})
+    assert opts["init_std"] == 0.05 and opts["prompt_ids_file"] == str(ids)
+    assert cli.resolve_all(cli.build_parser().parse_args([]), {})["init_std"] == 0.02

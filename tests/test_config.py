@@ -105,3 +105,19 @@ def test_spec_is_data():
     with pytest.raises(ValueError, match="earlier"):
         dataclasses.replace(spec, schedule=[LayerCall(0, cache_of=0)]).validate()
     dataclasses.replace(spec, schedule=[LayerCall(0), LayerCall(1, cache_of=0), LayerCall(0)]).validate()
+
+
+def test_generation_config_adds_stop_ids(tmp_path):
+    """Stop ids are the union of config.json's and generation_config.json's eos_token_id."""
+    import json
+    import plain_llama as plain
+    from llm_infer_engine_b200.config import load_config
+    (tmp_path / "config.json").write_text(json.dumps(dict(plain.TINY_A, eos_token_id=2)))
+    arch, cfg = load_config(str(tmp_path))
+    assert arch.to_spec(cfg).stop_token_ids == (2,)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [2, 7, 9], "temperature": 0.6}))
+    arch, cfg = load_config(str(tmp_path))
+    assert arch.to_spec(cfg).stop_token_ids == (2, 7, 9)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": "x"}))
+    with pytest.raises(Exception, match="generation_config.json: eos_token_id"):
+        load_config(str(tmp_path))

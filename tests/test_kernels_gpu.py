@@ -255,6 +255,18 @@ def test_argmax_ties_and_sizes():
         o.sample(logits.to(DEV), out)
         assert out.cpu().tolist() == [plain.greedy(r) for r in logits]
         assert out.cpu().tolist()[2] == 3
+    # many blocks per row: 16-byte loads (row length a multiple of 4) and plain ones (5003), few rows and many
+    # (the grid is cut differently), ties inside one 16-byte group, across groups and across slices
+    for V, R in ((4100, 3), (5003, 3), (128256, 64), (50000, 33)):
+        g = torch.Generator().manual_seed(V + R)
+        logits = torch.randn(R, V, generator=g)
+        logits[0, [V // 2 + 1, V // 2 + 2]] = 40.0
+        logits[1, [9, V - 2]] = 41.0
+        logits[2, [V // 3, V // 3 + 4]] = 42.0
+        out = torch.empty(R, dtype=torch.int32, device=DEV)
+        o.sample(logits.to(DEV), out)
+        assert out.cpu().tolist() == [plain.greedy(r) for r in logits]
+        assert out.cpu().tolist()[:3] == [V // 2 + 1, 9, V // 3]
 
 
 @pytest.mark.parametrize("top_p", [1.0, 0.9, 0.3, 0.0])
@@ -357,6 +369,47 @@ def test_gemm_tc(M, N, K):
     o.gemm_tc(a.to(DEV), w.to(DEV), out16)
     o.check_tc_status(DEV)
     assert torch.equal(out16.cpu(), out32.cpu().to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("M", [1, 9, 16, 17, 33, 64])
+@pytest.mark.parametrize("N,K,splits", [(3072, 2048, 0), (2048, 8192, 0), (2048, 2048, 8), (200, 520, 0), (1000, 72, 2),
+                                        (16384, 512, 0), (130, 4096, 4), (40000, 256, 1)])
+def test_gemm_stream(M, N, K, splits):
+    """The weight-streaming tcgen05 product for up to 64 rows: every store mode, K cut into 1 to 8 slices that meet in
+    the cluster's shared memory, widths and depths that are no multiples of the tiles (the TMA loads fill with zeros,
+    the stores are masked), clusters that take several tiles each, and twice in a row on the same output."""
+    o = ops()
+    g = torch.Generator().manual_seed(M * 7 + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    xd, wd = x.to(DEV), w.to(DEV)
+    out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    o.gemm_stream(xd, wd, out32, o.STREAM_STORE_F32, splits=splits)
+    o.check_tc_status(DEV)
+    err = float((out32.cpu().double() - ref).abs().max())
+    assert err < 1e-3, err
+    again = torch.full_like(out32, float("nan"))
+    o.gemm_stream(xd, wd, again, o.STREAM_STORE_F32, splits=splits)
+    assert torch.equal(again, out32)                    # slices are added in slice order: no run differs from another
+    out16 = torch.empty((M, N), dtype=torch.bfloat16, device=DEV)
+    o.gemm_stream(xd, wd, out16, o.STREAM_STORE_BF16, splits=splits)
+    assert torch.equal(out16.cpu(), out32.cpu().to(torch.bfloat16))
+    h = torch.randn(M, N, generator=g)
+    hd_ = h.to(DEV)
+    o.gemm_stream(xd, wd, hd_, o.STREAM_ADD_F32, splits=splits)
+    o.check_tc_status(DEV)
+    assert torch.equal(hd_.cpu(), h + out32.cpu())      # one rounding: h + (the float32 sum)
+
+
+def test_gemm_stream_refuses_what_it_cannot_take():
+    o = ops()
+    x = torch.zeros(65, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(128, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(o.KernelError, match="not supported"):
+        o.gemm_stream(x, w, torch.zeros(65, 128, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(o.KernelError, match="not supported"):
+        o.gemm_stream(x[:4, :60].contiguous(), w[:, :60].contiguous(), torch.zeros(4, 128, dtype=torch.bfloat16, device=DEV))
 
 
 def test_a_bounded_wait_that_runs_out_is_reported_and_leaves_the_device_usable():
