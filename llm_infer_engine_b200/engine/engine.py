@@ -108,6 +108,7 @@ class Engine:
         from .plan import KernelPlan
         self.kernels = KernelPlan(self)
         self._graphs: Dict[tuple, "DecodeGraph"] = {}
+        self._prefill_graphs: Dict[int, object] = {}        # prompt length -> False (seen once) or PrefillGraph
         self.launches = 0
         # a step's index arrays are written into pinned host memory and uploaded in one asynchronous copy
         self._staging_tensor = torch.empty(0, dtype=torch.int32)
@@ -206,6 +207,18 @@ class Engine:
             packed[offs[2]:offs[2] + T] = tok_seq
         for k, vals in ((3, cu), (4, slots), (5, starts), (6, kvlen), (7, rows)):
             packed[offs[k]:offs[k] + sizes[k]] = vals
+        # A lone prompt whose length has come before runs as a captured step (see PrefillGraph): no launch work
+        # on the host beyond one upload and one replay.
+        captured = None
+        if self.use_cuda_graph and n == 1 and want_last and T >= PrefillGraph.MIN_TOKENS and trace.timer is None:
+            captured = self._prefill_graph_for(T, offs, sizes)
+        if captured is not None and captured.graph is not None:
+            captured.meta.copy_(self._staging_tensor[:offs[-1]], non_blocking=True)
+            self._staging_done.record()
+            logits = captured.replay()
+            for s, new_len in zip(slots, kvlen):
+                cache.note_appended(s, new_len, device_updated=True)
+            return logits
         dev = torch.empty(offs[-1], dtype=torch.int32, device=self.device)
         dev.copy_(self._staging_tensor[:offs[-1]], non_blocking=True)
         self._staging_done.record()
@@ -225,7 +238,24 @@ class Engine:
         ops.advance_lengths(ctx.seq_slot, ctx.seq_kvlen, cache.seq_lens, n, cache.scratch_slot)
         for s, new_len in zip(slots, kvlen):
             cache.note_appended(s, new_len, device_updated=True)
+        if captured is not None:
+            captured.capture()               # this length came a second time: later steps of it are replays
         return logits
+
+    def _prefill_graph_for(self, T: int, offs, sizes) -> Optional["PrefillGraph"]:
+        """The captured lone-prompt step for prompts of T tokens: None at a length's first occurrence, an
+        uncaptured PrefillGraph at its second (the step still runs eagerly and captures afterwards), a ready one
+        from then on. The few most recently used lengths are kept."""
+        seen = self._prefill_graphs
+        entry = seen.pop(T, None)
+        if entry is None:
+            entry = False                     # seen once
+        elif entry is False:
+            entry = PrefillGraph(self, T, list(offs), list(sizes))
+        seen[T] = entry                       # most recently used last
+        while len(seen) > PrefillGraph.KEEP:
+            seen.pop(next(iter(seen)))
+        return entry or None
 
     # ---------------------------------------------------------------- captured one-token step
     def decode_graph(self, n_lanes: int, kv_len: Optional[int] = None, sampling=None,
@@ -283,6 +313,61 @@ def kv_bucket_for(kv_len: int, limit: int) -> int:
     while b < kv_len:
         b *= 2
     return min(b, limit)
+
+
+class PrefillGraph:
+    """The captured step of ONE prompt of T tokens whose last row's logits are wanted, at any start position
+    and in any slot: every index array of the step lives in one device buffer (`meta`, laid out as the eager
+    step's packed upload) that is filled before each replay, and every kernel of the step takes its positions,
+    slot and lengths from there. A prompt step is some 150 launches; replayed, the host's share of it is one
+    upload and one launch. Prompt lengths repeat where prompts are cut into pieces of a fixed size or come
+    from templates; a length is captured when it comes the second time, and the KEEP most recently used
+    lengths are kept (each holds the activations of a T-token step)."""
+    MIN_TOKENS = 16
+    KEEP = 4
+
+    def __init__(self, engine: Engine, n_tokens: int, offs, sizes):
+        self.engine, self.T = engine, n_tokens
+        self.offs, self.sizes = offs, sizes
+        self.meta = torch.zeros(offs[-1], dtype=torch.int32, device=engine.device)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+
+    def _forward(self) -> torch.Tensor:
+        e, T = self.engine, self.T
+        v = [self.meta[self.offs[k]:self.offs[k] + self.sizes[k]] for k in range(8)]
+        ctx = StepContext(
+            n_tokens=T, n_seqs=1, decode=False, max_q_len=T, max_kv_len=e.max_seq_len, tokens=v[0], tok_pos=v[1],
+            tok_seq=v[2], cu_q=v[3], seq_slot=v[4], seq_start=v[5], seq_kvlen=v[6], logit_rows=v[7], dtype=e.dtype,
+            device=e.device, kernels=e.kernels, all_rows=False)
+        logits = e.model.forward(ctx, e.cache)
+        ops.advance_lengths(ctx.seq_slot, ctx.seq_kvlen, e.cache.seq_lens, 1, e.cache.scratch_slot)
+        return logits
+
+    def capture(self) -> None:
+        """Records the step; nothing runs. Called right after an eager step of the same length, so every kernel
+        library is loaded and the allocator's pools are warm."""
+        if self.graph is not None:
+            return
+        torch.cuda.synchronize(self.engine.device)
+        graph = torch.cuda.CUDAGraph()
+        before = ops.LAUNCHES
+        gc.collect()
+        gc_was_on = gc.isenabled()
+        gc.disable()                      # see DecodeGraph._capture
+        try:
+            with torch.cuda.graph(graph):
+                self.logits = self._forward()
+        finally:
+            if gc_was_on:
+                gc.enable()
+        self.launches_per_replay = ops.LAUNCHES - before
+        self.graph = graph
+
+    def replay(self) -> torch.Tensor:
+        self.graph.replay()
+        ops.LAUNCHES += self.launches_per_replay
+        return self.logits.clone()        # the captured buffer is written again by the next replay
 
 
 class DecodeGraph:

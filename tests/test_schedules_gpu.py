@@ -214,3 +214,48 @@ def test_superseded_counters_stay_valid_for_earlier_captures():
     assert torch.equal(got, want), float((got - want).abs().max())
     assert int(plan._retired[0].abs().sum()) == 0    # the earlier capture left its counters clean
     del junk
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_captured_lone_prompt_steps(dtype):
+    """A lone prompt of a length that has come before runs as a captured step. Its logits are those of the
+    eager step whatever changes between replays: the tokens, the slot, the start position (a second piece of
+    the same length that goes on at position 70) and what the cache holds; other lengths and other `want`
+    forms stay eager; only a few lengths are kept."""
+    from llm_infer_engine_b200 import Engine
+    from llm_infer_engine_b200.engine.engine import PrefillGraph
+    tag, T = "c", 70
+    folder = helpers.model_folder(tag)
+    w, cfg = helpers.plain_weights(folder), helpers.read_config(folder)
+    engine = Engine(folder, dtype=dtype, max_batch=4, max_tokens=64 * 16, cuda_graph=True)
+    eager = Engine(folder, dtype=dtype, max_batch=4, max_tokens=64 * 16, cuda_graph=False)
+    seqs = [helpers.random_tokens(cfg["vocab_size"], 2 * T, seed=8000 + i) for i in range(4)]
+    held = engine.open()                                   # so that later requests get other slots
+    for i, toks in enumerate(seqs):
+        want = plain.logits(w, cfg, toks)
+        a, b = engine.open(), eager.open()
+        for piece in (toks[:T], toks[T:]):                 # the second piece starts at position 70
+            got = engine.step([a], [piece], "last")
+            ref = eager.step([b], [piece], "last")
+            assert torch.equal(got, ref), (i, float((got - ref).abs().max()))
+        err = float((got.float().cpu() - want[-1:]).abs().max())
+        assert err <= helpers.logit_bound(dtype, want), (i, err)
+        state = engine._prefill_graphs.get(T)
+        assert isinstance(state, PrefillGraph) and state.graph is not None      # captured at the second piece of length 70
+        engine.close(a)
+        eager.close(b)
+    engine.close(held)
+    # other forms of the same length are not served by the capture
+    slot = engine.open()
+    all_rows = engine.step([slot], [seqs[0][:T]], "all")
+    assert all_rows.shape[0] == T
+    engine.close(slot)
+    # lengths beyond the few that are kept push the oldest out
+    for n in range(20, 20 + PrefillGraph.KEEP + 2):
+        for _ in range(2):
+            slot = engine.open()
+            engine.step([slot], [seqs[1][:n]], "last")
+            engine.close(slot)
+    assert len(engine._prefill_graphs) == PrefillGraph.KEEP and T not in engine._prefill_graphs
+    engine.cache.check()
+    assert engine.cache.free_slots() == engine.cache.n_slots
