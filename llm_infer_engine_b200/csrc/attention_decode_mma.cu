@@ -91,13 +91,20 @@ __device__ __forceinline__ void md_merge_head(const float* part_m, const float* 
 }
 
 // grid (n_runs, n_kv * chunks, n_seqs), chunks = ceil(G / 16); WARPS warps per block.
-template <int HD, int WARPS>
+// With ROPE the kernel takes the step's raw projections instead of finished queries: `q` is then the packed
+// [n_seqs, (n_q + 2 n_kv) * HD] rows of q, k and v heads (row pitch q_ld), `rope` the float32 (cos, sin) table
+// [table_len, HD / 2]. Every lane rotates its own query fragments in registers (the rotate-half partner of a
+// column lies HD / 2 columns on, which is the same lane's fragment KS / 2 k-steps on), and the one warp whose
+// half page holds the sequence's newest position rotates the new key, puts key and value into its staged tile
+// and (with write_kv) into the cache. Rotation in float32, one rounding to bfloat16, as the separate kernel.
+template <int HD, int WARPS, bool ROPE>
 __global__ void __launch_bounds__(WARPS * 32, (HD == 64 && WARPS <= 4) ? 12 / WARPS : 1)
-decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
-                  const __nv_bfloat16* __restrict__ v_cache, float* __restrict__ part_m, float* __restrict__ part_l,
+decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* k_cache,
+                  const __nv_bfloat16* v_cache, float* __restrict__ part_m, float* __restrict__ part_l,
                   float* __restrict__ part_acc, const int* __restrict__ seq_slot, const int* __restrict__ seq_kvlen,
                   const int* __restrict__ block_table, int max_pages, int n_q, int n_kv, float scale, int window,
-                  int pages_per_run, int n_runs, int* __restrict__ counters, __nv_bfloat16* __restrict__ out) {
+                  int pages_per_run, int n_runs, int* __restrict__ counters, __nv_bfloat16* __restrict__ out,
+                  const float2* __restrict__ rope, int table_len, int q_ld, int write_kv) {
   pdl_launch_dependents();
   constexpr int PITCH = HD + 8;                         // elements; rows 16 bytes apart in the banks
   constexpr int KS = HD / 16;                           // k-steps of Q K^T
@@ -179,7 +186,8 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
   // the queries of this head group as A fragments: rows g and g + 8, all of head_dim
   unsigned qa[KS][4];
   {
-    const __nv_bfloat16* q_lo = q + ((size_t)seq * n_q + (size_t)hk * G + g0 + g) * HD;
+    const size_t q_row = ROPE ? (size_t)seq * q_ld : (size_t)seq * n_q * HD;
+    const __nv_bfloat16* q_lo = q + q_row + ((size_t)hk * G + g0 + g) * HD;
     const __nv_bfloat16* q_hi = q_lo + (size_t)8 * HD;
     const bool lo_ok = g < ng, hi_ok = g + 8 < ng;
 #pragma unroll
@@ -189,6 +197,22 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
       qa[ks][1] = hi_ok ? *reinterpret_cast<const unsigned*>(q_hi + c) : 0u;
       qa[ks][2] = lo_ok ? *reinterpret_cast<const unsigned*>(q_lo + c + 8) : 0u;
       qa[ks][3] = hi_ok ? *reinterpret_cast<const unsigned*>(q_hi + c + 8) : 0u;
+    }
+    if constexpr (ROPE) {
+      const int tpos = min(len - 1, table_len - 1);
+      const float2* cs = rope + (size_t)tpos * (HD / 2);
+#pragma unroll
+      for (int ks = 0; ks < KS / 2; ++ks) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {                    // registers 0, 1: columns c, c + 1; 2, 3: c + 8, c + 9
+          const int c = ks * 16 + 2 * t + (r >> 1) * 8;
+          const float2 c0 = cs[c], c1 = cs[c + 1];
+          const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qa[ks][r]));
+          const float2 x2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qa[ks + KS / 2][r]));
+          qa[ks][r] = md_pack(x1.x * c0.x - x2.x * c0.y, x1.y * c1.x - x2.y * c1.y);
+          qa[ks + KS / 2][r] = md_pack(x2.x * c0.x + x1.x * c0.y, x2.y * c1.x + x1.y * c1.y);
+        }
+      }
     }
   }
   float o[NT][4];
@@ -206,6 +230,41 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
     if (np <= p_last) asm volatile("cp.async.wait_group 1;" ::: "memory");   // this unit has arrived, the next is on its way
     else asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncwarp();
+    if constexpr (ROPE) {
+      if (p == p_new && h == ((len - 1) % kMdPage) / kHalf) {
+        // the sequence's newest position lies in this half page: its key and value come from the step's
+        // projections, not from the cache (which holds whatever the page held before at that row)
+        const int row = (len - 1) % kHalf;
+        const __nv_bfloat16* k_raw = q + (size_t)seq * q_ld + (size_t)(n_q + hk) * HD;
+        const __nv_bfloat16* v_raw = k_raw + (size_t)n_kv * HD;
+        const int tpos = min(len - 1, table_len - 1);
+        const float2* cs = rope + (size_t)tpos * (HD / 2);
+        __nv_bfloat16* k_row = k_tile + (size_t)s_ * 2 * (kHalf * PITCH) + (size_t)row * PITCH;
+        __nv_bfloat16* v_row = k_row + kHalf * PITCH;
+        const bool to_cache = write_kv && g0 == 0;       // one writer per (sequence, KV head)
+        const size_t dst = (size_t)pages[p] * page_stride + head_off + (size_t)(h * kHalf + row) * HD;
+        for (int d = lane; d < HD / 2; d += 32) {
+          const float2 c = cs[d];
+          const float x1 = __bfloat162float(k_raw[d]), x2 = __bfloat162float(k_raw[d + HD / 2]);
+          const __nv_bfloat16 y1 = __float2bfloat16_rn(x1 * c.x - x2 * c.y);
+          const __nv_bfloat16 y2 = __float2bfloat16_rn(x2 * c.x + x1 * c.y);
+          const __nv_bfloat16 v1 = v_raw[d], v2 = v_raw[d + HD / 2];
+          k_row[d] = y1;
+          k_row[d + HD / 2] = y2;
+          v_row[d] = v1;
+          v_row[d + HD / 2] = v2;
+          if (to_cache) {
+            __nv_bfloat16* kc = const_cast<__nv_bfloat16*>(k_cache) + dst;
+            __nv_bfloat16* vc = const_cast<__nv_bfloat16*>(v_cache) + dst;
+            kc[d] = y1;
+            kc[d + HD / 2] = y2;
+            vc[d] = v1;
+            vc[d + HD / 2] = v2;
+          }
+        }
+        __syncwarp();
+      }
+    }
     // ---- S = Q K^T: 4 tiles of 8 keys
     float s[4][4];
 #pragma unroll
@@ -356,23 +415,24 @@ decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
   }
 }
 
-template <int HD, int WARPS>
+template <int HD, int WARPS, bool ROPE>
 static int launch_mma(const void* q, const void* k_cache, const void* v_cache, float* part_m, float* part_l,
                       float* part_acc, const int* seq_slot, const int* seq_kvlen, const int* block_table, int max_pages,
                       int n_seqs, int n_q, int n_kv, float scale, int window, int pages_per_run, int n_runs,
-                      int* counters, void* out, cudaStream_t stream) {
+                      int* counters, void* out, const float2* rope, int table_len, int q_ld, int write_kv,
+                      cudaStream_t stream) {
   const int G = n_q / n_kv;
   const int chunks = (G + 15) / 16;
   const size_t smem = (size_t)WARPS * 2 * kMdPage * (HD + 8) * sizeof(__nv_bfloat16);
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<HD, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<HD, WARPS, ROPE>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  launch_k(decode_mma_kernel<HD, WARPS>, dim3(n_runs, n_kv * chunks, n_seqs), dim3(WARPS * 32), smem, stream,
+  launch_k(decode_mma_kernel<HD, WARPS, ROPE>, dim3(n_runs, n_kv * chunks, n_seqs), dim3(WARPS * 32), smem, stream,
            (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, part_m, part_l,
            part_acc, seq_slot, seq_kvlen, block_table, max_pages, n_q, n_kv, scale, window, pages_per_run, n_runs,
-           counters, (__nv_bfloat16*)out);
+           counters, (__nv_bfloat16*)out, rope, table_len, q_ld, write_kv);
   LLMIE_LAUNCH_CHECK();
   return LLMIE_OK;
 }
@@ -415,12 +475,11 @@ extern "C" int llmie_attention_decode_mma_pages(int n_seqs, int n_groups, int ma
 // including this step's. n_runs * pages_per_run * 64 must cover the longest sequence. part_*: float32
 // scratch as in llmie_attention_decode (untouched when n_runs == 1); counters: int32 zeros, one per
 // (sequence, KV head, chunk of 16 query heads), left zero.
-extern "C" int llmie_attention_decode_mma(const void* q, const void* k_cache, const void* v_cache, void* out,
-                                          float* part_m, float* part_l, float* part_acc, int* counters,
-                                          const int* seq_slot, const int* seq_kvlen, const int* block_table,
-                                          int max_pages, int page_size, int n_seqs, int n_q, int n_kv, int hd,
-                                          float scale, int window, int pages_per_run, int n_runs,
-                                          cudaStream_t stream) {
+static int decode_mma_entry(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_m,
+                            float* part_l, float* part_acc, int* counters, const int* seq_slot, const int* seq_kvlen,
+                            const int* block_table, int max_pages, int page_size, int n_seqs, int n_q, int n_kv, int hd,
+                            float scale, int window, int pages_per_run, int n_runs, const float2* rope, int table_len,
+                            int q_ld, int write_kv, cudaStream_t stream) {
   if (n_seqs < 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv || max_pages <= 0 || pages_per_run <= 0 || n_runs <= 0)
     return LLMIE_ERR_BAD_ARG;
   if (!llmie_attention_decode_mma_supported(hd, LLMIE_BF16, page_size)) return LLMIE_ERR_UNSUPPORTED_SIZE;
@@ -450,9 +509,13 @@ extern "C" int llmie_attention_decode_mma(const void* q, const void* k_cache, co
       best_w = w;
     }
   }
-#define LLMIE_MMA(HD, W)                                                                                         \
-  return launch_mma<HD, W>(q, k_cache, v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen, block_table,      \
-                           max_pages, n_seqs, n_q, n_kv, scale, window, pages_per_run, n_runs, counters, out, stream)
+#define LLMIE_MMA(HD, W)                                                                                             \
+  return rope ? launch_mma<HD, W, true>(q, k_cache, v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen,          \
+                                        block_table, max_pages, n_seqs, n_q, n_kv, scale, window, pages_per_run,     \
+                                        n_runs, counters, out, rope, table_len, q_ld, write_kv, stream)              \
+              : launch_mma<HD, W, false>(q, k_cache, v_cache, part_m, part_l, part_acc, seq_slot, seq_kvlen,         \
+                                         block_table, max_pages, n_seqs, n_q, n_kv, scale, window, pages_per_run,    \
+                                         n_runs, counters, out, nullptr, 0, 0, 0, stream)
   if (hd == 64) {
     if (best_w == 8) LLMIE_MMA(64, 8);
     if (best_w == 4) LLMIE_MMA(64, 4);
@@ -463,4 +526,34 @@ extern "C" int llmie_attention_decode_mma(const void* q, const void* k_cache, co
   if (best_w == 3) LLMIE_MMA(128, 3);
   LLMIE_MMA(128, 2);
 #undef LLMIE_MMA
+}
+
+extern "C" int llmie_attention_decode_mma(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                          float* part_m, float* part_l, float* part_acc, int* counters,
+                                          const int* seq_slot, const int* seq_kvlen, const int* block_table,
+                                          int max_pages, int page_size, int n_seqs, int n_q, int n_kv, int hd,
+                                          float scale, int window, int pages_per_run, int n_runs,
+                                          cudaStream_t stream) {
+  return decode_mma_entry(q, k_cache, v_cache, out, part_m, part_l, part_acc, counters, seq_slot, seq_kvlen, block_table,
+                          max_pages, page_size, n_seqs, n_q, n_kv, hd, scale, window, pages_per_run, n_runs, nullptr, 0,
+                          0, 0, stream);
+}
+
+// The same with position encoding and the cache write inside: qkv bfloat16 [n_seqs, (n_q + 2 n_kv) hd] holds the
+// step's raw projections (q heads, k heads, v heads), rope float32 [table_len, hd / 2, 2] the (cos, sin) of every
+// position for a rotation over the whole head size. The new key (rotated) and value of sequence i are used for
+// position seq_kvlen[i] - 1 and, with write_kv, written to the cache there.
+extern "C" int llmie_attention_decode_mma_rope(const void* qkv, void* k_cache, void* v_cache, void* out,
+                                               const float* rope, int table_len, float* part_m, float* part_l,
+                                               float* part_acc, int* counters, const int* seq_slot,
+                                               const int* seq_kvlen, const int* block_table, int max_pages,
+                                               int page_size, int n_seqs, int n_q, int n_kv, int hd, float scale,
+                                               int window, int pages_per_run, int n_runs, int write_kv,
+                                               cudaStream_t stream) {
+  if (!rope || table_len <= 0) return LLMIE_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(rope) & 7u) != 0) return LLMIE_ERR_ALIGNMENT;
+  return decode_mma_entry(qkv, k_cache, v_cache, out, part_m, part_l, part_acc, counters, seq_slot, seq_kvlen,
+                          block_table, max_pages, page_size, n_seqs, n_q, n_kv, hd, scale, window, pages_per_run, n_runs,
+                          reinterpret_cast<const float2*>(rope), table_len, (n_q + 2 * n_kv) * hd, write_kv ? 1 : 0,
+                          stream);
 }

@@ -42,6 +42,15 @@ class StepContext:
     all_rows: bool = False               # logit_rows is 0..n_tokens-1: every row's logits are wanted
     entry: int = 0                       # which entry of the run order is running (set by the model, for traces)
 
+    def attention_with_rope(self, qkv, table, kv, out, n_q: int, n_kv: int, head_dim: int, options: AttentionOptions,
+                            write_kv: bool) -> bool:
+        """Attention straight from the packed projections `qkv` of a one-token step, with the rotation by
+        `table` (a whole-head (cos, sin) table) and the cache write inside the attention kernel. Returns False
+        when no kernel does that for this step; the caller then encodes and stores first and calls `attention`."""
+        plan = self.kernels
+        return plan is not None and plan.attention_with_rope(self, qkv, table, kv, out, n_q, n_kv, head_dim, options,
+                                                             write_kv)
+
     def attention(self, q, kv, out, n_q: int, n_kv: int, head_dim: int, options: AttentionOptions) -> None:
         """softmax(q k^T * scale) v over the cache unit `kv`, each token seeing the keys of its own
         sequence up to its own position (and no further back than `options.window`, if set)."""

@@ -35,6 +35,23 @@ class KernelPlan:
         (src/flash_decode.py:271-272). Depends only on the step's shape, never on its data."""
         return ops.attention_decode_run_len(n_seqs, head_dim, dtype)
 
+    def attention_with_rope(self, ctx, qkv, table, kv, out, n_q, n_kv, head_dim, options, write_kv) -> bool:
+        """One-token steps whose projections were not made by the fused norm + QKV kernel (more than 8 rows):
+        rotation of q and k and the cache write happen inside the attention kernel, where a kernel for this
+        size exists. Returns False (and does nothing) otherwise; the caller then rotates and stores first."""
+        if not write_kv:
+            return False       # a borrowed cache already holds the owner's new key: it must be read, not replaced
+        if not (ctx.decode and self.decode_attention != "split" and qkv.dtype == torch.bfloat16
+                and table is not None and ops.attention_decode_mma_supported(head_dim, qkv.dtype, kv.page_size)):
+            return False
+        pages = ops.attention_decode_mma_pages(ctx.n_seqs, n_q, n_kv, ctx.max_kv_len)
+        n_runs = ((ctx.max_kv_len + 63) // 64 + pages - 1) // pages
+        counters = self._decode_counters(ops.decode_counter_ints(ctx.n_seqs, n_q, n_kv), qkv.device)
+        ops.attention_decode_mma_rope(qkv, kv.k, kv.v, out, table, ctx.seq_slot, ctx.seq_kvlen, kv.block_table,
+                                      kv.page_size, n_q, n_kv, head_dim, options.scale, options.window, pages, n_runs,
+                                      write_kv, counters=counters)
+        return True
+
     def attention(self, ctx, q, kv, out, n_q, n_kv, head_dim, options) -> bool:
         """Returns True when a specialised kernel ran. Every kernel below takes the options there are
         today (scale, window); a new option is checked here, kernel by kernel."""

@@ -401,6 +401,48 @@ def attention_decode_mma(q, k_cache, v_cache, out, seq_slot, seq_kvlen, block_ta
     return out
 
 
+def attention_decode_mma_rope(qkv, k_cache, v_cache, out, table, seq_slot, seq_kvlen, block_table, page_size: int,
+                              n_q: int, n_kv: int, head_dim: int, scale: float, window: int, pages_per_run: int,
+                              n_runs: int, write_kv: bool = True, counters: Optional[torch.Tensor] = None,
+                              scratch: Optional[torch.Tensor] = None):
+    """attention_decode_mma with the position encoding and the cache write inside: qkv bfloat16
+    [n, (n_q + 2 n_kv) hd] holds the step's raw q, k and v heads; table float32 [max_pos, hd / 2, 2] is the
+    (cos, sin) table of a rotation over the whole head size. Sequence i's new key and value are taken for
+    position seq_kvlen[i] - 1 and, with write_kv, written into the cache there."""
+    n = qkv.shape[0]
+    _need(qkv, "qkv", torch.bfloat16, (n, (n_q + 2 * n_kv) * head_dim))
+    _need(out, "out", torch.bfloat16, (n, n_q * head_dim))
+    _need(k_cache, "k_cache", torch.bfloat16, (None, n_kv, page_size, head_dim))
+    _need(v_cache, "v_cache", torch.bfloat16, tuple(k_cache.shape))
+    _need(table, "table", torch.float32, (None, head_dim // 2, 2))
+    for name, t in (("seq_slot", seq_slot), ("seq_kvlen", seq_kvlen), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    if seq_slot.numel() < n or seq_kvlen.numel() < n:
+        raise KernelError("attention_decode_mma_rope: seq_slot / seq_kvlen shorter than the number of sequences")
+    base = n_ml = 0
+    cptr = None
+    if n_runs > 1:
+        need = decode_scratch_floats(n, n_q, head_dim, n_runs)
+        if scratch is None:
+            scratch = torch.empty(need, dtype=torch.float32, device=qkv.device)
+        _need(scratch, "scratch", torch.float32)
+        if scratch.numel() < need:
+            raise KernelError(f"attention_decode_mma_rope: scratch holds {scratch.numel()} floats, {need} are needed")
+        if counters is None or counters.numel() < n * n_kv * ((n_q // n_kv + 15) // 16):
+            raise KernelError("attention_decode_mma_rope: counters are needed when a sequence spans several runs")
+        _need(counters, "counters", torch.int32)
+        base, n_ml, cptr = scratch.data_ptr(), n * n_q * n_runs, counters.data_ptr()
+    _work(_nbytes(qkv, out) + 2.0 * STEP_HINT["kv_total"] * n_kv * head_dim * 2, 4.0 * n_q * head_dim * STEP_HINT["pairs"])
+    f = _fn("attention_decode_mma", "llmie_attention_decode_mma_rope",
+            [_c_void_p] * 5 + [_c_int] + [_c_void_p] * 7 + [_c_int] * 6 + [_c_float] + [_c_int] * 4 + [_c_void_p])
+    _check(f(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), table.data_ptr(), table.shape[0],
+             base or None, (base + 4 * n_ml) or None, (base + 8 * n_ml) or None, cptr, seq_slot.data_ptr(),
+             seq_kvlen.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, n, n_q, n_kv, head_dim,
+             float(scale), int(window), int(pages_per_run), int(n_runs), 1 if write_kv else 0, _stream()),
+           "attention_decode_mma_rope")
+    return out
+
+
 def gemm_f32_nt(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[M, N] = a[M, K] @ w[N, K]^T in true float32 (FMA on CUDA cores, fixed summation order)."""
     M, K = a.shape

@@ -76,17 +76,30 @@ class GroupedQueryAttention(Mixer):
                                   self.head_dim, owns_cache)
             else:
                 x = x.apply()
+        attended = False
         if q is None:
             qkv = self.qkv(x)
             trace.pop()
-            trace.push("RoPE+KV_cache")
-            q = self.position.encode_and_store(qkv, ctx, kv, self.n_heads, self.n_kv_heads, self.head_dim,
-                                               owns_cache)
-        trace.pop()
-        out = torch.empty_like(q)
-        trace.push("FlashDecode" if ctx.decode else "FlashAttn")
-        ctx.attention(q, kv, out, self.n_heads, self.n_kv_heads, self.head_dim, self.options)
-        trace.pop()
+            if ctx.decode:
+                # one-token steps of more than 8 rows: rotation and cache write inside the attention kernel
+                out = torch.empty((qkv.shape[0], self.n_heads * self.head_dim), dtype=qkv.dtype, device=qkv.device)
+                trace.push("FlashDecode")
+                table = getattr(self.position, "fused_table", lambda hd: None)(self.head_dim)
+                attended = ctx.attention_with_rope(qkv, table, kv, out, self.n_heads, self.n_kv_heads, self.head_dim,
+                                                   self.options, owns_cache)
+                trace.pop()
+            if not attended:
+                trace.push("RoPE+KV_cache")
+                q = self.position.encode_and_store(qkv, ctx, kv, self.n_heads, self.n_kv_heads, self.head_dim,
+                                                   owns_cache)
+                trace.pop()
+        else:
+            trace.pop()
+        if not attended:
+            out = torch.empty_like(q)
+            trace.push("FlashDecode" if ctx.decode else "FlashAttn")
+            ctx.attention(q, kv, out, self.n_heads, self.n_kv_heads, self.head_dim, self.options)
+            trace.pop()
         trace.push("Output_proj")
         done = residual is not None and self.o.add_into(out, residual)
         y = None if done else self.o(out)

@@ -576,6 +576,68 @@ def test_norm_qkv_rope(batch, n_q, n_kv, hd, K):
             assert err <= 2e-2 * max(1.0, float(ref_t.abs().max())), (name, b, err, float(ref_t.abs().max()))
 
 
+@pytest.mark.parametrize("n_q,n_kv,hd", [(6, 2, 64), (32, 8, 64), (4, 1, 128), (24, 8, 128)])
+@pytest.mark.parametrize("window,pages", [(0, 0), (100, 0), (0, 4)])
+def test_decode_attention_with_rotation_and_cache_write_inside(n_q, n_kv, hd, window, pages):
+    """One-token attention straight from the raw projections (rotation of q and k and the cache write inside the
+    kernel) against the two separate kernels, for sequences whose newest position is a page's first row, its
+    last, the first of a half page, and deep in a long sequence cut into runs; and against plain attention."""
+    o = ops()
+    dtype = torch.bfloat16
+    lens = [1, 64, 65, 97, 128, 700, 333, 33, 1500]
+    n = len(lens)
+    pg = Paged(lens, n_kv, hd, dtype, seed=hd + n_q)
+    pg.fill(upto=[l - 1 for l in lens])                # everything but the newest position, which the step brings
+    g = torch.Generator().manual_seed(3)
+    qkv = torch.randn(n, (n_q + 2 * n_kv) * hd, generator=g).to(dtype).to(DEV)
+    inv = plain.inv_frequencies(hd, 10000.0, None)
+    cos, sin = plain.rotation_tables(torch.arange(2048), inv)
+    table = torch.stack([cos, sin], dim=-1).contiguous().to(DEV)
+    slots = torch.tensor(pg.slots, dtype=torch.int32, device=DEV)
+    kvlen = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=DEV)
+    tok_seq = torch.arange(n, dtype=torch.int32, device=DEV)
+    max_kv = 2048
+    pages = pages or o.attention_decode_mma_pages(n, n_q, n_kv, max_kv)     # 4: long sequences are merged from 8 runs
+    n_runs = ((max_kv + 63) // 64 + pages - 1) // pages
+    counters = torch.zeros(o.decode_counter_ints(n, n_q, n_kv) + 64, dtype=torch.int32, device=DEV)
+    # the two separate kernels
+    k1, v1, bt = pg.dev()
+    q1 = torch.empty(n, n_q * hd, dtype=dtype, device=DEV)
+    o.rope_store(qkv, q1, k1, v1, table, tok_pos, tok_seq, slots, bt, 64, n_q, n_kv, hd, hd)
+    want = torch.empty_like(q1)
+    o.attention_decode_mma(q1, k1, v1, want, slots, kvlen, bt, 64, n_q, n_kv, hd, hd ** -0.5, window, pages, n_runs,
+                           counters=counters)
+    # one kernel
+    k2, v2, _ = pg.dev()
+    got = torch.full_like(want, float("nan"))
+    o.attention_decode_mma_rope(qkv, k2, v2, got, table, slots, kvlen, bt, 64, n_q, n_kv, hd, hd ** -0.5, window, pages,
+                                n_runs, True, counters=counters)
+    assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2), float((got.float() - want.float()).abs().max())
+    assert torch.allclose(k2.float(), k1.float(), atol=1e-2, rtol=1e-2) and torch.equal(v2, v1)
+    assert torch.equal((k2 != pg.dev()[0]).any(-1), (k1 != pg.dev()[0]).any(-1))     # the same cache rows were written
+    assert int(counters.abs().sum()) == 0
+    # without the cache write the cache is left alone and the output is the same
+    k3, v3, _ = pg.dev()
+    again = torch.empty_like(want)
+    o.attention_decode_mma_rope(qkv, k3, v3, again, table, slots, kvlen, bt, 64, n_q, n_kv, hd, hd ** -0.5, window, pages,
+                                n_runs, False, counters=counters)
+    assert torch.equal(again, got) and torch.equal(k3, pg.dev()[0]) and torch.equal(v3, pg.dev()[1])
+    # plain attention over the dense keys (the newest one rotated in float32)
+    for i, L in enumerate(lens):
+        row = qkv[i].float().cpu()
+        qf = row[:n_q * hd].view(n_q, 1, hd)
+        kf = row[n_q * hd:(n_q + n_kv) * hd].view(n_kv, 1, hd)
+        vf = row[(n_q + n_kv) * hd:].view(n_kv, hd)
+        c, s_ = cos[L - 1:L], sin[L - 1:L]
+        qr = plain.rotate_half(qf, c, s_).view(1, n_q, hd).to(dtype).float()
+        kd, vd = pg.dense_k[i].float().clone(), pg.dense_v[i].float().clone()
+        kd[L - 1] = plain.rotate_half(kf, c, s_).view(n_kv, hd).to(dtype).float()
+        vd[L - 1] = vf
+        ref = ref_attention(qr, kd, vd, [L - 1], hd ** -0.5, window).reshape(-1)
+        assert torch.allclose(got[i].float().cpu(), ref, atol=3e-2), (i, L, float((got[i].float().cpu() - ref).abs().max()))
+
+
 def test_attention_decode_merge_reads_fresh_partials():
     """The block that merges the runs of a sequence must see the other blocks' partial results of THIS
     launch. Few query heads make the partial maxima of many sequences share a 128-byte line, the scratch
