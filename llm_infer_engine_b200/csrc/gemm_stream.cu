@@ -301,6 +301,35 @@ static StreamPlan stream_plan(int M, int N, int K, int n_sms, int force_splits =
 
 using namespace llmie;
 
+// How many clusters of `splits` blocks of the kernel for `rows` rows the device can hold at once (0 on error).
+extern "C" int llmie_gemm_stream_active_clusters(int rows, int N, int K, int n_sms, int splits) {
+  const StreamPlan p = stream_plan(rows, N, K, n_sms, splits);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.n_clusters * p.n_splits);
+  cfg.blockDim = dim3(kSThreads);
+  cfg.dynamicSmemBytes = p.smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = p.n_splits;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  cudaError_t e;
+  if (p.mpad == 16) {
+    cudaFuncSetAttribute(gemm_stream_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem);
+    e = cudaOccupancyMaxActiveClusters(&n, gemm_stream_kernel<16>, &cfg);
+  } else if (p.mpad == 32) {
+    cudaFuncSetAttribute(gemm_stream_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem);
+    e = cudaOccupancyMaxActiveClusters(&n, gemm_stream_kernel<32>, &cfg);
+  } else {
+    cudaFuncSetAttribute(gemm_stream_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem);
+    e = cudaOccupancyMaxActiveClusters(&n, gemm_stream_kernel<64>, &cfg);
+  }
+  return e == cudaSuccess ? n : 0;
+}
+
 // X [M <= 64, K] and W [N, K] bfloat16 row-major (K % 8 == 0, 16-byte aligned). mode 0: out bfloat16 [M, N];
 // 1: out float32 [M, N]; 2: out float32 [M, N] += the product. n_sms: SMs of the device (sizes the grid).
 // splits: 0 lets the launcher choose into how many slices K is cut; 1, 2, 4 or 8 fixes it.
