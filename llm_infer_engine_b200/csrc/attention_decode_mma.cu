@@ -98,7 +98,7 @@ __device__ __forceinline__ void md_merge_head(const float* part_m, const float* 
 // half page holds the sequence's newest position rotates the new key, puts key and value into its staged tile
 // and (with write_kv) into the cache. Rotation in float32, one rounding to bfloat16, as the separate kernel.
 template <int HD, int WARPS, bool ROPE>
-__global__ void __launch_bounds__(WARPS * 32, (HD == 64 && WARPS <= 4) ? 12 / WARPS : 1)
+__global__ void __launch_bounds__(WARPS * 32, (HD == 64 && WARPS <= 4) ? 16 / WARPS : 1)
 decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* k_cache,
                   const __nv_bfloat16* v_cache, float* __restrict__ part_m, float* __restrict__ part_l,
                   float* __restrict__ part_acc, const int* __restrict__ seq_slot, const int* __restrict__ seq_kvlen,
@@ -499,7 +499,7 @@ static int decode_mma_entry(const void* q, const void* k_cache, const void* v_ca
     const int w = options[i];
     if (w * tile_bytes > 200 * 1024) continue;
     int per_sm = (220 * 1024) / (w * tile_bytes);
-    if (hd == 64 && per_sm > 12 / w) per_sm = 12 / w > 0 ? 12 / w : 1;       // registers
+    if (hd == 64 && per_sm > 16 / w) per_sm = 16 / w > 0 ? 16 / w : 1;       // registers
     if (per_sm < 1) continue;
     const long long slots = 148LL * per_sm;
     const double waves = (double)((blocks + slots - 1) / slots);

@@ -213,7 +213,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       };
       if (ok) ok = issue_scores(0);
       for (int jt = 0; ok && jt < n_tiles; ++jt) {
-        if (jt + 1 < n_tiles && !issue_scores(jt + 1)) break;
+        // Two score buffers: the next tile's scores first, they need nothing of this tile's softmax. One buffer:
+        // the next scores have to wait for the softmax to let go of it, which is when P is ready too, and the
+        // softmax threads then wait for P.V, so P.V goes first.
+        if (Cfg::kSBufs > 1 && jt + 1 < n_tiles && !issue_scores(jt + 1)) break;
         const int vs = jt % Cfg::kVStages;
         if (!mbar_wait(&sh.p_ready, jt & 1, abort)) { LLMIE_FAIL(kStatusTimeoutMma); break; }
         if (!mbar_wait(&sh.v_full[vs], (jt / Cfg::kVStages) & 1, abort)) { LLMIE_FAIL(kStatusTimeoutFull); break; }
@@ -228,6 +231,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         mma_commit(&sh.pv_full);
         mma_commit(&sh.v_empty[vs]);
+        if (Cfg::kSBufs == 1 && jt + 1 < n_tiles && !issue_scores(jt + 1)) break;
       }
     }
   } else {
