@@ -394,7 +394,7 @@ def run_ours(args):
     full_layers = CONFIG_1B["num_hidden_layers"]
     n_layers = args.layers or full_layers
     folder = make_model_folder(CONFIG_1B, n_layers, seed=2, tag="1b")
-    max_batch = 64
+    max_batch = max(64, args.batch)
     per_seq = PROMPT_LEN + args.steps + args.warmup + 64
     engine = Engine(folder, dtype="bfloat16", device=0, max_batch=max_batch, max_seq_len=CONTEXT,
                     max_tokens=max(max_batch * ((per_seq + 63) // 64 * 64), PREFILL_TOKENS + 64), cuda_graph=True)
@@ -534,6 +534,8 @@ def main():
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=512,
+                    help="tokens every sequence holds before decoding starts (the benchmark's 512; up to the context)")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0 = all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
@@ -548,6 +550,8 @@ def main():
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    global PROMPT_LEN
+    PROMPT_LEN = max(1, min(args.prompt_len, CONTEXT - args.steps - max(args.warmup, 3) - 8))
     if args.impl == "reference":
         return run_reference(args)
     if args.warmup < 3:

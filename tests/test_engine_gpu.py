@@ -107,3 +107,60 @@ def test_wide_batches_match_plain(dtype, n_requests):
         from llm_infer_engine_b200.kernels import ops
         ops.check_tc_status("cuda")
     assert engine.cache.free_slots() == engine.cache.n_slots
+
+
+AWKWARD = [
+    # head size 48 (no tensor-core attention), width and feed-forward no multiples of 16, an odd vocabulary
+    dict(num_hidden_layers=2, hidden_size=136, num_attention_heads=3, num_key_value_heads=1, head_dim=48,
+         intermediate_size=200, vocab_size=1001, rope_theta=30000.0, rope_scaling=None, rms_norm_eps=3e-6,
+         tie_word_embeddings=True, max_position_embeddings=192),
+    # head size 80, five query heads on five KV heads, untied head, widths that are multiples of 8 only
+    dict(num_hidden_layers=1, hidden_size=200, num_attention_heads=5, num_key_value_heads=5, head_dim=80,
+         intermediate_size=328, vocab_size=777, rope_theta=10000.0, rope_scaling=None, rms_norm_eps=1e-5,
+         tie_word_embeddings=False, max_position_embeddings=160),
+    # head size 112 and 144 do not exist in the fast kernels either; 7 query heads on one KV head
+    dict(num_hidden_layers=1, hidden_size=96, num_attention_heads=7, num_key_value_heads=1, head_dim=112,
+         intermediate_size=72, vocab_size=130, rope_theta=500000.0,
+         rope_scaling={"rope_type": "llama3", "factor": 2.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                       "original_max_position_embeddings": 32},
+         rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=150),
+    # a width, a feed-forward width and a vocabulary that are no multiples of 8: no 16-byte loads anywhere
+    dict(num_hidden_layers=2, hidden_size=100, num_attention_heads=5, num_key_value_heads=5, head_dim=16,
+         intermediate_size=60, vocab_size=51, rope_theta=10000.0, rope_scaling=None, rms_norm_eps=1e-5,
+         tie_word_embeddings=True, max_position_embeddings=140),
+]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", [0, 1, 2, 3])
+def test_sizes_that_fit_no_fast_kernel(which, dtype):
+    """Head sizes in steps of 16 that the tensor-core kernels do not take, widths that are no multiples of 16, an odd
+    vocabulary, any number of heads and groups: the plain kernels of the same math serve them (or the engine refuses
+    with a clear error; it never gives a wrong result). Whole, one by one, in batches, in pieces."""
+    from llm_infer_engine_b200 import Engine, write_random_model
+    cfg = dict(plain.TINY_A, **AWKWARD[which])
+    folder = helpers.scratch_folder("llmie_awkward_")
+    write_random_model(cfg, folder, seed=20 + which, std=0.08, norm_range=(0.8, 1.2))
+    w = helpers.plain_weights(folder)
+    lens = [l for l in (1, 9, 64, 65, 130) if l <= cfg["max_position_embeddings"]]
+    requests = {f"k{i}": helpers.random_tokens(cfg["vocab_size"], n, seed=50 + i) for i, n in enumerate(lens)}
+    want = {rid: plain.logits(w, cfg, toks) for rid, toks in requests.items()}
+    engine = Engine(folder, dtype=dtype, max_batch=3, max_tokens=64 * 8, cuda_graph=False)
+    for plan in (helpers.plan_whole(requests), helpers.plan_tail(requests, 32), helpers.plan_batched(requests, 3),
+                 helpers.plan_chunked(requests, 33)):
+        check(helpers.run_plan_engine(engine, plan), want, dtype, f"awkward {which}/{dtype}")
+    # and through the captured step and the loop
+    from llm_infer_engine_b200 import generate
+    engine2 = Engine(folder, dtype=dtype, max_batch=3, cuda_graph=True)
+    prompts = [requests["k1"], requests["k2"][:20], requests["k0"]]
+    out = generate(engine2, prompts, max_new_tokens=5, stop_ids=[])
+    out_eager = generate(engine, prompts, max_new_tokens=5, stop_ids=[])
+    if dtype == "float32":
+        assert out == out_eager
+    for p, o in zip(prompts, out):
+        seq = list(p)
+        for tok in o:
+            row = plain.logits(w, cfg, seq)[-1]
+            best = int(row.argmax())
+            assert tok == best or float(row[best] - row[tok]) < (1e-5 if dtype == "float32" else 0.03) * max(1.0, float(row.abs().max()))
+            seq.append(tok)
