@@ -15,6 +15,7 @@ from __future__ import annotations
 import array
 import gc
 import itertools
+import sys
 from typing import Dict, List, Optional, Sequence, Union
 
 import numpy as np
@@ -282,6 +283,16 @@ class Engine:
             g.set_sampling(sampling)
         return g
 
+    def try_decode_graph(self, *args, **kwargs) -> Optional["DecodeGraph"]:
+        """`decode_graph`, or None when this model's step cannot be captured (`use_cuda_graph` is then off)."""
+        try:
+            return self.decode_graph(*args, **kwargs)
+        except RuntimeError as exc:
+            if "captur" not in str(exc).lower() and "graph" not in str(exc).lower():
+                raise
+            capture_failed(self, "the one-token step", exc)
+            return None
+
     def weight_bytes_per_step(self) -> int:
         return self.model.weight_bytes_per_step()
 
@@ -358,6 +369,9 @@ class PrefillGraph:
         try:
             with torch.cuda.graph(graph):
                 self.logits = self._forward()
+        except RuntimeError as exc:
+            capture_failed(self.engine, f"the prompt step of {self.T} tokens", exc)
+            return
         finally:
             if gc_was_on:
                 gc.enable()
@@ -368,6 +382,15 @@ class PrefillGraph:
         self.graph.replay()
         ops.LAUNCHES += self.launches_per_replay
         return self.logits.clone()        # the captured buffer is written again by the next replay
+
+
+def capture_failed(engine: Engine, what: str, exc: BaseException) -> None:
+    """A part that reads device memory on the host in its forward (a registered part written with plain tensor
+    code may) cannot be recorded into a graph. The engine then runs every step eagerly from here on."""
+    engine.use_cuda_graph = False
+    torch.cuda.synchronize(engine.device)
+    print(f"[llm_infer_engine_b200] {what} could not be captured as a CUDA graph ({type(exc).__name__}: "
+          f"{str(exc).splitlines()[0] if str(exc) else ''}); steps run eagerly from here on", file=sys.stderr)
 
 
 class DecodeGraph:

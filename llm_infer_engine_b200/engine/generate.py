@@ -179,10 +179,13 @@ def _run_batch(engine, prompts, batch, outputs, max_new_tokens, sampling, stop, 
                 longest = max(cache.lengths[s] for s in live_slots) + 1
                 if graph is None or graph.n != lanes or longest > graph.kv_limit:
                     # the upload of the tokens, the draw and the download of the drawn tokens are part of
-                    # the captured step: one launch a step
-                    graph = engine.decode_graph(lanes, longest, sampling, host_io=True)
-                    in_view, out_view = graph.host_in.numpy(), graph.host_out.numpy()
+                    # the captured step: one launch a step. A model with a part that cannot be captured makes
+                    # this None and switches the engine to eager steps.
+                    graph = engine.try_decode_graph(lanes, longest, sampling, host_io=True)
                     changed = True
+                    if graph is not None:
+                        in_view, out_view = graph.host_in.numpy(), graph.host_out.numpy()
+            if engine.use_cuda_graph:
                 for s in live_slots:
                     cache.reserve(s, cache.lengths[s] + 1)
                 if changed:

@@ -245,6 +245,26 @@ def test_toy_architecture_steps_like_its_plain_restatement(toy_folder, dtype, to
     assert engine.cache.free_slots() == 4 and engine.cache.free_pages() == engine.cache.n_pages
 
 
+def test_a_part_that_cannot_be_captured_falls_back_to_eager_steps(toy_folder, capsys):
+    """The toy recurrent mixer reads lengths on the host in its forward, which no CUDA graph can record. An engine with
+    captured steps switched on (the default) notices at its first capture, says so once, and goes on eagerly: the
+    generated tokens are those of an engine that was eager from the start, and the cache is given back whole."""
+    from llm_infer_engine_b200 import Engine, generate
+    prompts = [helpers.random_tokens(TOY["vocab"], n, seed=90 + n) for n in (20, 5, 20)]
+    eager = Engine(toy_folder, dtype="float32", max_batch=2, max_tokens=64 * 4, cuda_graph=False)
+    want = generate(eager, prompts, max_new_tokens=6, stop_ids=[])
+    engine = Engine(toy_folder, dtype="float32", max_batch=2, max_tokens=64 * 4, cuda_graph=True)
+    got = generate(engine, prompts, max_new_tokens=6, stop_ids=[])
+    assert got == want
+    assert engine.use_cuda_graph is False
+    assert "could not be captured" in capsys.readouterr().err
+    # lone prompts of a repeating length would be captured too: they also simply run
+    again = generate(engine, [prompts[0], prompts[0], prompts[0]], max_new_tokens=3, stop_ids=[])
+    assert again[0] == again[1] == again[2] == want[0][:3]
+    engine.cache.check()
+    assert engine.cache.free_slots() == 2 and engine.cache.free_pages() == engine.cache.n_pages
+
+
 def test_state_is_reset_when_a_slot_is_used_again(toy_folder):
     from llm_infer_engine_b200 import Engine
     engine = Engine(toy_folder, dtype="float32", max_batch=1, max_tokens=64 * 4, cuda_graph=False)
