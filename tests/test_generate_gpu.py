@@ -263,3 +263,22 @@ def test_command_line_with_prompt_ids(tmp_path):
     ids = [int(x) for x in block.split()]
     want = plain_greedy(w, cfg, prompt, 6, stop=(2,))
     assert ids == want
+
+
+def test_one_captured_step_serves_every_sampling_setting():
+    """Temperature, top-p and seed live in device memory beside the captured step: calls with other settings reuse the
+    capture (a greedy and a drawing one per lane count and length bucket, however many settings come) and draw what an
+    engine that has seen only that setting draws."""
+    from llm_infer_engine_b200 import Engine, SamplingParams, generate
+    folder = helpers.model_folder("b", std=0.12)
+    cfg = helpers.read_config(folder)
+    prompts = [helpers.random_tokens(cfg["vocab_size"], n, seed=900 + n) for n in (7, 21)]
+    settings = [SamplingParams(0.8, 0.9, 1), SamplingParams(0.8, 0.9, 2), SamplingParams(1.3, 0.5, 2), SamplingParams(),
+                SamplingParams(0.3, 1.0, 77), SamplingParams(0.8, 0.9, 1)]
+    engine = Engine(folder, dtype="float32", max_batch=2)
+    outs = [generate(engine, prompts, 10, sp, stop_ids=[]) for sp in settings]
+    assert len(engine._graphs) == 2, sorted(engine._graphs)          # (2 lanes, 512, greedy) and (2 lanes, 512, draw)
+    assert outs[0] == outs[5] and outs[0] != outs[1]                  # the seed matters, and nothing else sticks
+    for sp, out in zip(settings, outs):
+        fresh = generate(Engine(folder, dtype="float32", max_batch=2), prompts, 10, sp, stop_ids=[])
+        assert out == fresh, sp
