@@ -258,8 +258,15 @@ def run_3b(n_layers: int, pk: dict, new_tokens: int = 256) -> dict:
     # warm-up with the same lengths: the sequences outgrow a captured step's length bucket on the way (2,048 to
     # 4,096), and capturing the next one belongs to start-up, not to the steps that are timed
     generate(engine, prompts, max_new_tokens=new_tokens, stop_ids=[])
-    stats = GenerationStats()
-    generate(engine, prompts, max_new_tokens=new_tokens, stop_ids=[], stats=stats)
+    # three timed runs, the median of each figure: the prompt step is a single eager step of 18 thousand tokens
+    # and its time scatters from run to run
+    runs = []
+    for _ in range(3):
+        st = GenerationStats()
+        generate(engine, prompts, max_new_tokens=new_tokens, stop_ids=[], stats=st)
+        runs.append(st)
+    stats = sorted(runs, key=lambda r: r.decode_seconds)[1]
+    stats.prefill_seconds = sorted(r.prefill_seconds for r in runs)[1]
     steps = stats.decode_steps
     mean_keys = sum(lens) + 16 * (steps + 1) / 2.0                               # keys all 16 hold, mean over the steps
     step_bytes = engine.weight_bytes_per_step() + engine.kv_bytes_per_token() * mean_keys
@@ -274,7 +281,7 @@ def run_3b(n_layers: int, pk: dict, new_tokens: int = 256) -> dict:
         "prefill_tok_s": round(stats.prefill_tokens / stats.prefill_seconds, 1),
         "prefill_ms": round(stats.prefill_seconds * 1e3, 3),
         "prefill_frac_bf16": round(flops / stats.prefill_seconds / (pk["bf16_tflops"] * 1e12), 4),
-        "path": "generate(): host tokens in and out every step",
+        "path": "generate(): host tokens in and out every step", "timed_runs": 3,
     }
     del engine
     torch.cuda.empty_cache()
