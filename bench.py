@@ -265,6 +265,8 @@ def run_3b(n_layers: int, pk: dict, new_tokens: int = 256) -> dict:
         st = GenerationStats()
         generate(engine, prompts, max_new_tokens=new_tokens, stop_ids=[], stats=st)
         runs.append(st)
+    print("[bench] 3B runs: prefill ms " + ", ".join(f"{r.prefill_seconds * 1e3:.1f}" for r in runs) + "; decode ms/step "
+          + ", ".join(f"{r.decode_seconds / r.decode_steps * 1e3:.3f}" for r in runs), file=sys.stderr)
     stats = sorted(runs, key=lambda r: r.decode_seconds)[1]
     stats.prefill_seconds = sorted(r.prefill_seconds for r in runs)[1]
     steps = stats.decode_steps
