@@ -72,10 +72,10 @@ def test_a_prompt_in_pieces_beside_one_token_sequences(tag, dtype, chunk):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("n_requests,lanes", [(13, 16), (40, 64)])
+@pytest.mark.parametrize("n_requests,lanes", [(13, 16), (40, 64), (130, 256)])
 def test_captured_steps_of_many_lanes(dtype, n_requests, lanes):
-    """13 sequences in a captured step of 16 lanes and 40 in one of 64 (the rest are padding lanes on the
-    scratch slot): the last 6 tokens of every request go through the captured step and are compared with
+    """13 sequences in a captured step of 16 lanes, 40 in one of 64 and 130 in one of 256 (the rest are padding
+    lanes on the scratch slot): the last 6 tokens of every request go through the captured step and are compared with
     the plain implementation and, in float32, bit for bit with the same steps run eagerly."""
     tag, tail = "c", 6
     g = torch.Generator().manual_seed(n_requests)
