@@ -117,10 +117,13 @@ def _check(status: int, name: str) -> None:
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
+_get_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> int:
     """The current CUDA stream of the current device as a raw handle."""
     if _raw_stream is not None:
-        return _raw_stream(torch.cuda.current_device())
+        return _raw_stream(_get_device() if _get_device is not None else torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -132,15 +135,24 @@ def _dt(t: torch.Tensor, what: str) -> int:
 
 
 def _need(t: torch.Tensor, what: str, dtype=None, shape=None) -> None:
+    """The checks every launch makes of every tensor it is given (written for speed: an eager step makes
+    several hundred of them)."""
     if not t.is_cuda:
         raise KernelError(f"{what}: must be a CUDA tensor (this library has no CPU path)")
     if not t.is_contiguous():
         raise KernelError(f"{what}: must be contiguous")
-    if dtype is not None and t.dtype != dtype:
+    if dtype is not None and t.dtype is not dtype:
         raise KernelError(f"{what}: dtype {t.dtype}, expected {dtype}")
     if shape is not None:
-        if t.dim() != len(shape) or any(s is not None and s != a for s, a in zip(shape, t.shape)):
-            raise KernelError(f"{what}: shape {tuple(t.shape)}, expected {tuple(shape)}")
+        have = t.shape
+        bad = len(have) != len(shape)
+        if not bad:
+            for want, got in zip(shape, have):
+                if want is not None and want != got:
+                    bad = True
+                    break
+        if bad:
+            raise KernelError(f"{what}: shape {tuple(have)}, expected {tuple(shape)}")
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:

@@ -124,6 +124,15 @@ AWKWARD = [
          rope_scaling={"rope_type": "llama3", "factor": 2.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                        "original_max_position_embeddings": 32},
          rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=150),
+    # sizes the tensor-core kernels DO take, at their edges: 20 query heads on one KV head of 64 (two chunks of 16
+    # query heads per KV head in the decode attention, only the first of which writes the cache) ...
+    dict(num_hidden_layers=2, hidden_size=128, num_attention_heads=20, num_key_value_heads=1, head_dim=64,
+         intermediate_size=160, vocab_size=300, rope_theta=10000.0, rope_scaling=None, rms_norm_eps=1e-5,
+         tie_word_embeddings=True, max_position_embeddings=200),
+    # ... and as many KV heads as query heads, head size 128
+    dict(num_hidden_layers=1, hidden_size=64, num_attention_heads=3, num_key_value_heads=3, head_dim=128,
+         intermediate_size=96, vocab_size=200, rope_theta=10000.0, rope_scaling=None, rms_norm_eps=1e-5,
+         tie_word_embeddings=False, max_position_embeddings=200),
     # a width, a feed-forward width and a vocabulary that are no multiples of 8: no 16-byte loads anywhere
     dict(num_hidden_layers=2, hidden_size=100, num_attention_heads=5, num_key_value_heads=5, head_dim=16,
          intermediate_size=60, vocab_size=51, rope_theta=10000.0, rope_scaling=None, rms_norm_eps=1e-5,
@@ -132,22 +141,24 @@ AWKWARD = [
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", [0, 1, 2, 3])
-def test_sizes_that_fit_no_fast_kernel(which, dtype):
-    """Head sizes in steps of 16 that the tensor-core kernels do not take, widths that are no multiples of 16, an odd
-    vocabulary, any number of heads and groups: the plain kernels of the same math serve them (or the engine refuses
-    with a clear error; it never gives a wrong result). Whole, one by one, in batches, in pieces."""
+@pytest.mark.parametrize("which", [0, 1, 2, 3, 4, 5])
+def test_unusual_sizes(which, dtype):
+    """Head sizes in steps of 16 that the tensor-core kernels do not take, widths that are no multiples of 16 or 8, an
+    odd vocabulary, any number of heads and groups (the plain kernels of the same math serve them), and the edges of
+    what the tensor-core kernels do take (more than 16 query heads per KV head, one query head per KV head). Whole, one
+    by one, in batches of 3 and of 10, in pieces; never a wrong result."""
     from llm_infer_engine_b200 import Engine, write_random_model
     cfg = dict(plain.TINY_A, **AWKWARD[which])
     folder = helpers.scratch_folder("llmie_awkward_")
     write_random_model(cfg, folder, seed=20 + which, std=0.08, norm_range=(0.8, 1.2))
     w = helpers.plain_weights(folder)
-    lens = [l for l in (1, 9, 64, 65, 130) if l <= cfg["max_position_embeddings"]]
+    lens = [l for l in (1, 9, 64, 65, 130, 12, 31, 100, 7, 50) if l <= cfg["max_position_embeddings"]]
     requests = {f"k{i}": helpers.random_tokens(cfg["vocab_size"], n, seed=50 + i) for i, n in enumerate(lens)}
     want = {rid: plain.logits(w, cfg, toks) for rid, toks in requests.items()}
-    engine = Engine(folder, dtype=dtype, max_batch=3, max_tokens=64 * 8, cuda_graph=False)
+    engine = Engine(folder, dtype=dtype, max_batch=10, max_tokens=64 * 24, cuda_graph=False)
+    # batches of 3 and of 10: one-token steps of up to 8 rows and of more take different kernels
     for plan in (helpers.plan_whole(requests), helpers.plan_tail(requests, 32), helpers.plan_batched(requests, 3),
-                 helpers.plan_chunked(requests, 33)):
+                 helpers.plan_batched(requests, 10), helpers.plan_chunked(requests, 33)):
         check(helpers.run_plan_engine(engine, plan), want, dtype, f"awkward {which}/{dtype}")
     # and through the captured step and the loop
     from llm_infer_engine_b200 import generate
