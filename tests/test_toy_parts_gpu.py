@@ -281,12 +281,13 @@ def test_state_is_reset_when_a_slot_is_used_again(toy_folder):
 # ------------------------------------------------------------------------------------------ other arrangements
 # A second toy architecture for the edges of the part interfaces: a block with THREE norms (one of them on the
 # mixer's output), a block with TWO mixers behind ONE shared norm whose three branches run in parallel (its
-# cache unit holds keys and values for one mixer and a state for the other), learned absolute positions and a
+# cache unit holds keys and values for one mixer and a state for the other), another position encoding (pairs of
+# neighbouring elements, written with plain tensor code including its cache write), learned absolute positions and a
 # scale right after the embedding, and a cap on the logits after the head. All of it is defined here.
 def _register_arrangements():
     from llm_infer_engine_b200.config import LayerCall, LayerSpec, ModelSpec, PartSpec, register_architecture
-    from llm_infer_engine_b200.parts import (Block, ParamSpec, Pointwise, call_branch, register_block,
-                                             register_pointwise)
+    from llm_infer_engine_b200.parts import (Block, ParamSpec, Pointwise, PositionEncoding, call_branch,
+                                             register_block, register_pointwise, register_position_encoding)
 
     class SandwichBlock(Block):
         """h += post_norm(mixer(norm(h))); h += feed_forward(norm(h))."""
@@ -330,6 +331,38 @@ def _register_arrangements():
             cap = float(self.params["cap"])
             return cap * torch.tanh(x / cap)
 
+    class InterleavedRotary(PositionEncoding):
+        """Another position encoding: neighbouring elements (2i, 2i + 1) of a head are rotated as a pair (the
+        library's own pairs element i with i + head_dim / 2), written with plain tensor code, the cache write
+        included: the page of every token is looked up in the unit's block table."""
+
+        def __init__(self, params, runtime):
+            super().__init__(params, runtime)
+            self.theta = float(params["theta"])
+
+        def encode_and_store(self, qkv, ctx, kv, n_q, n_kv, head_dim, write_kv):
+            T = qkv.shape[0]
+            inv = 1.0 / (self.theta ** (torch.arange(0, head_dim, 2, device=qkv.device).float() / head_dim))
+            angle = ctx.tok_pos.float()[:, None] * inv[None, :]                   # [T, hd / 2]
+            cos, sin = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+
+            def turn(x):                                                           # [T, heads, hd]
+                x = x.float()
+                even, odd = x[..., 0::2], x[..., 1::2]
+                return torch.stack([even * cos - odd * sin, odd * cos + even * sin], dim=-1).flatten(-2).to(qkv.dtype)
+
+            q = turn(qkv[:, :n_q * head_dim].view(T, n_q, head_dim))
+            if write_kv:
+                k = turn(qkv[:, n_q * head_dim:(n_q + n_kv) * head_dim].view(T, n_kv, head_dim))
+                v = qkv[:, (n_q + n_kv) * head_dim:].view(T, n_kv, head_dim)
+                pos = ctx.tok_pos.long()
+                slot = ctx.seq_slot.long()[ctx.tok_seq.long()]
+                page = kv.block_table[slot, pos // kv.page_size].long()
+                kv.k[page, :, pos % kv.page_size] = k
+                kv.v[page, :, pos % kv.page_size] = v
+            return q.reshape(T, n_q * head_dim).contiguous()
+
+    register_position_encoding("toy_interleaved_rotary", InterleavedRotary)
     register_block("toy_sandwich", SandwichBlock)
     register_block("toy_parallel", ParallelBlock)
     register_pointwise("toy_scale_positions", ScaleAndPositions)
@@ -352,6 +385,11 @@ def _register_arrangements():
                                                                      "scaling": None})})
         rec = PartSpec("toy_decay", {"hidden": c["hidden"], "width": c["width"], "decay": c["decay"]})
         ff = PartSpec("swiglu", {"hidden": c["hidden"], "intermediate": c["inner"]})
+        attn2 = PartSpec("gqa_attention", dict(attn.params, position=PartSpec("toy_interleaved_rotary", {"theta": 50.0})))
+        sandwich2 = LayerSpec("toy_sandwich", parts={"mixer": attn2, "feed_forward": ff, "mixer_norm": norm,
+                                                      "mixer_post_norm": norm, "feed_forward_norm": norm},
+                              names={"mixer": "mix", "feed_forward": "ff", "mixer_norm": "n1", "mixer_post_norm": "n1b",
+                                     "feed_forward_norm": "n2"})
         sandwich = LayerSpec("toy_sandwich", parts={"mixer": attn, "feed_forward": ff, "mixer_norm": norm,
                                                      "mixer_post_norm": norm, "feed_forward_norm": norm},
                              names={"mixer": "mix", "feed_forward": "ff", "mixer_norm": "n1", "mixer_post_norm": "n1b",
@@ -359,7 +397,7 @@ def _register_arrangements():
         parallel = LayerSpec("toy_parallel", parts={"attn": attn, "rec": rec, "feed_forward": ff, "norm": norm},
                              names={"attn": "attn", "rec": "rec", "feed_forward": "ff", "norm": "n"})
         return ModelSpec(hidden_size=c["hidden"], vocab_size=c["vocab"], max_position=c["max_pos"],
-                         layers=[sandwich, parallel, sandwich], schedule=[LayerCall(0), LayerCall(1), LayerCall(2)],
+                         layers=[sandwich, parallel, sandwich2], schedule=[LayerCall(0), LayerCall(1), LayerCall(2)],
                          final_norm=norm, tie_head=False, embedding_name="emb.weight", layer_prefix="blocks.{i}.",
                          final_norm_name="final", head_name="head.weight",
                          after_embedding=PartSpec("toy_scale_positions", {"scale": c["emb_scale"], "hidden": c["hidden"],
@@ -378,9 +416,17 @@ def arrangements_plain_logits(w, cfg, tokens):
     cos, sin = plain.rotation_tables(torch.arange(T), plain.inv_frequencies(hd, 100.0, None))
     norm = lambda x, name: plain.rms_norm(x, w[name + ".weight"], cfg["eps"])
 
-    def attention(x, p):
-        q = plain.rotate_half((x @ w[p + "q_proj.weight"].T).view(T, H, hd).transpose(0, 1), cos, sin)
-        k = plain.rotate_half((x @ w[p + "k_proj.weight"].T).view(T, Hkv, hd).transpose(0, 1), cos, sin)
+    inv2 = 1.0 / (50.0 ** (torch.arange(0, hd, 2).float() / hd))
+    cos2, sin2 = torch.cos(torch.arange(T).float()[:, None] * inv2), torch.sin(torch.arange(T).float()[:, None] * inv2)
+
+    def pairs(x):                                           # [heads, T, hd]: elements (2i, 2i + 1) turn together
+        even, odd = x[..., 0::2], x[..., 1::2]
+        return torch.stack([even * cos2 - odd * sin2, odd * cos2 + even * sin2], dim=-1).flatten(-2)
+
+    def attention(x, p, turn=None):
+        turn = turn or (lambda t: plain.rotate_half(t, cos, sin))
+        q = turn((x @ w[p + "q_proj.weight"].T).view(T, H, hd).transpose(0, 1))
+        k = turn((x @ w[p + "k_proj.weight"].T).view(T, Hkv, hd).transpose(0, 1))
         v = (x @ w[p + "v_proj.weight"].T).view(T, Hkv, hd).transpose(0, 1)
         return plain.causal_gqa_attention(q, k, v).transpose(0, 1).reshape(T, H * hd) @ w[p + "o_proj.weight"].T
 
@@ -403,7 +449,7 @@ def arrangements_plain_logits(w, cfg, tokens):
             x = norm(h, p + "n")
             h = h + attention(x, p + "attn.") + recurrent(x, p + "rec.") + swiglu(x, p + "ff.")
         else:
-            h = h + norm(attention(norm(h, p + "n1"), p + "mix."), p + "n1b")
+            h = h + norm(attention(norm(h, p + "n1"), p + "mix.", pairs if layer == 2 else None), p + "n1b")
             h = h + swiglu(norm(h, p + "n2"), p + "ff.")
     logits = norm(h, "final") @ w["head.weight"].T
     return cfg["cap"] * torch.tanh(logits / cfg["cap"])
