@@ -11,14 +11,21 @@
 // One block = 128 consecutive query tokens of one sequence and one query head, 320 threads:
 //   warp 0      TMA producer: the Q tile once, then for every tile of 128 keys the two cache pages
 //               of K and of V ([64 keys, hd] each) into their stages
-//   warp 1      owns TMEM (score buffer(s) of 128 columns, one P.V buffer of hd); one lane issues
-//               S = Q K^T for the NEXT key tile as soon as its buffer is free, then O_j = P_j V_j
+//   warp 1      owns TMEM (two score buffers of 128 columns); one lane issues S = Q K^T two key
+//               tiles ahead, as soon as a buffer is free, and O_j = P_j V_j when P_j is there
 //   warps 2..9  softmax, two threads per query row (each half of a key tile's columns and half of
 //               the output's): read S from TMEM (tcgen05.ld), mask, running max and sum, write P
-//               as bfloat16 into shared memory in the tensor core's swizzled operand layout, then
-//               add the P.V tile to the output kept in registers
+//               as bfloat16 into shared memory in the tensor core's swizzled operand layout; the
+//               P.V tile of the PREVIOUS key tile is added to the output kept in registers in the
+//               middle of this work, so that no thread ever waits for the second product
 // V is used as an MN-major B operand (rows of the cache are keys, i.e. the K dimension of P.V),
 // so nothing is transposed. Every barrier wait is bounded (tcgen05.cuh).
+//
+// Registers: a block has 10 warps, which the SM deals to its four schedulers in turn, so a scheduler
+// may get three warps of each of two blocks. With more than 85 registers a thread (16,384 a scheduler
+// / 6 warps / 32) a new block then finds no room beside a running one although half the SM is free,
+// and the SM is refilled only when both of its blocks have ended: the head-size-64 kernel, which
+// wants two blocks an SM, is therefore held at 80.
 #include "tcgen05.cuh"
 #include <math.h>
 
@@ -33,15 +40,18 @@ constexpr int kSubTileBytes = 128 * 128;   // [128 rows x 64 bf16], 16 KB
 
 template <int HD> struct AttnCfg {
   static constexpr int kSub = HD / 64;                       // 64-wide blocks of the head dimension
-  // head size 64: two blocks share an SM (each 256 TMEM columns, 97 KB), so one block's softmax
-  // overlaps the other's MMAs; one score buffer and one V stage per block suffice.
-  // head size 128: one block per SM; two score buffers let S of the next key tile be computed
-  // while the softmax of the current one runs.
-  static constexpr int kSBufs = HD == 64 ? 1 : 2;
+  // Two score buffers: S of the next key tile is computed while the softmax of the current one runs.
+  // head size 64: two blocks share an SM (each 256 TMEM columns, 97 KB). The two score buffers fill the 256
+  // columns, so the P.V tile of key tile j is written over S_j, which nobody reads any more once P_j is
+  // complete; the buffer is free for S_j+2 when the P.V tile has been read out.
+  // head size 128: one block per SM, 512 columns: the P.V tile has columns of its own.
+  static constexpr int kSBufs = 2;
+  static constexpr bool kPvAlias = HD == 64;
   static constexpr int kKStages = 2;
   static constexpr int kVStages = HD == 64 ? 1 : 2;
   static constexpr int kTmemCols = HD == 64 ? 256 : 512;
-  static constexpr int kPvCol = kSBufs * 128;                // TMEM column of the P.V tile
+  static constexpr int kPvCol = 256;                         // TMEM column of the P.V tile if it has its own
+  static constexpr int kMaxRegs = HD == 64 ? 80 : 168;   // 168: three warps of a block on one scheduler
   static constexpr int kQBytes = kSub * kSubTileBytes;
   static constexpr int kKvBytes = kSub * kSubTileBytes;      // one K (or V) tile of 128 keys
   static constexpr int kPBytes = 2 * kSubTileBytes;          // P: [128 rows x 128 keys] bf16
@@ -77,7 +87,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 }
 
 template <int HD>
-__global__ void __launch_bounds__(kAttnThreads, (HD == 64 ? 2 : 1))
+__global__ void __maxnreg__(AttnCfg<HD>::kMaxRegs)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                             const int* __restrict__ cu_q, const int* __restrict__ seq_slot,
@@ -109,6 +119,35 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int tile_lo = first_key / kKTile, tile_hi = last_key / kKTile;
   const int n_tiles = tile_hi - tile_lo + 1;
 
+  // One thread is the TMA producer. K and V of a key tile are the two cache pages that hold its 128 keys.
+  const int* pages = block_table + (size_t)seq_slot[seq] * max_pages;
+  auto load_k = [&](int jt) {
+    const int ks = jt % Cfg::kKStages;
+    const int lp = (tile_lo + jt) * 2;           // logical pages of this key tile
+    const int last_page = last_key / 64;         // pages beyond the sequence's last key are not mapped
+    const int pg0 = pages[lp];
+    const int pg1 = (lp + 1 <= last_page && lp + 1 < max_pages) ? pages[lp + 1] : scratch_page;
+    uint8_t* kd = k_smem + ks * Cfg::kKvBytes;
+    mbar_arrive_expect_tx(&sh.k_full[ks], Cfg::kKvBytes);
+    for (int sub = 0; sub < Cfg::kSub; ++sub) {
+      tma_load_2d(kd + sub * kSubTileBytes, &map_k, sub * 64, (pg0 * n_kv + hk) * 64, &sh.k_full[ks]);
+      tma_load_2d(kd + sub * kSubTileBytes + 8192, &map_k, sub * 64, (pg1 * n_kv + hk) * 64, &sh.k_full[ks]);
+    }
+  };
+  auto load_v = [&](int jt) {
+    const int vs = jt % Cfg::kVStages;
+    const int lp = (tile_lo + jt) * 2;
+    const int last_page = last_key / 64;
+    const int pg0 = pages[lp];
+    const int pg1 = (lp + 1 <= last_page && lp + 1 < max_pages) ? pages[lp + 1] : scratch_page;
+    uint8_t* vd = v_smem + vs * Cfg::kKvBytes;
+    mbar_arrive_expect_tx(&sh.v_full[vs], Cfg::kKvBytes);
+    for (int sub = 0; sub < Cfg::kSub; ++sub) {
+      tma_load_2d(vd + sub * kSubTileBytes, &map_v, sub * 64, (pg0 * n_kv + hk) * 64, &sh.v_full[vs]);
+      tma_load_2d(vd + sub * kSubTileBytes + 8192, &map_v, sub * 64, (pg1 * n_kv + hk) * 64, &sh.v_full[vs]);
+    }
+  };
+
   if (threadIdx.x == 0) {
     mbar_init(&sh.q_full, 1);
     for (int s = 0; s < 2; ++s) {
@@ -126,6 +165,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     for (int i = 0; i < 4; ++i) mbar_init(&sh.pair_bar[i], 64);
     sh.abort = 0;
     fence_mbar_init();
+    // The first loads leave at once, while warp 1 still asks for tensor memory: only this thread touches the
+    // barriers they complete on until the block has met below.
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
+    mbar_arrive_expect_tx(&sh.q_full, Cfg::kQBytes);
+    for (int sub = 0; sub < Cfg::kSub; ++sub)
+      tma_load_2d(q_smem + sub * kSubTileBytes, &map_q, head * HD + sub * 64, q_begin + t0, &sh.q_full);
+    load_k(0);
+    load_v(0);
   }
   if (warp == 1) {
     tmem_alloc(&sh.tmem_base, Cfg::kTmemCols);
@@ -139,43 +188,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #define LLMIE_FAIL(code) do { if (!*abort) { *abort = 1; atomicExch(status, (code)); } } while (0)
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    if (elect_one()) {
-      tma_prefetch_desc(&map_q);
-      tma_prefetch_desc(&map_k);
-      tma_prefetch_desc(&map_v);
-      mbar_arrive_expect_tx(&sh.q_full, Cfg::kQBytes);
-      for (int sub = 0; sub < Cfg::kSub; ++sub)
-        tma_load_2d(q_smem + sub * kSubTileBytes, &map_q, head * HD + sub * 64, q_begin + t0, &sh.q_full);
-      const int* pages = block_table + (size_t)seq_slot[seq] * max_pages;
-      int issued = 0;
-      for (int jt = 0; jt < n_tiles; ++jt) {
+    // ------------------------------------------------------------------ TMA producer (tile 0 is on its way)
+    if (lane == 0) {
+      int issued = 1;
+      for (int jt = 1; jt < n_tiles; ++jt) {
         const int ks = jt % Cfg::kKStages, vs = jt % Cfg::kVStages;
-        const int lp = (tile_lo + jt) * 2;         // logical pages of this key tile
-        const int last_page = last_key / 64;       // pages beyond the sequence's last key are not mapped
-        const int pg0 = pages[lp];
-        const int pg1 = (lp + 1 <= last_page && lp + 1 < max_pages) ? pages[lp + 1] : scratch_page;
         if (jt >= Cfg::kKStages && !mbar_wait(&sh.k_empty[ks], ((jt / Cfg::kKStages) - 1) & 1, abort)) {
           LLMIE_FAIL(kStatusTimeoutEmpty);
           break;
         }
-        uint8_t* kd = k_smem + ks * Cfg::kKvBytes;
-        mbar_arrive_expect_tx(&sh.k_full[ks], Cfg::kKvBytes);
-        for (int sub = 0; sub < Cfg::kSub; ++sub) {
-          tma_load_2d(kd + sub * kSubTileBytes, &map_k, sub * 64, (pg0 * n_kv + hk) * 64, &sh.k_full[ks]);
-          tma_load_2d(kd + sub * kSubTileBytes + 8192, &map_k, sub * 64, (pg1 * n_kv + hk) * 64, &sh.k_full[ks]);
-        }
+        load_k(jt);
         if (jt >= Cfg::kVStages && !mbar_wait(&sh.v_empty[vs], ((jt / Cfg::kVStages) - 1) & 1, abort)) {
           LLMIE_FAIL(kStatusTimeoutEmpty);
           issued = jt + 1;                         // K of this tile is in flight
           break;
         }
-        uint8_t* vd = v_smem + vs * Cfg::kKvBytes;
-        mbar_arrive_expect_tx(&sh.v_full[vs], Cfg::kKvBytes);
-        for (int sub = 0; sub < Cfg::kSub; ++sub) {
-          tma_load_2d(vd + sub * kSubTileBytes, &map_v, sub * 64, (pg0 * n_kv + hk) * 64, &sh.v_full[vs]);
-          tma_load_2d(vd + sub * kSubTileBytes + 8192, &map_v, sub * 64, (pg1 * n_kv + hk) * 64, &sh.v_full[vs]);
-        }
+        load_v(jt);
         issued = jt + 1;
       }
       if (*abort) {   // let copies that are still in flight land before the block gives its memory up
@@ -212,12 +240,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         return true;
       };
       if (ok) ok = issue_scores(0);
+      if (ok && n_tiles > 1) ok = issue_scores(1);
       for (int jt = 0; ok && jt < n_tiles; ++jt) {
-        // Two score buffers: the next tile's scores first, they need nothing of this tile's softmax. One buffer:
-        // the next scores have to wait for the softmax to let go of it, which is when P is ready too, and the
-        // softmax threads then wait for P.V, so P.V goes first.
-        if (Cfg::kSBufs > 1 && jt + 1 < n_tiles && !issue_scores(jt + 1)) break;
         const int vs = jt % Cfg::kVStages;
+        const uint32_t pv_col = Cfg::kPvAlias ? (uint32_t)(jt & 1) * 128 : (uint32_t)Cfg::kPvCol;
         if (!mbar_wait(&sh.p_ready, jt & 1, abort)) { LLMIE_FAIL(kStatusTimeoutMma); break; }
         if (!mbar_wait(&sh.v_full[vs], (jt / Cfg::kVStages) & 1, abort)) { LLMIE_FAIL(kStatusTimeoutFull); break; }
         tc_fence_after_sync();
@@ -227,11 +253,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           // A = P, K-major: 16 keys = 32 bytes inside a 64-key sub-tile. B = V, MN-major: 16 keys = 16 rows.
           const uint64_t dp = make_smem_desc(p_addr + (kk >> 2) * kSubTileBytes + (kk & 3) * 32, 16, 1024);
           const uint64_t dv = make_smem_desc(v_addr + kk * 2048, kSubTileBytes, 1024);
-          mma_bf16_ss(tmem + Cfg::kPvCol, dp, dv, idesc_pv, kk > 0 ? 1u : 0u);
+          mma_bf16_ss(tmem + pv_col, dp, dv, idesc_pv, kk > 0 ? 1u : 0u);
         }
         mma_commit(&sh.pv_full);
         mma_commit(&sh.v_empty[vs]);
-        if (Cfg::kSBufs == 1 && jt + 1 < n_tiles && !issue_scores(jt + 1)) break;
+        // the scores two tiles ahead go into the buffer of this tile, once the softmax threads have let go of it
+        if (jt + 2 < n_tiles && !issue_scores(jt + 2)) break;
       }
     }
   } else {
@@ -263,6 +290,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       ++n_exchanges;
       return ok_;
     };
+    // Adds the P.V tile of key tile j to the output, which is first brought to that tile's maximum by alpha_j.
+    // The whole warp calls it together, after it has seen pv_full for this tile.
+    auto add_pv = [&](int j, float alpha_j) {
+      tc_fence_after_sync();
+      const uint32_t col = Cfg::kPvAlias ? (uint32_t)(j & 1) * 128 : (uint32_t)Cfg::kPvCol;
+#pragma unroll
+      for (int c0 = 0; c0 < kOut; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(lane_addr + col + half * kOut + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha_j, __uint_as_float(v[i]));
+      }
+      tc_fence_before_sync();                  // our TMEM reads are done before the arrival below counts
+      if (Cfg::kPvAlias) mbar_arrive(&sh.s_free[j & 1]);     // the buffer may take the scores of tile j + 2
+    };
+    float alpha_prev = 1.f;                    // alpha of the tile whose P.V tile has not been added yet
     for (int jt = 0; jt < n_tiles; ++jt) {
       const int b = jt % Cfg::kSBufs;
       // every decision to give up is taken by the whole warp: the tensor-memory reads below are warp-wide
@@ -276,23 +320,29 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // (four running maxima and, below, four running sums: one chain of 64 dependent operations would be
       // what a row's time consists of)
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      const int lo_rel = lo - kbase;
 #pragma unroll
       for (int c0 = 0; c0 < kCols; c0 += 32) {
         uint32_t v[32];
         tmem_ld_32x32(lane_addr + b * 128 + half * kCols + c0, v);
         tmem_ld_wait();
         if (edge) {
+          // A tile that the causal line or the window's far end crosses: the scores this row may not see become
+          // -inf here, in tensor memory too, so that the second pass is the same for every tile (2^-inf = 0).
+          // Column c of this thread's half is seen if lo <= kbase + c <= qpos: one unsigned comparison.
+          const unsigned span = (unsigned)(qpos - lo);
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const int key = kbase + c0 + i;
-            const float s = (key > qpos || key < lo) ? -INFINITY : __uint_as_float(v[i]);
-            mx[i & 3] = fmaxf(mx[i & 3], s);
+            if ((unsigned)(c0 + i - lo_rel) > span) v[i] = 0xff800000u;
+            mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(v[i]));
           }
+          tmem_st_32x32(lane_addr + b * 128 + half * kCols + c0, v);
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(v[i]));
         }
       }
+      if (edge) tmem_st_wait();
       float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       float other;
       if (!__all_sync(0xffffffffu, exchange(m_tile, other))) { LLMIE_FAIL(kStatusTimeoutMma); ok = false; break; }
@@ -303,54 +353,51 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const float m_scaled = m_use * sl2;
       // pass 2: probabilities, their sum, and P in bfloat16 into the swizzled operand tile
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int c0 = 0; c0 < kCols; c0 += 32) {
+      // 32 keys from column c0 of this thread's half: probabilities, summed and packed two to a word
+      auto probabilities = [&](int c0, uint32_t (&w)[16]) {
         uint32_t v[32];
         tmem_ld_32x32(lane_addr + b * 128 + half * kCols + c0, v);
         tmem_ld_wait();
         float p[32];
-        if (edge) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = kbase + c0 + i;
-            const float e = exp2_approx(fmaf(__uint_as_float(v[i]), sl2, -m_scaled));
-            p[i] = (key > qpos || key < lo) ? 0.f : e;
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) p[i] = exp2_approx(fmaf(__uint_as_float(v[i]), sl2, -m_scaled));
-        }
+        for (int i = 0; i < 32; ++i) p[i] = exp2_approx(fmaf(__uint_as_float(v[i]), sl2, -m_scaled));
 #pragma unroll
         for (int i = 0; i < 32; ++i) ls[i & 3] += p[i];
 #pragma unroll
+        for (int i = 0; i < 16; ++i) w[i] = pack_bf16(p[2 * i], p[2 * i + 1]);
+      };
+      auto store_p = [&](int c0, const uint32_t (&w)[16]) {
+#pragma unroll
         for (int ch = 0; ch < 4; ++ch) {                 // four 16-byte chunks of 8 keys
           const int chunk = ((half * kCols + c0) >> 3) + ch;       // 0..15 within the 128 keys
-          uint4 w;
-          w.x = pack_bf16(p[ch * 8 + 0], p[ch * 8 + 1]);
-          w.y = pack_bf16(p[ch * 8 + 2], p[ch * 8 + 3]);
-          w.z = pack_bf16(p[ch * 8 + 4], p[ch * 8 + 5]);
-          w.w = pack_bf16(p[ch * 8 + 6], p[ch * 8 + 7]);
-          *reinterpret_cast<uint4*>(p_smem + (chunk >> 3) * kSubTileBytes + swizzle128_offset(r, chunk & 7)) = w;
+          const uint4 q4 = make_uint4(w[ch * 4 + 0], w[ch * 4 + 1], w[ch * 4 + 2], w[ch * 4 + 3]);
+          *reinterpret_cast<uint4*>(p_smem + (chunk >> 3) * kSubTileBytes + swizzle128_offset(r, chunk & 7)) = q4;
         }
+      };
+      static_assert(kCols == 64, "two chunks of 32 keys a thread");
+      {
+        // The first 32 probabilities are worked out while the tensor core may still be reading the previous P
+        // for its P.V product; they go to shared memory once that product is done. Its tile is then added to
+        // the output here, in the middle of this tile's work, where it is long complete: no thread waits for it.
+        uint32_t w[16];
+        probabilities(0, w);
+        if (jt > 0 && !__all_sync(0xffffffffu, mbar_wait(&sh.pv_full, (jt - 1) & 1, abort))) { LLMIE_FAIL(kStatusTimeoutMma); ok = false; break; }
+        store_p(0, w);
+        if (jt > 0) add_pv(jt - 1, alpha_prev);
+        probabilities(32, w);
+        store_p(32, w);
       }
-      tc_fence_before_sync();                  // our TMEM reads of S are done before the barrier is passed
-      mbar_arrive(&sh.s_free[b]);
+      tc_fence_before_sync();                  // our TMEM reads of S are done before the barriers are passed
+      if (!Cfg::kPvAlias) mbar_arrive(&sh.s_free[b]);
       fence_proxy_async_smem();                // P is visible to the tensor core's reads
       mbar_arrive(&sh.p_ready);
-      // the P.V tile for these keys: this thread's half of the head dimension
-      if (!__all_sync(0xffffffffu, mbar_wait(&sh.pv_full, jt & 1, abort))) { LLMIE_FAIL(kStatusTimeoutMma); ok = false; break; }
-      tc_fence_after_sync();
-#pragma unroll
-      for (int c0 = 0; c0 < kOut; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(lane_addr + Cfg::kPvCol + half * kOut + c0, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha, __uint_as_float(v[i]));
-      }
       l_run = fmaf(l_run, alpha, (ls[0] + ls[1]) + (ls[2] + ls[3]));
       m_run = m_new;
-      tc_fence_before_sync();                  // ordered before the next arrival on p_ready
+      alpha_prev = alpha;
+    }
+    if (ok) {
+      if (__all_sync(0xffffffffu, mbar_wait(&sh.pv_full, (n_tiles - 1) & 1, abort))) add_pv(n_tiles - 1, alpha_prev);
+      else { LLMIE_FAIL(kStatusTimeoutMma); ok = false; }
     }
     // the row's sum is the two halves' sums (both were kept relative to the same running maximum)
     if (ok) {
@@ -416,6 +463,7 @@ extern "C" int llmie_attention_prefill_tc_supported(int hd, int page_size) {
 // caches: bfloat16 [n_pages_total, n_kv, 64, hd]; the LAST page (n_pages_total - 1) is a scratch
 // page that may be read for key positions nobody holds. seq_start[i]: tokens sequence i held
 // before this step (its new keys are already in the cache). max_q_len: longest new run, for the grid.
+// scale must be positive.
 extern "C" int llmie_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out,
                                           const int* cu_q, const int* seq_slot, const int* seq_start,
                                           const int* block_table, int max_pages, int n_pages_total, int n_tokens,
@@ -423,6 +471,7 @@ extern "C" int llmie_attention_prefill_tc(const void* q, const void* k_cache, co
                                           int* status, cudaStream_t stream) {
   if (n_tokens < 0 || n_seqs < 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv || max_pages <= 0 || n_pages_total <= 0)
     return LLMIE_ERR_BAD_ARG;
+  if (!(scale > 0.f)) return LLMIE_ERR_BAD_ARG;   // the running maximum is taken before the scores are scaled
   if (!aligned16(q) || !aligned16(out) || !aligned16(k_cache) || !aligned16(v_cache)) return LLMIE_ERR_ALIGNMENT;
   if (n_tokens == 0 || n_seqs == 0 || max_q_len <= 0) return LLMIE_OK;
   if (n_seqs > 65535 || n_q > 65535) return LLMIE_ERR_UNSUPPORTED_SIZE;

@@ -72,7 +72,7 @@ class KernelPlan:
             ops.attention_decode(q, kv.k, kv.v, out, ctx.seq_slot, ctx.seq_kvlen, kv.block_table, kv.page_size,
                                  n_q, n_kv, head_dim, scale, window, run, n_runs, counters=counters)
             return True
-        if not ctx.decode and ops.attention_prefill_tc_supported(head_dim, kv.page_size, q.dtype):
+        if not ctx.decode and scale > 0 and ops.attention_prefill_tc_supported(head_dim, kv.page_size, q.dtype):
             ops.attention_prefill_tc(q, kv.k, kv.v, out, ctx.cu_q, ctx.seq_slot, ctx.seq_start, kv.block_table,
                                      kv.page_size, ctx.n_seqs, ctx.max_q_len, n_q, n_kv, head_dim, scale, window)
             return True

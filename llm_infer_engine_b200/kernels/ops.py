@@ -631,6 +631,8 @@ def attention_prefill_tc(q, k_cache, v_cache, out, cu_q, seq_slot, seq_start, bl
         raise KernelError(f"attention_prefill_tc: head_dim {head_dim} / page size {page_size} is not supported")
     if cu_q.numel() < n_seqs + 1 or seq_slot.numel() < n_seqs or seq_start.numel() < n_seqs:
         raise KernelError("attention_prefill_tc: a per-sequence array is shorter than n_seqs")
+    if not scale > 0:
+        raise KernelError(f"attention_prefill_tc: the scale must be positive, got {scale}")
     _work(2 * _nbytes(q) + 2.0 * STEP_HINT["kv_total"] * n_kv * head_dim * 2, 4.0 * n_q * head_dim * STEP_HINT["pairs"])
     f = _fn("attention_prefill_tc", "llmie_attention_prefill_tc",
             [_c_void_p] * 8 + [_c_int] * 8 + [_c_float, _c_int, _c_void_p, _c_void_p])
