@@ -81,6 +81,28 @@ __device__ __forceinline__ float exp2_approx(float x) {
   return y;
 }
 
+// Two float32 operations in one instruction (the packed forms of sm_100): what limits the softmax threads is
+// the number of instructions they issue as much as the exponentials.
+__device__ __forceinline__ uint64_t pair_of(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void split_pair(uint64_t p, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(p));
+}
+// (y0, y1) = (x0, x1) * b + c, each still one rounding
+__device__ __forceinline__ void fma_pair(float& y0, float& y1, float x0, float x1, uint64_t b, uint64_t c) {
+  uint64_t y;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(y) : "l"(pair_of(x0, x1)), "l"(b), "l"(c));
+  split_pair(y, y0, y1);
+}
+__device__ __forceinline__ uint64_t add_pair(uint64_t a, float x0, float x1) {
+  uint64_t y;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(y) : "l"(a), "l"(pair_of(x0, x1)));
+  return y;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -295,13 +317,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     auto add_pv = [&](int j, float alpha_j) {
       tc_fence_after_sync();
       const uint32_t col = Cfg::kPvAlias ? (uint32_t)(j & 1) * 128 : (uint32_t)Cfg::kPvCol;
+      const uint64_t alpha_pair = pair_of(alpha_j, alpha_j);
 #pragma unroll
       for (int c0 = 0; c0 < kOut; c0 += 32) {
         uint32_t v[32];
         tmem_ld_32x32(lane_addr + col + half * kOut + c0, v);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha_j, __uint_as_float(v[i]));
+        for (int i = 0; i < 32; i += 2)
+          fma_pair(o[c0 + i], o[c0 + i + 1], o[c0 + i], o[c0 + i + 1], alpha_pair,
+                   pair_of(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
       }
       tc_fence_before_sync();                  // our TMEM reads are done before the arrival below counts
       if (Cfg::kPvAlias) mbar_arrive(&sh.s_free[j & 1]);     // the buffer may take the scores of tile j + 2
@@ -352,7 +377,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const float alpha = exp2_approx((m_run - m_use) * sl2);      // 0 while m_run is -inf
       const float m_scaled = m_use * sl2;
       // pass 2: probabilities, their sum, and P in bfloat16 into the swizzled operand tile
-      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+      uint64_t ls[2] = {0ull, 0ull};             // four running sums, as two pairs
+      const uint64_t sl2_pair = pair_of(sl2, sl2), m_pair = pair_of(-m_scaled, -m_scaled);
       // 32 keys from column c0 of this thread's half: probabilities, summed and packed two to a word
       auto probabilities = [&](int c0, uint32_t (&w)[16]) {
         uint32_t v[32];
@@ -360,9 +386,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         tmem_ld_wait();
         float p[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) p[i] = exp2_approx(fmaf(__uint_as_float(v[i]), sl2, -m_scaled));
+        for (int i = 0; i < 32; i += 2) {
+          float x0, x1;
+          fma_pair(x0, x1, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), sl2_pair, m_pair);
+          p[i] = exp2_approx(x0);
+          p[i + 1] = exp2_approx(x1);
+        }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) ls[i & 3] += p[i];
+        for (int i = 0; i < 32; i += 2) ls[(i >> 1) & 1] = add_pair(ls[(i >> 1) & 1], p[i], p[i + 1]);
 #pragma unroll
         for (int i = 0; i < 16; ++i) w[i] = pack_bf16(p[2 * i], p[2 * i + 1]);
       };
@@ -391,7 +422,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       if (!Cfg::kPvAlias) mbar_arrive(&sh.s_free[b]);
       fence_proxy_async_smem();                // P is visible to the tensor core's reads
       mbar_arrive(&sh.p_ready);
-      l_run = fmaf(l_run, alpha, (ls[0] + ls[1]) + (ls[2] + ls[3]));
+      float l0, l1, l2, l3;
+      split_pair(ls[0], l0, l1);
+      split_pair(ls[1], l2, l3);
+      l_run = fmaf(l_run, alpha, (l0 + l1) + (l2 + l3));
       m_run = m_new;
       alpha_prev = alpha;
     }
