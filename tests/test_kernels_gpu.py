@@ -65,6 +65,36 @@ def test_add_rmsnorm(dtype, d):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d", [8, 264, 2048, 3080, 4096])
+def test_add_rmsnorm_many_rows(dtype, d):
+    """A prompt's worth of rows (more blocks than the GPU holds at once), one row far from the others' scale,
+    also with gathered rows."""
+    g = torch.Generator().manual_seed(2)
+    T, eps = 1030, 1e-5
+    h = torch.randn(T, d, generator=g) * 2
+    h[5] *= 40.0                                                # one row far from the others' scale
+    delta = torch.randn(T, d, generator=g).to(dtype)
+    w = torch.rand(d, generator=g) + 0.5
+    h_dev = h.clone().to(DEV)
+    out = torch.empty(T, d, dtype=dtype, device=DEV)
+    ops().add_rmsnorm(h_dev, delta.to(DEV), w.to(DEV), eps, out)
+    h_ref = h + delta.float()
+    y_ref = plain.rms_norm(h_ref, w, eps)
+    assert torch.allclose(h_dev.cpu(), h_ref, atol=1e-6, rtol=1e-6)
+    assert torch.allclose(out.float().cpu(), y_ref, atol=tol(dtype, 3e-6, 3e-2), rtol=tol(dtype, 3e-6, 1e-2))
+    h2 = h.clone().to(DEV)
+    ops().add_rmsnorm(h2, None, w.to(DEV), eps, out)
+    assert torch.equal(h2.cpu(), h)
+    assert torch.allclose(out.float().cpu(), plain.rms_norm(h, w, eps), atol=tol(dtype, 3e-6, 3e-2), rtol=1e-2)
+    rows = torch.randperm(T, generator=g)[:1024].to(torch.int32)
+    h3 = h.clone().to(DEV)
+    out3 = torch.empty(1024, d, dtype=dtype, device=DEV)
+    ops().add_rmsnorm(h3, delta.to(DEV), w.to(DEV), eps, out3, rows.to(DEV))
+    assert torch.equal(h3.cpu(), h)
+    assert torch.allclose(out3.float().cpu(), y_ref[rows.long()], atol=tol(dtype, 3e-6, 3e-2), rtol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("ff", [192, 250, 8192])
 def test_swiglu(dtype, ff):
     g = torch.Generator().manual_seed(2)
