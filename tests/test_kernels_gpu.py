@@ -477,7 +477,8 @@ def test_attention_prefill_tc(n_q, n_kv, hd):
     o = ops()
     dtype = torch.bfloat16
     assert o.attention_prefill_tc_supported(hd, 64, dtype)
-    starts, news = [0, 70, 3, 200, 0, 130], [50, 9, 300, 129, 1, 128]
+    # the last two run over six and eight key tiles: both score buffers and every barrier phase come round again
+    starts, news = [0, 70, 3, 200, 0, 130, 0, 600], [50, 9, 300, 129, 1, 128, 700, 300]
     totals = [s + n for s, n in zip(starts, news)]
     pg = Paged(totals, n_kv, hd, dtype, seed=hd + n_q)
     T = sum(news)
