@@ -386,6 +386,89 @@ def run_per_kernel(args, engine, pk: dict) -> str:
     return "\n".join(parts)
 
 
+# ------------------------------------------------------------------------------------------ attention kernels alone
+def attention_sweep(heads: int, kv_heads: int, head_dim: int, pk: dict) -> str:
+    """The two attention kernels alone, at several batch sizes and context lengths, against the measured peaks:
+    the one-token kernel by the cache bytes it has to read, the prompt kernel by its FLOPs. Every case is 16
+    launches in one CUDA graph over caches that rotate through more than the L2 holds; CUDA events around two
+    replays."""
+    import torch
+    from llm_infer_engine_b200.kernels import ops
+    dev, P = "cuda", 64
+    ops.set_pdl(False)                      # a launch may not start while the one before it runs: these are kernel times
+
+    def timed(call, n=16):
+        for i in range(3):
+            call(i)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(n):
+                call(i)
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (2 * n)
+
+    lines = [f"Attention kernels alone, {heads} query / {kv_heads} KV heads of {head_dim}, bfloat16 "
+             f"(peaks: {pk['hbm_gbs']:.0f} GB/s, {pk['bf16_tflops']:.0f} TFLOP/s, {pk['source']}).", "",
+             "### one token a sequence (`attention_decode_mma` with rotation and cache write inside)", "",
+             "| batch | context | MB of cache read | us | GB/s | of HBM peak |", "|---|---|---|---|---|---|"]
+    gen = torch.Generator(device=dev).manual_seed(0)
+    for batch, ctx in [(1, 512), (8, 512), (32, 512), (64, 512), (128, 512), (64, 1024), (16, 1200), (8, 3500),
+                       (64, 3500)]:
+        pages_per = (ctx + 16 + P - 1) // P
+        nbytes = batch * ctx * kv_heads * head_dim * 2 * 2
+        copies = max(2, int(300e6 // nbytes) + 1)
+        ks = [torch.randn(batch * pages_per + 1, kv_heads, P, head_dim, device=dev, generator=gen).to(torch.bfloat16)
+              for _ in range(copies)]
+        vs = [torch.randn(batch * pages_per + 1, kv_heads, P, head_dim, device=dev, generator=gen).to(torch.bfloat16)
+              for _ in range(copies)]
+        table = torch.randperm(batch * pages_per, device=dev, generator=gen).to(torch.int32).view(batch, pages_per)
+        qkv = torch.randn(batch, (heads + 2 * kv_heads) * head_dim, device=dev, generator=gen).to(torch.bfloat16)
+        out = torch.empty(batch, heads * head_dim, dtype=torch.bfloat16, device=dev)
+        rope = torch.randn(ctx + 64, head_dim // 2, 2, device=dev, generator=gen)
+        slots = torch.arange(batch, device=dev, dtype=torch.int32)
+        lens = torch.full((batch,), ctx, device=dev, dtype=torch.int32)
+        pages = ops.attention_decode_mma_pages(batch, heads, kv_heads, ctx)
+        n_runs = ((ctx + 63) // 64 + pages - 1) // pages
+        counters = torch.zeros(ops.decode_counter_ints(batch, heads, kv_heads) + 64, dtype=torch.int32, device=dev)
+        scratch = torch.empty(max(1, ops.decode_scratch_floats(batch, heads, head_dim, n_runs)), dtype=torch.float32,
+                              device=dev)
+        us = timed(lambda i: ops.attention_decode_mma_rope(
+            qkv, ks[i % copies], vs[i % copies], out, rope, slots, lens, table.contiguous(), P, heads, kv_heads,
+            head_dim, head_dim ** -0.5, 0, pages, n_runs, True, counters=counters, scratch=scratch))
+        gbs = nbytes / us / 1e3
+        lines.append(f"| {batch} | {ctx} | {nbytes / 1e6:.1f} | {us:.1f} | {gbs:.0f} | {100 * gbs / pk['hbm_gbs']:.0f} % |")
+        del ks, vs
+    lines += ["", "### prompts (`attention_prefill_tc`, causal, from position 0)", "",
+              "| prompts | tokens each | GFLOP | us | TFLOP/s | of bf16 peak |", "|---|---|---|---|---|---|"]
+    for n_seqs, T in [(8, 512), (3, 1000), (1, 2048), (1, 4096), (1, 8192), (4, 2048)]:
+        pages_per = (T + P - 1) // P
+        k = torch.randn(n_seqs * pages_per + 1, kv_heads, P, head_dim, device=dev, generator=gen).to(torch.bfloat16)
+        v = torch.randn(n_seqs * pages_per + 1, kv_heads, P, head_dim, device=dev, generator=gen).to(torch.bfloat16)
+        table = torch.arange(n_seqs * pages_per, device=dev, dtype=torch.int32).view(n_seqs, pages_per).contiguous()
+        q = torch.randn(n_seqs * T, heads * head_dim, device=dev, generator=gen).to(torch.bfloat16)
+        out = torch.empty_like(q)
+        cu = torch.arange(0, (n_seqs + 1) * T, T, device=dev, dtype=torch.int32)
+        slots = torch.arange(n_seqs, device=dev, dtype=torch.int32)
+        start = torch.zeros(n_seqs, device=dev, dtype=torch.int32)
+        us = timed(lambda i: ops.attention_prefill_tc(q, k, v, out, cu, slots, start, table, P, n_seqs, T, heads,
+                                                      kv_heads, head_dim, head_dim ** -0.5, 0), n=8)
+        ops.check_tc_status(dev)
+        flops = n_seqs * 4.0 * heads * head_dim * (T * (T + 1) / 2)
+        tf = flops / us / 1e6
+        lines.append(f"| {n_seqs} | {T} | {flops / 1e9:.1f} | {us:.1f} | {tf:.0f} | {100 * tf / pk['bf16_tflops']:.0f} % |")
+        del k, v, q, out
+    ops.set_pdl(True)
+    return "\n".join(lines)
+
+
 # ------------------------------------------------------------------------------------------ the two arms
 def run_ours(args):
     import torch
@@ -394,6 +477,13 @@ def run_ours(args):
         return 1
     from llm_infer_engine_b200 import Engine
     pk = peaks()
+    if args.attention_sweep:
+        text = attention_sweep(args.heads, args.kv_heads, args.head_dim, pk)
+        print(text)
+        if args.per_kernel_out:
+            with open(args.per_kernel_out, "w", encoding="utf-8") as f:
+                f.write(text + "\n")
+        return 0
     if args.shape:                                          # one of the larger workloads alone, at full depth
         cfg = CONFIG_3B if args.shape == "3b" else CONFIG_8B
         n = args.layers or cfg["num_hidden_layers"]
@@ -555,6 +645,11 @@ def main():
     ap.add_argument("--per-kernel", action="store_true",
                     help="also time every kernel of the eager steps and print the tables (stderr)")
     ap.add_argument("--per-kernel-out", default="", help="write the per-kernel tables to this file as well")
+    ap.add_argument("--attention-sweep", action="store_true",
+                    help="time the two attention kernels alone at several batch sizes and contexts; prints a table")
+    ap.add_argument("--heads", type=int, default=32, help="query heads of --attention-sweep")
+    ap.add_argument("--kv-heads", type=int, default=8, help="KV heads of --attention-sweep")
+    ap.add_argument("--head-dim", type=int, default=64, choices=[64, 128], help="head size of --attention-sweep")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")

@@ -498,7 +498,7 @@ static int decode_mma_entry(const void* q, const void* k_cache, const void* v_ca
   for (int i = 0; i < 4; ++i) {
     const int w = options[i];
     if (w * tile_bytes > 200 * 1024) continue;
-    int per_sm = (220 * 1024) / (w * tile_bytes);
+    int per_sm = (227 * 1024) / (w * tile_bytes + 1024);                      // 1 KB of every block is the system's
     if (hd == 64 && per_sm > 16 / w) per_sm = 16 / w > 0 ? 16 / w : 1;       // registers
     if (per_sm < 1) continue;
     const long long slots = 148LL * per_sm;
