@@ -196,6 +196,9 @@ class Cache:
             raise CacheError(f"slot {slot} is given back but is not held (freed twice?)")
         for g in self._groups.values():
             g.table.close_slot(slot)
+            # The row names the scratch page again: whatever a later step addresses behind a sequence's last mapped
+            # page must never lead to a page that has since been given to another sequence.
+            g.block_table[slot].fill_(self.n_pages)
         self.slots.give_back(slot)
         self.lengths[slot] = 0
         self._mapped_upto[slot] = 0

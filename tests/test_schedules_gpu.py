@@ -259,3 +259,7 @@ def test_captured_lone_prompt_steps(dtype):
     assert len(engine._prefill_graphs) == PrefillGraph.KEEP and T not in engine._prefill_graphs
     engine.cache.check()
     assert engine.cache.free_slots() == engine.cache.n_slots
+    # a slot that was given back names the scratch page in every entry of its block table again, never a page
+    # that another sequence may hold by now
+    for group in engine.cache._groups.values():
+        assert bool((group.block_table == engine.cache.n_pages).all())
