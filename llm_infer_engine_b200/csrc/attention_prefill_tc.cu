@@ -229,6 +229,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         issued = jt + 1;
       }
       if (*abort) {   // let copies that are still in flight land before the block gives its memory up
+        for (unsigned spin = 0; spin < (1u << 16) && !mbar_test(&sh.q_full, 0); ++spin) __nanosleep(64);
         for (int jt = max(0, issued - 2); jt < issued; ++jt) {
           uint64_t* kb = &sh.k_full[jt % Cfg::kKStages];
           uint64_t* vb = &sh.v_full[jt % Cfg::kVStages];
