@@ -230,8 +230,10 @@ template <int NB>
 static int launch_nb(int epi, const void* x, const void* W, void* out, int batch, int K, int ldo, int tiles,
                      int tile_stride, int hi_delta, cudaStream_t stream) {
   const int chunks = K / 32;
+  // An SM holds about 16 of these warps (registers). Doubling the warps of a block must leave every block
+  // resident at once: 192 tiles of 16 warps would run as 148 blocks and then 44.
   int warps = 4;
-  while (warps < 16 && tiles * warps < 148 * 16 && chunks >= warps * 2 * kSkUnroll) warps *= 2;
+  while (warps < 16 && tiles * warps * 2 <= 148 * 16 && chunks >= warps * 2 * kSkUnroll) warps *= 2;
   if (warps >= 16) return launch_epi<NB, 16>(epi, x, W, out, batch, K, ldo, tiles, tile_stride, hi_delta, stream);
   if (warps >= 8) return launch_epi<NB, 8>(epi, x, W, out, batch, K, ldo, tiles, tile_stride, hi_delta, stream);
   return launch_epi<NB, 4>(epi, x, W, out, batch, K, ldo, tiles, tile_stride, hi_delta, stream);

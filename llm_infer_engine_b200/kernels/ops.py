@@ -477,13 +477,16 @@ SKINNY_ADD_BEST_BATCH = 16     # the `h +=` form saves a pass over h as well: 3.
                                # library product of the output / down projection at 16 rows (1B shape); equal at 32
 
 
-def gemm_skinny_add_wins(rows: int, n: int, device) -> bool:
+def gemm_skinny_add_wins(rows: int, n: int, k: int, device) -> bool:
     """Whether `h += x w^T` is better done by gemm_skinny than by the library product followed by the add in the
-    next norm kernel. Up to 8 rows always. From 9 to 16 rows only while the kernel's blocks (16 weight rows each,
-    one block an SM at the many warps it then uses) fit the GPU at once: 3,072 outputs are 192 blocks on 148 SMs and
-    take two rounds (measured at 16 rows, output / down projection: 2,048 outputs 4.0 / 9.4 us against the library's
-    5.6 / 12.8 us; 3,072 outputs 8.4 / 16.2 us against 7.0 / 13.8 us; 4,096 outputs 10.6 / 29.6 us against 9.3 / 22.9 us)."""
-    return rows <= SKINNY_BEST_BATCH or (rows <= SKINNY_ADD_BEST_BATCH and n // 16 <= _sms(device))
+    next norm kernel. Up to 8 rows always. From 9 to 16 rows only for up to one block (16 weight rows) an SM, the
+    1B shape's 2,048 outputs: there it takes 4.0 / 9.3 us (output / down projection, 16 rows) against the library's
+    5.7 / 12.9 us. Wider outputs were measured inside whole steps (3B shape, 16 sequences of 1,400 tokens): library
+    for both 2.254 ms a step, this kernel for the output projection 2.286 ms, for both 2.329 ms, although alone the
+    kernel is level with the library there (3,072 x 3,072: 6.6 against 7.0 us)."""
+    if rows <= SKINNY_BEST_BATCH:
+        return True
+    return rows <= SKINNY_ADD_BEST_BATCH and n // 16 <= _sms(device)
 
 
 def gemm_skinny_ok(batch: int, n: int, k: int, epilogue: int = SKINNY_STORE_BF16) -> bool:

@@ -1,7 +1,7 @@
 """Matrix products y = x W^T of the parts (no bias), chosen by the weight's precision.
 
-bfloat16 weights: up to 8 rows this library's skinny kernel (up to 16 with the add, while its blocks
-fit the GPU at once); above that the library GEMM (cuBLAS through torch.mm), as the reference does with nn.Linear (src/model.py:17-19,34-37,137),
+bfloat16 weights: up to 8 rows this library's skinny kernel (up to 16 with the add, for up to one of its
+blocks an SM); above that the library GEMM (cuBLAS through torch.mm), as the reference does with nn.Linear (src/model.py:17-19,34-37,137),
 accumulating in float32, except where this library's weight-streaming tcgen05 kernel measured faster
 (`ops.gemm_stream_wins`: a vocabulary-sized head at 33 to 64 rows). float32 weights: this
 library's own FMA kernel, true 32-bit with a fixed summation order; that is the whole of
@@ -53,7 +53,7 @@ class Linear:
         exists. Returns False (and does nothing) otherwise."""
         if self.weight.dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
             return False
-        if not ops.gemm_skinny_add_wins(x.shape[0], self.out_features, x.device) \
+        if not ops.gemm_skinny_add_wins(x.shape[0], self.out_features, self.in_features, x.device) \
                 or not ops.gemm_skinny_ok(x.shape[0], self.out_features, self.in_features):
             return False
         ops.gemm_skinny(x, self.weight, h, ops.SKINNY_ADD_F32)
