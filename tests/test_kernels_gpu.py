@@ -789,3 +789,34 @@ def check_attention_decode_mma(n_q, n_kv, hd, n_seqs, pages_per_run):
                                 pg.dense_v[i].float(), [lens[i] - 1], hd ** -0.5, window)[0]
             assert torch.allclose(got[i], ref, atol=3e-2), (window, i, float((got[i] - ref).abs().max()))
     assert int(counters.abs().sum()) == 0          # left clean
+
+
+@pytest.mark.parametrize("hd,window", [(64, 0), (128, 0), (64, 256)])
+def test_attention_prefill_tc_is_repeatable(hd, window):
+    """The prompt kernel overlaps a key tile's second product with the next tile's softmax and reuses its score
+    buffers for other data; a missing wait would show as outputs that change from run to run. Twelve runs of
+    unequal sequences at start positions above zero must agree bit for bit."""
+    o = ops()
+    n_q, n_kv, P = 8, 2, 64
+    lens, starts = [700, 129, 1000, 64, 1], [0, 300, 77, 1000, 5]
+    n = len(lens)
+    pages_per = max((s + l + P - 1) // P for s, l in zip(starts, lens))
+    g = torch.Generator().manual_seed(31)
+    k = torch.randn(n * pages_per + 1, n_kv, P, hd, generator=g).to(torch.bfloat16).to(DEV)
+    v = torch.randn(n * pages_per + 1, n_kv, P, hd, generator=g).to(torch.bfloat16).to(DEV)
+    bt = torch.randperm(n * pages_per, generator=g).to(torch.int32).view(n, pages_per).contiguous().to(DEV)
+    T = sum(lens)
+    q = torch.randn(T, n_q * hd, generator=g).to(torch.bfloat16).to(DEV)
+    cu = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32, device=DEV)
+    slots = torch.arange(n, dtype=torch.int32, device=DEV)
+    st = torch.tensor(starts, dtype=torch.int32, device=DEV)
+    first = None
+    for _ in range(12):
+        out = torch.full((T, n_q * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        o.attention_prefill_tc(q, k, v, out, cu, slots, st, bt, P, n, max(lens), n_q, n_kv, hd, hd ** -0.5, window)
+        if first is None:
+            first = out
+            assert not torch.isnan(out.float()).any()
+        else:
+            assert torch.equal(out, first)
+    o.check_tc_status(DEV)
